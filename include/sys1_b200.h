@@ -1,0 +1,99 @@
+/*
+ * sys1_b200 - C ABI of the B200 (sm_100a) dense-projection / gated-delta-rule path.
+ *
+ * This is the boundary a sys1 maintainer binds from Rust (`extern "C"`) in place of the candle calls on the
+ * model hot path. Every pointer below is a DEVICE pointer unless the name ends in `_host`; activations and
+ * weights are bf16, row-major, rows at least 16-byte aligned (leading dimensions are multiples of 8 elements).
+ * The caller owns every buffer it passes; the library keeps no copy of weights and allocates no activation.
+ *
+ * Conventions
+ *   - every function returns 0 (S1_OK) or a negative S1_E* code; nothing throws or aborts across the boundary;
+ *     `s1_last_error` gives the message of the last failing call on that context;
+ *   - work is enqueued on the context's stream and is asynchronous; `s1_sync` joins it and reports errors the
+ *     kernels recorded on the device (a wait inside a kernel that ran out of time, for instance);
+ *   - one host thread per context at a time (the reference runs one `predict_batch` at a time,
+ *     src/batching.rs:121); contexts on different GPUs are independent;
+ *   - there is no CPU or library fallback: on a machine without an sm_100 GPU `s1_ctx_create` fails.
+ */
+#ifndef SYS1_B200_H_
+#define SYS1_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct s1_ctx s1_ctx;
+
+enum {
+    S1_OK = 0,
+    S1_EINVAL = -1,   /* bad argument: null pointer, shape or alignment the kernels cannot take */
+    S1_ECUDA = -2,    /* a CUDA runtime / driver call failed */
+    S1_EDEVICE = -3,  /* not an sm_100 device, or no device */
+    S1_EKERNEL = -4,  /* a kernel recorded an error status (bounded wait ran out) */
+    S1_ENOMEM = -5
+};
+
+/* Epilogue fused behind the contraction. */
+enum {
+    S1_EPI_NONE = 0,   /* y = x W^T                                                                         */
+    S1_EPI_GEGLU = 1,  /* w is [2I, K]; y[:, c] = bf16(bf16(gelu_erf(p[:, c])) * p[:, c + I]), c < I          */
+    S1_EPI_SWIGLU = 2  /* w = gate_proj [I, K], w_up = up_proj [I, K]; y = bf16(bf16(silu(x Wg^T)) * x Wu^T) */
+};
+
+/* Activation applied after the bias (S1_EPI_NONE only). */
+enum { S1_ACT_NONE = 0, S1_ACT_RELU = 1, S1_ACT_GELU = 2 };
+
+/*
+ * Replaces `device::load` (src/device.rs:43-56, which always opens device 0): opens GPU `device_ordinal`.
+ * `cuda_stream` is a cudaStream_t to enqueue on, or NULL to let the context create its own.
+ */
+int s1_ctx_create(int device_ordinal, void* cuda_stream, s1_ctx** out);
+int s1_ctx_destroy(s1_ctx* ctx);
+const char* s1_last_error(const s1_ctx* ctx);
+/* Joins the stream; returns S1_EKERNEL if any kernel since the last sync recorded an error. */
+int s1_sync(s1_ctx* ctx);
+/* Number of GPUs visible (replaces the single-device assumption of src/device.rs:48-51). */
+int s1_device_count(int* out);
+/* Number of kernels this context has launched so far. */
+long long s1_launch_count(const s1_ctx* ctx);
+/* Tuning knob: "gemm_bn" = 0 (auto), 128 or 256 accumulator columns per tile. */
+int s1_set_option(s1_ctx* ctx, const char* name, long long value);
+
+/*
+ * One projection of the reference: a candle `Linear` (weight [N, K] as `vb.get((output, input), "weight")`
+ * stores it, src/archs/modernbert.rs:1036-1046, src/archs/qwen35_text.rs:174-176) plus what follows it.
+ * `ldw` lets a tensor-parallel rank pass a row range (column-parallel) or a K range (row-parallel) of the
+ * full matrix without copying it.
+ */
+typedef struct s1_linear_desc {
+    const void* w;     /* bf16 [N, K], row stride ldw                                              */
+    long long ldw;
+    const void* w_up;  /* S1_EPI_SWIGLU only: up_proj bf16 [N, K], row stride ldw_up; else NULL    */
+    long long ldw_up;
+    const void* bias;  /* bf16 [N] or NULL (S1_EPI_NONE only)                                      */
+    int N;             /* rows of w; S1_EPI_GEGLU: N = 2 I                                          */
+    int K;
+    int epilogue;      /* S1_EPI_*                                                                 */
+    int act;           /* S1_ACT_*                                                                 */
+} s1_linear_desc;
+
+/*
+ * y[T, N_out] = epilogue(x[T, K] W^T) (+ residual), N_out = N (S1_EPI_NONE, S1_EPI_SWIGLU) or N / 2 (GEGLU).
+ * Rounding follows the reference op by op: the contraction accumulates in f32 and is rounded to bf16 (candle's
+ * bf16 matmul), the bias / activation / gate product / residual add each round to bf16 again
+ * (src/kernels/modernbert.cu:11-13; src/archs/modernbert.rs:882-886; src/archs/qwen35_text.rs:238-239,938-939).
+ * Replaces: modernbert `Attention::forward` Wqkv / Wo (src/archs/modernbert.rs:184-191), `Mlp::forward`
+ * (:521-533), qwen35 `Mlp::forward` (src/archs/qwen35_text.rs:232-240), q/k/v/o_proj (:314-339,410),
+ * in_proj_* / out_proj (:516,567-568,605-628) and the biased head Linears (src/models/laya.rs:133-155).
+ * T is the packed token count (any value >= 1); K and N_out must be multiples of 8.
+ */
+int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, const void* residual,
+              long long ldr, void* y, long long ldy, int T);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SYS1_B200_H_ */

@@ -1,0 +1,71 @@
+"""ctypes binding of `libsys1_b200.so` (the C ABI in `include/sys1_b200.h`).
+
+There is no fallback of any kind: if the library is missing, or a context cannot be opened on an sm_100 GPU,
+the call raises. PyTorch is used by the callers only to hold device memory and streams; the pointers handed
+to the library are plain addresses.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libsys1_b200.so"
+
+S1_OK = 0
+S1_EINVAL, S1_ECUDA, S1_EDEVICE, S1_EKERNEL, S1_ENOMEM = -1, -2, -3, -4, -5
+EPI_NONE, EPI_GEGLU, EPI_SWIGLU = 0, 1, 2
+ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
+
+_ERR_NAMES = {-1: "S1_EINVAL", -2: "S1_ECUDA", -3: "S1_EDEVICE", -4: "S1_EKERNEL", -5: "S1_ENOMEM"}
+
+
+class S1Error(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{_ERR_NAMES.get(code, code)}: {message}")
+        self.code = code
+
+
+class LinearDesc(C.Structure):
+    _fields_ = [
+        ("w", C.c_void_p), ("ldw", C.c_longlong),
+        ("w_up", C.c_void_p), ("ldw_up", C.c_longlong),
+        ("bias", C.c_void_p),
+        ("N", C.c_int), ("K", C.c_int), ("epilogue", C.c_int), ("act", C.c_int),
+    ]
+
+
+# name -> (restype, argtypes); kept in one table so the symbol-export test can walk it.
+SIGNATURES = {
+    "s1_device_count": (C.c_int, [C.POINTER(C.c_int)]),
+    "s1_ctx_create": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "s1_ctx_destroy": (C.c_int, [C.c_void_p]),
+    "s1_last_error": (C.c_char_p, [C.c_void_p]),
+    "s1_sync": (C.c_int, [C.c_void_p]),
+    "s1_launch_count": (C.c_longlong, [C.c_void_p]),
+    "s1_set_option": (C.c_int, [C.c_void_p, C.c_char_p, C.c_longlong]),
+    "s1_linear": (C.c_int, [C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
+                            C.c_void_p, C.c_longlong, C.c_int]),
+}
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    """dlopen the in-tree library and attach signatures. Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m sys1_b200.build` (nvcc, sm_100a). "
+            "There is no CPU or library fallback for this path.")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

@@ -1,0 +1,235 @@
+// C-ABI entry points: context management and the fused projection (s1_linear).
+#include <string.h>
+
+#include <new>
+
+#include "context.h"
+#include "gemm_sm100.cuh"
+
+using namespace s1;
+
+// ---------------------------------------------------------------------------------------------- context
+extern "C" int s1_device_count(int* out) {
+    if (!out) return S1_EINVAL;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        *out = 0;
+        return S1_EDEVICE;
+    }
+    *out = n;
+    return S1_OK;
+}
+
+extern "C" int s1_ctx_create(int device_ordinal, void* cuda_stream, s1_ctx** out) {
+    if (!out) return S1_EINVAL;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) return S1_EDEVICE;
+    if (device_ordinal < 0 || device_ordinal >= n) return S1_EINVAL;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) return S1_ECUDA;
+    if (prop.major != 10) return S1_EDEVICE;  // the kernels are sm_100a only; there is no other path
+    if (cudaSetDevice(device_ordinal) != cudaSuccess) return S1_ECUDA;
+
+    s1_ctx* ctx = new (std::nothrow) s1_ctx();
+    if (!ctx) return S1_ENOMEM;
+    ctx->device = device_ordinal;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cuda_stream) {
+        ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    } else {
+        if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+            delete ctx;
+            return S1_ECUDA;
+        }
+        ctx->own_stream = true;
+    }
+    if (cudaMalloc(&ctx->status_dev, 4 * sizeof(int)) != cudaSuccess ||
+        cudaMemset(ctx->status_dev, 0, 4 * sizeof(int)) != cudaSuccess) {
+        delete ctx;
+        return S1_ECUDA;
+    }
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+        qres != cudaDriverEntryPointSuccess) {
+        cudaFree(ctx->status_dev);
+        delete ctx;
+        return S1_ECUDA;
+    }
+    ctx->encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+    *out = ctx;
+    return S1_OK;
+}
+
+extern "C" int s1_ctx_destroy(s1_ctx* ctx) {
+    if (!ctx) return S1_EINVAL;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return S1_OK;
+}
+
+extern "C" const char* s1_last_error(const s1_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+extern "C" long long s1_launch_count(const s1_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int s1_set_option(s1_ctx* ctx, const char* name, long long value) {
+    if (!ctx || !name) return S1_EINVAL;
+    if (strcmp(name, "gemm_bn") == 0) {
+        if (value != 0 && value != 128 && value != 256)
+            return s1_fail(ctx, S1_EINVAL, "gemm_bn must be 0, 128 or 256 (got %lld)", value);
+        ctx->opt_gemm_bn = static_cast<int>(value);
+        return S1_OK;
+    }
+    return s1_fail(ctx, S1_EINVAL, "unknown option '%s'", name);
+}
+
+extern "C" int s1_sync(s1_ctx* ctx) {
+    if (!ctx) return S1_EINVAL;
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    S1_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    int st[4] = {0, 0, 0, 0};
+    S1_CUDA_OK(ctx, cudaMemcpy(st, ctx->status_dev, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st[0] != 0) {
+        cudaMemset(ctx->status_dev, 0, sizeof(st));
+        return s1_fail(ctx, S1_EKERNEL, "kernel gave up on a bounded wait: code %d block %d role %d tile %d", st[0],
+                       st[1], st[2], st[3]);
+    }
+    return S1_OK;
+}
+
+int s1_get_tmap(s1_ctx* ctx, const void* ptr, long long rows, long long cols, long long ld, int box_rows,
+                int box_cols, int elem_bytes, bool swizzle128, CUtensorMap* out) {
+    S1TmapKey key{ptr, rows, cols, ld, box_rows, swizzle128 ? box_cols : -box_cols, elem_bytes};
+    auto it = ctx->tmaps.find(key);
+    if (it != ctx->tmaps.end()) {
+        *out = it->second;
+        return S1_OK;
+    }
+    CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t gstr[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = ctx->encode(&m, dt, 2, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return s1_fail(ctx, S1_ECUDA, "cuTensorMapEncodeTiled failed (%d) ptr=%p rows=%lld cols=%lld ld=%lld box=%dx%d",
+                       static_cast<int>(r), ptr, rows, cols, ld, box_rows, box_cols);
+    if (ctx->tmaps.size() > 4096) ctx->tmaps.clear();
+    ctx->tmaps.emplace(key, m);
+    *out = m;
+    return S1_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- s1_linear
+template <int BN, int EPI>
+static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1,
+                       const GemmParams& p) {
+    using Cfg = GemmCfg<BN>;
+    auto kern = s1_gemm_kernel<BN, EPI>;
+    static thread_local int configured_device = -1;
+    if (configured_device != ctx->device) {
+        S1_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        configured_device = ctx->device;
+    }
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    kern<<<grid, kGemmThreads, Cfg::kSmemBytes, ctx->stream>>>(a, b0, b1, p);
+    S1_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return S1_OK;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, const void* residual,
+                         long long ldr, void* y, long long ldy, int T) {
+    if (!ctx) return S1_EINVAL;
+    if (!lin || !x || !y || !lin->w) return s1_fail(ctx, S1_EINVAL, "s1_linear: null pointer");
+    const int epi = lin->epilogue;
+    if (epi != S1_EPI_NONE && epi != S1_EPI_GEGLU && epi != S1_EPI_SWIGLU)
+        return s1_fail(ctx, S1_EINVAL, "s1_linear: unknown epilogue %d", epi);
+    if (T < 1 || lin->N < 1 || lin->K < 1)
+        return s1_fail(ctx, S1_EINVAL, "s1_linear: T=%d N=%d K=%d must be positive", T, lin->N, lin->K);
+    if (epi == S1_EPI_GEGLU && (lin->N % 2)) return s1_fail(ctx, S1_EINVAL, "s1_linear: GEGLU needs even N");
+    if (epi == S1_EPI_SWIGLU && !lin->w_up) return s1_fail(ctx, S1_EINVAL, "s1_linear: SWIGLU needs w_up");
+    if (epi != S1_EPI_NONE && (lin->bias || lin->act != S1_ACT_NONE || residual))
+        return s1_fail(ctx, S1_EINVAL, "s1_linear: bias / act / residual are not defined behind a gated epilogue");
+    if (lin->act < S1_ACT_NONE || lin->act > S1_ACT_GELU)
+        return s1_fail(ctx, S1_EINVAL, "s1_linear: unknown act %d", lin->act);
+    const int n_out = (epi == S1_EPI_GEGLU) ? lin->N / 2 : lin->N;
+    if ((lin->K % 8) || (n_out % 8))
+        return s1_fail(ctx, S1_EINVAL, "s1_linear: K=%d and N_out=%d must be multiples of 8", lin->K, n_out);
+    if (ldx < lin->K || lin->ldw < lin->K || ldy < n_out || (residual && ldr < n_out) ||
+        (lin->w_up && lin->ldw_up < lin->K))
+        return s1_fail(ctx, S1_EINVAL, "s1_linear: a leading dimension is smaller than its row");
+    if ((ldx % 8) || (lin->ldw % 8) || (ldy % 8) || (residual && (ldr % 8)) || (lin->w_up && (lin->ldw_up % 8)))
+        return s1_fail(ctx, S1_EINVAL, "s1_linear: leading dimensions must be multiples of 8 elements (16 bytes)");
+    if (!aligned16(x) || !aligned16(lin->w) || !aligned16(y) || !aligned16(residual) || !aligned16(lin->w_up))
+        return s1_fail(ctx, S1_EINVAL, "s1_linear: pointers must be 16-byte aligned");
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+
+    // Tile width: 256 accumulator columns unless 128 fills the 148 SMs' waves visibly better.
+    const int tiles_m = (T + kBM - 1) / kBM;
+    auto n_tiles_for = [&](int bn) {
+        const int w = (epi == S1_EPI_NONE) ? bn : bn / 2;
+        return (n_out + w - 1) / w;
+    };
+    auto wave_eff = [&](int bn) {
+        const long long t = static_cast<long long>(tiles_m) * n_tiles_for(bn);
+        const long long waves = (t + ctx->sm_count - 1) / ctx->sm_count;
+        return static_cast<double>(t) / static_cast<double>(waves * ctx->sm_count);
+    };
+    int bn = ctx->opt_gemm_bn;
+    if (bn == 0) bn = (wave_eff(128) > wave_eff(256) + 0.08) ? 128 : 256;
+
+    GemmParams p;
+    p.M = T;
+    p.n_out = n_out;
+    p.K = lin->K;
+    p.tiles_m = tiles_m;
+    p.tiles_n = n_tiles_for(bn);
+    p.act = lin->act;
+    p.ldy = ldy;
+    p.ldr = ldr;
+    p.y = static_cast<__nv_bfloat16*>(y);
+    p.residual = static_cast<const __nv_bfloat16*>(residual);
+    p.bias = static_cast<const __nv_bfloat16*>(lin->bias);
+    p.status = ctx->status_dev;
+
+    CUtensorMap ta, tb0, tb1;
+    int rc = s1_get_tmap(ctx, x, T, lin->K, ldx, kBM, kBK, 2, true, &ta);
+    if (rc) return rc;
+    rc = s1_get_tmap(ctx, lin->w, lin->N, lin->K, lin->ldw, bn / 2, kBK, 2, true, &tb0);
+    if (rc) return rc;
+    if (epi == S1_EPI_SWIGLU) {
+        rc = s1_get_tmap(ctx, lin->w_up, lin->N, lin->K, lin->ldw_up, bn / 2, kBK, 2, true, &tb1);
+        if (rc) return rc;
+        p.n_tile_stride = bn / 2;
+        p.half1_base = 0;
+    } else if (epi == S1_EPI_GEGLU) {
+        tb1 = tb0;
+        p.n_tile_stride = bn / 2;
+        p.half1_base = n_out;  // gate rows follow the I activated rows
+    } else {
+        tb1 = tb0;
+        p.n_tile_stride = bn;
+        p.half1_base = bn / 2;
+    }
+
+    if (bn == 256) {
+        if (epi == S1_EPI_NONE) return launch_gemm<256, EPI_NONE>(ctx, ta, tb0, tb1, p);
+        if (epi == S1_EPI_GEGLU) return launch_gemm<256, EPI_GEGLU>(ctx, ta, tb0, tb1, p);
+        return launch_gemm<256, EPI_SWIGLU>(ctx, ta, tb0, tb1, p);
+    }
+    if (epi == S1_EPI_NONE) return launch_gemm<128, EPI_NONE>(ctx, ta, tb0, tb1, p);
+    if (epi == S1_EPI_GEGLU) return launch_gemm<128, EPI_GEGLU>(ctx, ta, tb0, tb1, p);
+    return launch_gemm<128, EPI_SWIGLU>(ctx, ta, tb0, tb1, p);
+}

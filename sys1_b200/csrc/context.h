@@ -1,0 +1,70 @@
+// Host-side context shared by the C-ABI entry points: stream, device status word,
+// tensor-map encoder entry point and a small cache of encoded maps.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <unordered_map>
+
+#include "../../include/sys1_b200.h"
+
+struct S1TmapKey {
+    const void* ptr;
+    long long rows, cols, ld;
+    int box_rows, box_cols, elem_bytes;
+    bool operator==(const S1TmapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+               box_cols == o.box_cols && elem_bytes == o.elem_bytes;
+    }
+};
+struct S1TmapKeyHash {
+    size_t operator()(const S1TmapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.ptr);
+        auto mix = [&h](long long v) { h ^= static_cast<size_t>(v) + 0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2); };
+        mix(k.rows);
+        mix(k.cols);
+        mix(k.ld);
+        mix(k.box_rows);
+        mix(k.box_cols);
+        mix(k.elem_bytes);
+        return h;
+    }
+};
+
+struct s1_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    int* status_dev = nullptr;  // int[4], written by kernels on failure
+    long long launches = 0;
+    int opt_gemm_bn = 0;
+    PFN_cuTensorMapEncodeTiled encode = nullptr;
+    std::unordered_map<S1TmapKey, CUtensorMap, S1TmapKeyHash> tmaps;
+    char err[512] = {0};
+};
+
+inline int s1_fail(s1_ctx* ctx, int code, const char* fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+#define S1_CUDA_OK(ctx, call)                                                                        \
+    do {                                                                                             \
+        cudaError_t e__ = (call);                                                                    \
+        if (e__ != cudaSuccess)                                                                      \
+            return s1_fail((ctx), S1_ECUDA, "%s failed: %s", #call, cudaGetErrorString(e__));         \
+    } while (0)
+
+// Encodes (or fetches from the cache) a 2-D tiled tensor map over a row-major matrix whose rows are `ld`
+// elements apart: dim0 = cols (contiguous), dim1 = rows. swizzle128 selects CU_TENSOR_MAP_SWIZZLE_128B.
+int s1_get_tmap(s1_ctx* ctx, const void* ptr, long long rows, long long cols, long long ld, int box_rows,
+                int box_cols, int elem_bytes, bool swizzle128, CUtensorMap* out);

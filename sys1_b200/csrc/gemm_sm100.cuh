@@ -1,0 +1,309 @@
+// Persistent, warp-specialised bf16 projection GEMM for sm_100a:
+//   Y[T, N] = X[T, K] * W[N, K]^T   (f32 accumulate in TMEM, bf16 out)
+// with the reference's follow-up elementwise ops folded into the epilogue
+// (bias add, GeGLU / SwiGLU gating, residual add, bf16 casts in the reference's rounding order).
+//
+// Replaces, per call: candle `Linear::forward` (src/archs/modernbert.rs:184-191,522-532;
+// src/archs/qwen35_text.rs:232-240,314-339,410,516,567-568,605-628) plus the GeGLU kernel
+// (src/kernels/modernbert.cu:4-14) and the residual adds (src/archs/modernbert.rs:882-886,
+// src/archs/qwen35_text.rs:938-939).
+//
+// Roles inside one CTA (one CTA per SM, static round-robin tile schedule):
+//   warp 0      : TMA producer  - X box {64 x 128 rows} and two W boxes {64 x BN/2 rows} per k-block,
+//                 128-byte swizzle, ring of STAGES buffers guarded by full/empty mbarriers
+//   warp 1      : TMEM allocation + single-thread tcgen05.mma issue (M=128, N=BN, K=16 per instruction),
+//                 two TMEM accumulators so the epilogue of tile i overlaps the MMAs of tile i+1
+//   warps 2..5  : epilogue - tcgen05.ld of the warp's TMEM lane quarter, rounding/gating, 16-byte stores
+#pragma once
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+
+namespace s1 {
+
+enum : int { EPI_NONE = 0, EPI_GEGLU = 1, EPI_SWIGLU = 2 };
+enum : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2 };
+
+struct GemmParams {
+    int M;              // packed token rows
+    int n_out;          // output columns written (N for plain, I for gated)
+    int K;
+    int tiles_m, tiles_n;
+    int n_tile_stride;  // W rows advanced per n-tile for the first B box
+    int half1_base;     // W row offset of the second B box (relative to tile_n * n_tile_stride)
+    int act;            // ACT_* applied after bias (plain epilogue only)
+    long long ldy;      // elements between output rows
+    long long ldr;      // elements between residual rows
+    __nv_bfloat16* y;
+    const __nv_bfloat16* residual;  // [M, n_out] or null
+    const __nv_bfloat16* bias;      // [n_out] or null
+    int* status;                    // device int[4]: {code, block, role, tile}; 0 = ok
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kGemmThreads = 192;
+constexpr int kEpiWarp0 = 2;
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kABytes = kBM * kBK * 2;
+    static constexpr int kBHalfBytes = (BN / 2) * kBK * 2;
+    static constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;
+    static constexpr int kTmemCols = 2 * BN;  // two accumulators; 256 or 512, both powers of two
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float gelu_erf_ref(float v) { return v * normcdff(v); }
+__device__ __forceinline__ float silu_ref(float v) { return v / (1.f + __expf(-v)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ void unpack_bf16x2(uint32_t v, float& lo, float& hi) {
+    __nv_bfloat162 t = *reinterpret_cast<__nv_bfloat162*>(&v);
+    lo = __low2float(t);
+    hi = __high2float(t);
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
+               const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::kStages;
+    constexpr bool PAIRED = (EPI != EPI_NONE);
+    constexpr int OUT_W = PAIRED ? BN / 2 : BN;  // output columns per tile
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * Cfg::kStageBytes);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = full0 + 8u * STAGES;
+    const uint32_t tfull0 = full0 + 8u * (2 * STAGES);
+    const uint32_t tempty0 = full0 + 8u * (2 * STAGES + 2);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_kb = (p.K + kBK - 1) / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8u * s, 1);
+            mbar_init(empty0 + 8u * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull0 + 8u * a, 1);
+            mbar_init(tempty0 + 8u * a, 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB0);
+        tma_prefetch_desc(&tmB1);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    int fail_role = 0, fail_tile = -1;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t cnt = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !fail_role; tile += gridDim.x) {
+                const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
+                const int m0 = tm * kBM;
+                const int r0 = tn * p.n_tile_stride;
+                const int r1 = r0 + p.half1_base;
+                for (int kb = 0; kb < num_kb; ++kb, ++cnt) {
+                    const uint32_t s = cnt % STAGES, ph = (cnt / STAGES) & 1u;
+                    if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag)) {
+                        fail_role = 1;
+                        fail_tile = tile;
+                        break;
+                    }
+                    const uint32_t sa = smem_base + s * Cfg::kStageBytes;
+                    const uint32_t fb = full0 + 8u * s;
+                    mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
+                    tma_load_2d(sa, &tmA, kb * kBK, m0, fb);
+                    tma_load_2d(sa + Cfg::kABytes, &tmB0, kb * kBK, r0, fb);
+                    tma_load_2d(sa + Cfg::kABytes + Cfg::kBHalfBytes, &tmB1, kb * kBK, r1, fb);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(1, kBM, BN);
+            uint32_t cnt = 0, it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !fail_role; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
+                if (!mbar_wait(tempty0 + 8u * acc, aph ^ 1u, abort_flag)) {
+                    fail_role = 2;
+                    fail_tile = tile;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++cnt) {
+                    const uint32_t s = cnt % STAGES, ph = (cnt / STAGES) & 1u;
+                    if (!mbar_wait(full0 + 8u * s, ph, abort_flag)) {
+                        fail_role = 3;
+                        fail_tile = tile;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * Cfg::kStageBytes;
+                    const uint64_t da = make_sw128_kmajor_desc(sa);
+                    const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::kABytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        // +32 bytes along K per instruction = +2 in the (addr >> 4) field
+                        umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8u * s);  // smem stage reusable once these MMAs retire
+                }
+                if (fail_role) break;
+                umma_commit(tfull0 + 8u * acc);  // accumulator complete
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------- epilogue warps
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+            const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
+            const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
+            // the whole warp must agree before any .sync.aligned tcgen05 instruction
+            const bool ready = mbar_wait(tfull0 + 8u * acc, aph, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) {
+                fail_role = 4;
+                fail_tile = tile;
+                break;
+            }
+            tc_fence_after();
+            const int row = tm * kBM + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const int col0 = tn * OUT_W;
+            const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+            __nv_bfloat16* yrow = p.y + static_cast<long long>(row) * p.ldy;
+            const __nv_bfloat16* rrow = p.residual ? p.residual + static_cast<long long>(row) * p.ldr : nullptr;
+
+#pragma unroll 1
+            for (int c = 0; c < OUT_W / 32; ++c) {
+                const int col = col0 + c * 32;
+                uint32_t out[16];
+                if constexpr (!PAIRED) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32, v);
+                    uint4 rv[4] = {};
+                    if (rrow && row_ok) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (col + j * 8 < p.n_out)
+                                rv[j] = __ldg(reinterpret_cast<const uint4*>(rrow + col + j * 8));
+                    }
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float a = bf16_round(__uint_as_float(v[2 * j]));
+                        float b = bf16_round(__uint_as_float(v[2 * j + 1]));
+                        if (p.bias) {
+                            const int cc = col + 2 * j;
+                            if (cc < p.n_out) {
+                                a = bf16_round(a + __bfloat162float(p.bias[cc]));
+                                b = bf16_round(b + __bfloat162float(p.bias[cc + 1]));
+                            }
+                        }
+                        if (p.act == ACT_RELU) {
+                            a = fmaxf(a, 0.f);
+                            b = fmaxf(b, 0.f);
+                        } else if (p.act == ACT_GELU) {
+                            a = bf16_round(gelu_erf_ref(a));
+                            b = bf16_round(gelu_erf_ref(b));
+                        }
+                        if (rrow) {
+                            const uint32_t rw = reinterpret_cast<const uint32_t*>(rv)[j];
+                            float r0, r1;
+                            unpack_bf16x2(rw, r0, r1);
+                            a += r0;
+                            b += r1;
+                        }
+                        out[j] = pack_bf16x2(a, b);
+                    }
+                } else {
+                    uint32_t va[32], vg[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32, va);
+                    tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, vg);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float o[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float a = bf16_round(__uint_as_float(va[2 * j + e]));
+                            const float g = bf16_round(__uint_as_float(vg[2 * j + e]));
+                            const float act = bf16_round(EPI == EPI_GEGLU ? gelu_erf_ref(a) : silu_ref(a));
+                            o[e] = act * g;
+                        }
+                        out[j] = pack_bf16x2(o[0], o[1]);
+                    }
+                }
+                if (c == OUT_W / 32 - 1) {
+                    // every TMEM read of this accumulator has landed in registers: hand it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (col + j * 8 < p.n_out) {
+                            *reinterpret_cast<uint4*>(yrow + col + j * 8) =
+                                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    if (fail_role) {
+        // first failing thread of the grid records where it gave up; host turns it into an error
+        if (atomicCAS(p.status, 0, 1) == 0) {
+            p.status[1] = blockIdx.x;
+            p.status[2] = fail_role;
+            p.status[3] = fail_tile;
+        }
+    }
+    if (*abort_flag) {
+        // give copies that are still in flight time to land before shared memory is released
+        __nanosleep(200000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+}  // namespace s1
