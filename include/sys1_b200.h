@@ -48,7 +48,8 @@ enum { S1_ACT_NONE = 0, S1_ACT_RELU = 1, S1_ACT_GELU = 2 };
 
 /*
  * Replaces `device::load` (src/device.rs:43-56, which always opens device 0): opens GPU `device_ordinal`.
- * `cuda_stream` is a cudaStream_t to enqueue on, or NULL to let the context create its own.
+ * `cuda_stream` is the cudaStream_t every call of this context enqueues on; NULL is CUDA's default stream.
+ * The stream stays the caller's.
  */
 int s1_ctx_create(int device_ordinal, void* cuda_stream, s1_ctx** out);
 int s1_ctx_destroy(s1_ctx* ctx);

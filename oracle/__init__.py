@@ -1,0 +1,18 @@
+"""CPU oracle: a restatement of the reference's arithmetic for the projection / gated-delta-rule path.
+
+TEST INFRASTRUCTURE ONLY. Nothing in the product package imports this; it is used by `tests/`, by the smoke
+check and by the CPU-baseline leg of the benchmark as the checker / the timed CPU arm, never as a fallback.
+
+Pinning status
+  * gated delta rule: PINNED - reproduces the reference's self-contained known-answer tests
+    (src/archs/qwen35_text.rs:1391-1462: closed-form inputs, in-test scalar recurrence, tolerance 1e-4), and the
+    two independent forms here (token-sequential, 32-token chunked) agree with each other.
+  * GeGLU elementwise: PINNED against the 16-value test of src/archs/modernbert.rs:743-766 (expected values
+    from the exact-erf GELU definition the test itself uses).
+  * Linear / GEMM arithmetic: PARITY UNPINNED - the only reference tests that pin it are whole-model snapshots
+    that need Hugging Face checkpoints which are not available offline, and the arithmetic itself lives in
+    third-party crates (candle-core / candle-nn 0.11.0, gemm 0.19.0) whose source is not part of the reference
+    tree. It is restated from the public contract `Linear::forward(x) = x Wᵀ (+ b)` with f32 accumulation.
+"""
+from .projection import (geglu, linear, mlp_modernbert, mlp_qwen35, round_bf16, swiglu)  # noqa: F401
+from .delta_rule import (chunked_delta_rule, delta_inputs, finish_delta, sequential_delta_rule)  # noqa: F401

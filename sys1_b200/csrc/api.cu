@@ -36,15 +36,7 @@ extern "C" int s1_ctx_create(int device_ordinal, void* cuda_stream, s1_ctx** out
     if (!ctx) return S1_ENOMEM;
     ctx->device = device_ordinal;
     ctx->sm_count = prop.multiProcessorCount;
-    if (cuda_stream) {
-        ctx->stream = static_cast<cudaStream_t>(cuda_stream);
-    } else {
-        if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
-            delete ctx;
-            return S1_ECUDA;
-        }
-        ctx->own_stream = true;
-    }
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);  // NULL is CUDA's default stream
     if (cudaMalloc(&ctx->status_dev, 4 * sizeof(int)) != cudaSuccess ||
         cudaMemset(ctx->status_dev, 0, 4 * sizeof(int)) != cudaSuccess) {
         delete ctx;
@@ -68,7 +60,6 @@ extern "C" int s1_ctx_destroy(s1_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
-    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return S1_OK;
 }
@@ -83,6 +74,10 @@ extern "C" int s1_set_option(s1_ctx* ctx, const char* name, long long value) {
         if (value != 0 && value != 128 && value != 256)
             return s1_fail(ctx, S1_EINVAL, "gemm_bn must be 0, 128 or 256 (got %lld)", value);
         ctx->opt_gemm_bn = static_cast<int>(value);
+        return S1_OK;
+    }
+    if (strcmp(name, "debug") == 0) {
+        ctx->opt_debug = static_cast<int>(value);
         return S1_OK;
     }
     return s1_fail(ctx, S1_EINVAL, "unknown option '%s'", name);
@@ -103,8 +98,8 @@ extern "C" int s1_sync(s1_ctx* ctx) {
 }
 
 int s1_get_tmap(s1_ctx* ctx, const void* ptr, long long rows, long long cols, long long ld, int box_rows,
-                int box_cols, int elem_bytes, bool swizzle128, CUtensorMap* out) {
-    S1TmapKey key{ptr, rows, cols, ld, box_rows, swizzle128 ? box_cols : -box_cols, elem_bytes};
+                int box_cols, int elem_bytes, int swizzle_bytes, CUtensorMap* out) {
+    S1TmapKey key{ptr, rows, cols, ld, box_rows, box_cols + 1024 * swizzle_bytes, elem_bytes};
     auto it = ctx->tmaps.find(key);
     if (it != ctx->tmaps.end()) {
         *out = it->second;
@@ -117,7 +112,9 @@ int s1_get_tmap(s1_ctx* ctx, const void* ptr, long long rows, long long cols, lo
     cuuint32_t estr[2] = {1, 1};
     CUtensorMap m;
     CUresult r = ctx->encode(&m, dt, 2, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                             swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                             : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                   : CU_TENSOR_MAP_SWIZZLE_NONE,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return s1_fail(ctx, S1_ECUDA, "cuTensorMapEncodeTiled failed (%d) ptr=%p rows=%lld cols=%lld ld=%lld box=%dx%d",
@@ -131,7 +128,7 @@ int s1_get_tmap(s1_ctx* ctx, const void* ptr, long long rows, long long cols, lo
 // ---------------------------------------------------------------------------------------------- s1_linear
 template <int BN, int EPI>
 static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1,
-                       const GemmParams& p) {
+                       const CUtensorMap& ty, const GemmParams& p) {
     using Cfg = GemmCfg<BN>;
     auto kern = s1_gemm_kernel<BN, EPI>;
     static thread_local int configured_device = -1;
@@ -141,7 +138,7 @@ static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0,
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kern<<<grid, kGemmThreads, Cfg::kSmemBytes, ctx->stream>>>(a, b0, b1, p);
+    kern<<<grid, kGemmThreads, Cfg::kSmemBytes, ctx->stream>>>(a, b0, b1, ty, p);
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return S1_OK;
@@ -197,20 +194,21 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
     p.tiles_m = tiles_m;
     p.tiles_n = n_tiles_for(bn);
     p.act = lin->act;
-    p.ldy = ldy;
+    p.debug = ctx->opt_debug;
     p.ldr = ldr;
-    p.y = static_cast<__nv_bfloat16*>(y);
     p.residual = static_cast<const __nv_bfloat16*>(residual);
     p.bias = static_cast<const __nv_bfloat16*>(lin->bias);
     p.status = ctx->status_dev;
 
-    CUtensorMap ta, tb0, tb1;
-    int rc = s1_get_tmap(ctx, x, T, lin->K, ldx, kBM, kBK, 2, true, &ta);
+    CUtensorMap ta, tb0, tb1, ty;
+    int rc = s1_get_tmap(ctx, x, T, lin->K, ldx, kBM, kBK, 2, 128, &ta);
     if (rc) return rc;
-    rc = s1_get_tmap(ctx, lin->w, lin->N, lin->K, lin->ldw, bn / 2, kBK, 2, true, &tb0);
+    rc = s1_get_tmap(ctx, y, T, n_out, ldy, 32, 32, 2, 64, &ty);
+    if (rc) return rc;
+    rc = s1_get_tmap(ctx, lin->w, lin->N, lin->K, lin->ldw, bn / 2, kBK, 2, 128, &tb0);
     if (rc) return rc;
     if (epi == S1_EPI_SWIGLU) {
-        rc = s1_get_tmap(ctx, lin->w_up, lin->N, lin->K, lin->ldw_up, bn / 2, kBK, 2, true, &tb1);
+        rc = s1_get_tmap(ctx, lin->w_up, lin->N, lin->K, lin->ldw_up, bn / 2, kBK, 2, 128, &tb1);
         if (rc) return rc;
         p.n_tile_stride = bn / 2;
         p.half1_base = 0;
@@ -225,11 +223,11 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
     }
 
     if (bn == 256) {
-        if (epi == S1_EPI_NONE) return launch_gemm<256, EPI_NONE>(ctx, ta, tb0, tb1, p);
-        if (epi == S1_EPI_GEGLU) return launch_gemm<256, EPI_GEGLU>(ctx, ta, tb0, tb1, p);
-        return launch_gemm<256, EPI_SWIGLU>(ctx, ta, tb0, tb1, p);
+        if (epi == S1_EPI_NONE) return launch_gemm<256, EPI_NONE>(ctx, ta, tb0, tb1, ty, p);
+        if (epi == S1_EPI_GEGLU) return launch_gemm<256, EPI_GEGLU>(ctx, ta, tb0, tb1, ty, p);
+        return launch_gemm<256, EPI_SWIGLU>(ctx, ta, tb0, tb1, ty, p);
     }
-    if (epi == S1_EPI_NONE) return launch_gemm<128, EPI_NONE>(ctx, ta, tb0, tb1, p);
-    if (epi == S1_EPI_GEGLU) return launch_gemm<128, EPI_GEGLU>(ctx, ta, tb0, tb1, p);
-    return launch_gemm<128, EPI_SWIGLU>(ctx, ta, tb0, tb1, p);
+    if (epi == S1_EPI_NONE) return launch_gemm<128, EPI_NONE>(ctx, ta, tb0, tb1, ty, p);
+    if (epi == S1_EPI_GEGLU) return launch_gemm<128, EPI_GEGLU>(ctx, ta, tb0, tb1, ty, p);
+    return launch_gemm<128, EPI_SWIGLU>(ctx, ta, tb0, tb1, ty, p);
 }

@@ -38,10 +38,10 @@ struct s1_ctx {
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
-    bool own_stream = false;
     int* status_dev = nullptr;  // int[4], written by kernels on failure
     long long launches = 0;
     int opt_gemm_bn = 0;
+    int opt_debug = 0;
     PFN_cuTensorMapEncodeTiled encode = nullptr;
     std::unordered_map<S1TmapKey, CUtensorMap, S1TmapKeyHash> tmaps;
     char err[512] = {0};
@@ -65,6 +65,6 @@ inline int s1_fail(s1_ctx* ctx, int code, const char* fmt, ...) {
     } while (0)
 
 // Encodes (or fetches from the cache) a 2-D tiled tensor map over a row-major matrix whose rows are `ld`
-// elements apart: dim0 = cols (contiguous), dim1 = rows. swizzle128 selects CU_TENSOR_MAP_SWIZZLE_128B.
+// elements apart: dim0 = cols (contiguous), dim1 = rows. swizzle_bytes is 0, 64 or 128.
 int s1_get_tmap(s1_ctx* ctx, const void* ptr, long long rows, long long cols, long long ld, int box_rows,
-                int box_cols, int elem_bytes, bool swizzle128, CUtensorMap* out);
+                int box_cols, int elem_bytes, int swizzle_bytes, CUtensorMap* out);

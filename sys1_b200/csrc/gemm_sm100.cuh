@@ -13,7 +13,8 @@
 //                 128-byte swizzle, ring of STAGES buffers guarded by full/empty mbarriers
 //   warp 1      : TMEM allocation + single-thread tcgen05.mma issue (M=128, N=BN, K=16 per instruction),
 //                 two TMEM accumulators so the epilogue of tile i overlaps the MMAs of tile i+1
-//   warps 2..5  : epilogue - tcgen05.ld of the warp's TMEM lane quarter, rounding/gating, 16-byte stores
+//   warps 2..9  : epilogue - tcgen05.ld of the warp's TMEM lane quarter, rounding/gating in registers,
+//                 swizzled staging tile in shared memory, TMA store (full-line writes, clipped at the edges)
 #pragma once
 #include <cuda_bf16.h>
 
@@ -32,9 +33,8 @@ struct GemmParams {
     int n_tile_stride;  // W rows advanced per n-tile for the first B box
     int half1_base;     // W row offset of the second B box (relative to tile_n * n_tile_stride)
     int act;            // ACT_* applied after bias (plain epilogue only)
-    long long ldy;      // elements between output rows
+    int debug;          // measurement aid: bit0 = skip global stores, bit1 = skip TMEM reads and stores
     long long ldr;      // elements between residual rows
-    __nv_bfloat16* y;
     const __nv_bfloat16* residual;  // [M, n_out] or null
     const __nv_bfloat16* bias;      // [n_out] or null
     int* status;                    // device int[4]: {code, block, role, tile}; 0 = ok
@@ -42,7 +42,7 @@ struct GemmParams {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;  // 64 bf16 = 128 bytes = one swizzle row
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // TMA warp + MMA warp + 8 epilogue warps
 constexpr int kEpiWarp0 = 2;
 
 template <int BN>
@@ -52,7 +52,8 @@ struct GemmCfg {
     static constexpr int kBHalfBytes = (BN / 2) * kBK * 2;
     static constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;
     static constexpr int kTmemCols = 2 * BN;  // two accumulators; 256 or 512, both powers of two
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int kEpiStagingBytes = 8 * 4096;  // per epilogue warp: two 32x32 bf16 tiles
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiStagingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ float gelu_erf_ref(float v) { return v * normcdff(v); }
@@ -71,7 +72,8 @@ __device__ __forceinline__ void unpack_bf16x2(uint32_t v, float& lo, float& hi) 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
-               const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
+               const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmY,
+               const GemmParams p) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::kStages;
     constexpr bool PAIRED = (EPI != EPI_NONE);
@@ -80,7 +82,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * Cfg::kStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * Cfg::kStageBytes + Cfg::kEpiStagingBytes);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -102,13 +104,14 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8u * a, 1);
-            mbar_init(tempty0 + 8u * a, 4);
+            mbar_init(tempty0 + 8u * a, 8);
         }
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB0);
         tma_prefetch_desc(&tmB1);
+        tma_prefetch_desc(&tmY);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
@@ -186,8 +189,15 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         __syncwarp();
     } else {
         // ------------------------------------------------------------- epilogue warps
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
-        uint32_t it = 0;
+        // Warp (q, hh): TMEM lane quarter q = warp % 4 (rows q*32 .. q*32+31 of the tile, one row per lane),
+        // column half hh. Work unit = 32 output columns: tcgen05.ld -> rounding / gating in registers ->
+        // 16-byte swizzled st.shared into a 32x32 bf16 staging tile -> one TMA store (clips rows >= M and
+        // columns >= n_out by itself). Two staging tiles per warp so a store drains while the next is built.
+        const int q = warp & 3;
+        const int hh = (warp - kEpiWarp0) >> 2;
+        constexpr int CH = OUT_W / 64;  // 32-column work units per warp per tile
+        const uint32_t stage_buf = smem_base + STAGES * Cfg::kStageBytes + (warp - kEpiWarp0) * 4096;
+        uint32_t it = 0, nstore = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
             const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
@@ -199,28 +209,48 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 break;
             }
             tc_fence_after();
-            const int row = tm * kBM + q * 32 + lane;
+            const int row0 = tm * kBM + q * 32;
+            const int row = row0 + lane;
             const bool row_ok = row < p.M;
-            const int col0 = tn * OUT_W;
-            const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-            __nv_bfloat16* yrow = p.y + static_cast<long long>(row) * p.ldy;
+            const int col0 = tn * OUT_W + hh * (CH * 32);
+            const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + hh * (CH * 32);
             const __nv_bfloat16* rrow = p.residual ? p.residual + static_cast<long long>(row) * p.ldr : nullptr;
 
-#pragma unroll 1
-            for (int c = 0; c < OUT_W / 32; ++c) {
-                const int col = col0 + c * 32;
-                uint32_t out[16];
+            if (p.debug & 2) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+                continue;
+            }
+            uint32_t va[2][32];
+            uint32_t vg[PAIRED ? 2 : 1][PAIRED ? 32 : 1];
+            tmem_ld_32x32b_x32(taddr, va[0]);
+            if constexpr (PAIRED) tmem_ld_32x32b_x32(taddr + BN / 2, vg[0]);
+#pragma unroll
+            for (int ci = 0; ci < CH; ++ci) {
+                const int col = col0 + ci * 32;
+                uint4 rv[4] = {};
                 if constexpr (!PAIRED) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, v);
-                    uint4 rv[4] = {};
                     if (rrow && row_ok) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
                             if (col + j * 8 < p.n_out)
                                 rv[j] = __ldg(reinterpret_cast<const uint4*>(rrow + col + j * 8));
                     }
-                    tmem_ld_wait();
+                }
+                tmem_ld_wait();
+                if (ci + 1 < CH) {
+                    tmem_ld_32x32b_x32(taddr + (ci + 1) * 32, va[(ci + 1) & 1]);
+                    if constexpr (PAIRED) tmem_ld_32x32b_x32(taddr + BN / 2 + (ci + 1) * 32, vg[(ci + 1) & 1]);
+                } else {
+                    // every TMEM read of this accumulator has landed in registers: hand it back to the MMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+                }
+                uint32_t out[16];
+                if constexpr (!PAIRED) {
+                    const uint32_t* v = va[ci & 1];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         float a = bf16_round(__uint_as_float(v[2 * j]));
@@ -240,49 +270,53 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             b = bf16_round(gelu_erf_ref(b));
                         }
                         if (rrow) {
-                            const uint32_t rw = reinterpret_cast<const uint32_t*>(rv)[j];
                             float r0, r1;
-                            unpack_bf16x2(rw, r0, r1);
+                            unpack_bf16x2(reinterpret_cast<const uint32_t*>(rv)[j], r0, r1);
                             a += r0;
                             b += r1;
                         }
                         out[j] = pack_bf16x2(a, b);
                     }
                 } else {
-                    uint32_t va[32], vg[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, va);
-                    tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, vg);
-                    tmem_ld_wait();
+                    const uint32_t* v = va[ci & 1];
+                    const uint32_t* w = vg[ci & 1];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         float o[2];
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
-                            const float a = bf16_round(__uint_as_float(va[2 * j + e]));
-                            const float g = bf16_round(__uint_as_float(vg[2 * j + e]));
+                            const float a = bf16_round(__uint_as_float(v[2 * j + e]));
+                            const float g = bf16_round(__uint_as_float(w[2 * j + e]));
                             const float act = bf16_round(EPI == EPI_GEGLU ? gelu_erf_ref(a) : silu_ref(a));
                             o[e] = act * g;
                         }
                         out[j] = pack_bf16x2(o[0], o[1]);
                     }
                 }
-                if (c == OUT_W / 32 - 1) {
-                    // every TMEM read of this accumulator has landed in registers: hand it back
-                    tc_fence_before();
+                if (row0 < p.M && col < p.n_out && !(p.debug & 1)) {
+                    const uint32_t buf = stage_buf + (nstore & 1u) * 2048u;
+                    ++nstore;
+                    // the staging tile written two stores ago must have been read out by its TMA store
+                    if (lane == 0) tma_store_wait_read<1>();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
-                }
-                if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        if (col + j * 8 < p.n_out) {
-                            *reinterpret_cast<uint4*>(yrow + col + j * 8) =
-                                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
-                        }
+                        // 64-byte rows, 64B swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
+                        const uint32_t addr = buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out[4 * j]),
+                                     "r"(out[4 * j + 1]), "r"(out[4 * j + 2]), "r"(out[4 * j + 3])
+                                     : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmY, buf, col, row0);
+                        tma_store_commit();
                     }
                 }
             }
         }
+        if (lane == 0) tma_store_wait<0>();  // smem read and global writes of this warp's stores are complete
         __syncwarp();
     }
 
