@@ -71,8 +71,8 @@ extern "C" long long s1_launch_count(const s1_ctx* ctx) { return ctx ? ctx->laun
 extern "C" int s1_set_option(s1_ctx* ctx, const char* name, long long value) {
     if (!ctx || !name) return S1_EINVAL;
     if (strcmp(name, "gemm_bn") == 0) {
-        if (value != 0 && value != 128 && value != 256)
-            return s1_fail(ctx, S1_EINVAL, "gemm_bn must be 0, 128 or 256 (got %lld)", value);
+        if (value != 0 && value != 128 && value != 256 && value != 512)
+            return s1_fail(ctx, S1_EINVAL, "gemm_bn must be 0, 128, 256 or 512 (got %lld)", value);
         ctx->opt_gemm_bn = static_cast<int>(value);
         return S1_OK;
     }
@@ -126,20 +126,32 @@ int s1_get_tmap(s1_ctx* ctx, const void* ptr, long long rows, long long cols, lo
 }
 
 // ---------------------------------------------------------------------------------------------- s1_linear
-template <int BN, int EPI>
+template <int BN, int EPI, int MODE, int CTAS>
 static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1,
                        const CUtensorMap& ty, const GemmParams& p) {
-    using Cfg = GemmCfg<BN>;
-    auto kern = s1_gemm_kernel<BN, EPI>;
+    using Cfg = GemmCfg<BN, CTAS>;
+    auto kern = s1_gemm_kernel<BN, EPI, MODE, CTAS>;
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
         S1_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         configured_device = ctx->device;
     }
     const int tiles = p.tiles_m * p.tiles_n;
-    const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kern<<<grid, kGemmThreads, Cfg::kSmemBytes, ctx->stream>>>(a, b0, b1, ty, p);
-    S1_CUDA_OK(ctx, cudaGetLastError());
+    const int units = ctx->sm_count / CTAS;  // CTAs, or CTA pairs
+    const int grid = (tiles < units ? tiles : units) * CTAS;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    S1_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, kern, a, b0, b1, ty, p));
     ctx->launches += 1;
     return S1_OK;
 }
@@ -173,19 +185,33 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
         return s1_fail(ctx, S1_EINVAL, "s1_linear: pointers must be 16-byte aligned");
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
 
-    // Tile width: 256 accumulator columns unless 128 fills the 148 SMs' waves visibly better.
-    const int tiles_m = (T + kBM - 1) / kBM;
-    auto n_tiles_for = [&](int bn) {
-        const int w = (epi == S1_EPI_NONE) ? bn : bn / 2;
+    // Tile shape. A CTA pair (256 x 256 per pair) once there is at least a wave of pair-tiles; otherwise one CTA
+    // per tile, 128 x 256, or 128 x 128 when that fills the SMs visibly better.
+    // "gemm_bn": 0 = auto, 512 = force the pair kernel, 256 / 128 = force the single-CTA kernel of that width.
+    const int out_w256 = (epi == S1_EPI_NONE) ? 256 : 128;
+    const int n_tiles256 = (n_out + out_w256 - 1) / out_w256;
+    auto wave_eff = [&](long long t, int units) {
+        const long long waves = (t + units - 1) / units;
+        return static_cast<double>(t) / static_cast<double>(waves * units);
+    };
+    int ctas = 1, bn = 256;
+    const long long pair_tiles = static_cast<long long>((T + 2 * kBM - 1) / (2 * kBM)) * n_tiles256;
+    const int tiles_m1 = (T + kBM - 1) / kBM;
+    if (ctx->opt_gemm_bn == 512 || (ctx->opt_gemm_bn == 0 && pair_tiles >= ctx->sm_count / 2)) {
+        ctas = 2;
+    } else if (ctx->opt_gemm_bn == 128 || ctx->opt_gemm_bn == 256) {
+        bn = ctx->opt_gemm_bn;
+    } else {
+        const int out_w128 = out_w256 / 2;
+        const long long t256 = static_cast<long long>(tiles_m1) * n_tiles256;
+        const long long t128 = static_cast<long long>(tiles_m1) * ((n_out + out_w128 - 1) / out_w128);
+        bn = (wave_eff(t128, ctx->sm_count) > wave_eff(t256, ctx->sm_count) + 0.08) ? 128 : 256;
+    }
+    const int tiles_m = (ctas == 2) ? (T + 2 * kBM - 1) / (2 * kBM) : tiles_m1;
+    auto n_tiles_for = [&](int bn_) {
+        const int w = (epi == S1_EPI_NONE) ? bn_ : bn_ / 2;
         return (n_out + w - 1) / w;
     };
-    auto wave_eff = [&](int bn) {
-        const long long t = static_cast<long long>(tiles_m) * n_tiles_for(bn);
-        const long long waves = (t + ctx->sm_count - 1) / ctx->sm_count;
-        return static_cast<double>(t) / static_cast<double>(waves * ctx->sm_count);
-    };
-    int bn = ctx->opt_gemm_bn;
-    if (bn == 0) bn = (wave_eff(128) > wave_eff(256) + 0.08) ? 128 : 256;
 
     GemmParams p;
     p.M = T;
@@ -222,12 +248,20 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
         p.half1_base = bn / 2;
     }
 
-    if (bn == 256) {
-        if (epi == S1_EPI_NONE) return launch_gemm<256, EPI_NONE>(ctx, ta, tb0, tb1, ty, p);
-        if (epi == S1_EPI_GEGLU) return launch_gemm<256, EPI_GEGLU>(ctx, ta, tb0, tb1, ty, p);
-        return launch_gemm<256, EPI_SWIGLU>(ctx, ta, tb0, tb1, ty, p);
-    }
-    if (epi == S1_EPI_NONE) return launch_gemm<128, EPI_NONE>(ctx, ta, tb0, tb1, ty, p);
-    if (epi == S1_EPI_GEGLU) return launch_gemm<128, EPI_GEGLU>(ctx, ta, tb0, tb1, ty, p);
-    return launch_gemm<128, EPI_SWIGLU>(ctx, ta, tb0, tb1, ty, p);
+    const int mode = (residual ? 1 : 0) | ((lin->bias || lin->act != S1_ACT_NONE) ? 2 : 0);
+#define S1_LAUNCH(BN_, CTAS_)                                                                            \
+    do {                                                                                                 \
+        if (epi == S1_EPI_GEGLU) return launch_gemm<BN_, EPI_GEGLU, 0, CTAS_>(ctx, ta, tb0, tb1, ty, p);   \
+        if (epi == S1_EPI_SWIGLU) return launch_gemm<BN_, EPI_SWIGLU, 0, CTAS_>(ctx, ta, tb0, tb1, ty, p); \
+        switch (mode) {                                                                                  \
+            case 0: return launch_gemm<BN_, EPI_NONE, 0, CTAS_>(ctx, ta, tb0, tb1, ty, p);                \
+            case 1: return launch_gemm<BN_, EPI_NONE, 1, CTAS_>(ctx, ta, tb0, tb1, ty, p);                \
+            case 2: return launch_gemm<BN_, EPI_NONE, 2, CTAS_>(ctx, ta, tb0, tb1, ty, p);                \
+            default: return launch_gemm<BN_, EPI_NONE, 3, CTAS_>(ctx, ta, tb0, tb1, ty, p);               \
+        }                                                                                                \
+    } while (0)
+    if (ctas == 2) S1_LAUNCH(256, 2);
+    if (bn == 256) S1_LAUNCH(256, 1);
+    S1_LAUNCH(128, 1);
+#undef S1_LAUNCH
 }

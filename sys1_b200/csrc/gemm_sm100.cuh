@@ -8,13 +8,23 @@
 // (src/kernels/modernbert.cu:4-14) and the residual adds (src/archs/modernbert.rs:882-886,
 // src/archs/qwen35_text.rs:938-939).
 //
-// Roles inside one CTA (one CTA per SM, static round-robin tile schedule):
-//   warp 0      : TMA producer  - X box {64 x 128 rows} and two W boxes {64 x BN/2 rows} per k-block,
-//                 128-byte swizzle, ring of STAGES buffers guarded by full/empty mbarriers
-//   warp 1      : TMEM allocation + single-thread tcgen05.mma issue (M=128, N=BN, K=16 per instruction),
-//                 two TMEM accumulators so the epilogue of tile i overlaps the MMAs of tile i+1
+// Two shapes of the same kernel (template parameter CTAS):
+//   CTAS = 1  one CTA per SM computes a 128 x BN tile (tcgen05.mma cta_group::1, M = 128).
+//   CTAS = 2  a cluster of two CTAs (two SMs) computes a 256 x 256 tile with cta_group::2 MMAs (M = 256):
+//             each CTA stages its own 128 rows of X and its own 128-row half of the W tile, so the
+//             L2 -> shared-memory traffic per SM drops by a third; the leader CTA issues the MMAs and each CTA
+//             ends up with the accumulator of its own 128 rows in its own TMEM. No TMA multicast is used:
+//             every CTA issues its own loads; only tcgen05.commit is multicast to the two CTAs' barriers.
+//
+// Roles inside a CTA (320 threads, static round-robin tile schedule, tile index n-fastest so the CTAs that
+// run together share X rows and the whole (small) W through L2):
+//   warp 0      : TMA producer  - 128-byte-swizzled boxes {64 x 128 rows} of X and {64 x BN/2 rows} of W into a
+//                 ring of STAGES buffers guarded by full/empty mbarriers
+//   warp 1      : TMEM allocation + single-thread tcgen05.mma issue (K = 16 per instruction), two TMEM
+//                 accumulators so the epilogue of tile i overlaps the MMAs of tile i+1
 //   warps 2..9  : epilogue - tcgen05.ld of the warp's TMEM lane quarter, rounding/gating in registers,
 //                 swizzled staging tile in shared memory, TMA store (full-line writes, clipped at the edges)
+// Every wait is bounded (see mbar_wait); a wait that runs out raises a status word the host reads.
 #pragma once
 #include <cuda_bf16.h>
 
@@ -33,30 +43,34 @@ struct GemmParams {
     int n_tile_stride;  // W rows advanced per n-tile for the first B box
     int half1_base;     // W row offset of the second B box (relative to tile_n * n_tile_stride)
     int act;            // ACT_* applied after bias (plain epilogue only)
-    int debug;          // measurement aid: bit0 = skip global stores, bit1 = skip TMEM reads and stores
+    int debug;          // measurement aid: bit0 = skip output stores, bit1 = skip the whole epilogue
     long long ldr;      // elements between residual rows
     const __nv_bfloat16* residual;  // [M, n_out] or null
     const __nv_bfloat16* bias;      // [n_out] or null
     int* status;                    // device int[4]: {code, block, role, tile}; 0 = ok
 };
 
-constexpr int kBM = 128;
-constexpr int kBK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kBM = 128;  // rows per CTA
+constexpr int kBK = 64;   // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kGemmThreads = 320;  // TMA warp + MMA warp + 8 epilogue warps
 constexpr int kEpiWarp0 = 2;
 
-template <int BN>
+template <int BN, int CTAS>
 struct GemmCfg {
-    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "the CTA-pair kernel is 256 x 256 only");
     static constexpr int kABytes = kBM * kBK * 2;
     static constexpr int kBHalfBytes = (BN / 2) * kBK * 2;
-    static constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;
-    static constexpr int kTmemCols = 2 * BN;  // two accumulators; 256 or 512, both powers of two
-    static constexpr int kEpiStagingBytes = 8 * 4096;  // per epilogue warp: two 32x32 bf16 tiles
+    // one CTA stages both halves of the W tile; in a pair each CTA stages one
+    static constexpr int kStageBytes = kABytes + (CTAS == 1 ? 2 : 1) * kBHalfBytes;
+    static constexpr int kStages = (192 * 1024) / kStageBytes;  // 4 (48 KB stages) or 6 (32 KB stages)
+    static constexpr int kTmemCols = 2 * BN;            // two accumulators; 256 or 512, powers of two
+    static constexpr int kEpiStagingBytes = 8 * 4096;   // per epilogue warp: two 32x32 bf16 tiles
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiStagingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ float gelu_erf_ref(float v) { return v * normcdff(v); }
+// Exact-erf GELU x * Phi(x) (src/kernels/modernbert.cu:11-12 writes it as value * normcdff(value)); erff is the
+// cheaper of the two library routes and agrees with it to within an f32 ulp of Phi before the bf16 rounding.
+__device__ __forceinline__ float gelu_erf_ref(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
 __device__ __forceinline__ float silu_ref(float v) { return v / (1.f + __expf(-v)); }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -69,15 +83,138 @@ __device__ __forceinline__ void unpack_bf16x2(uint32_t v, float& lo, float& hi) 
     hi = __high2float(t);
 }
 
-template <int BN, int EPI>
+// One epilogue warp, one tile: reads its 32 rows x (CH*32) accumulator columns out of TMEM, applies the epilogue
+// and stores. `tempty_bar` is the (cluster-space) address of the barrier that hands the accumulator back.
+// MODE (plain epilogue only): bit0 = residual add, bit1 = bias and/or activation present (general path).
+template <int BN, int EPI, int MODE>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap* tmY, uint32_t taddr, int row0,
+                                              int col0, uint32_t stage_buf, uint32_t& nstore, uint32_t tempty_bar,
+                                              int lane) {
+    constexpr bool PAIRED = (EPI != EPI_NONE);
+    constexpr int OUT_W = PAIRED ? BN / 2 : BN;
+    constexpr int CH = OUT_W / 64;  // 32-column work units per warp per tile
+    const int row = row0 + lane;
+    const bool row_ok = row < p.M;
+    const __nv_bfloat16* rrow = (MODE & 1) ? p.residual + static_cast<long long>(row) * p.ldr : nullptr;
+
+    uint32_t va[2][32];
+    uint32_t vg[PAIRED ? 2 : 1][PAIRED ? 32 : 1];
+    tmem_ld_32x32b_x32(taddr, va[0]);
+    if constexpr (PAIRED) tmem_ld_32x32b_x32(taddr + BN / 2, vg[0]);
+#pragma unroll
+    for (int ci = 0; ci < CH; ++ci) {
+        const int col = col0 + ci * 32;
+        uint4 rv[4] = {};
+        if constexpr (!PAIRED && (MODE & 1)) {
+            if (row_ok) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (col + j * 8 < p.n_out) rv[j] = __ldg(reinterpret_cast<const uint4*>(rrow + col + j * 8));
+            }
+        }
+        tmem_ld_wait();
+        if (ci + 1 < CH) {
+            tmem_ld_32x32b_x32(taddr + (ci + 1) * 32, va[(ci + 1) & 1]);
+            if constexpr (PAIRED) tmem_ld_32x32b_x32(taddr + BN / 2 + (ci + 1) * 32, vg[(ci + 1) & 1]);
+        } else {
+            // every TMEM read of this accumulator has landed in registers: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_bar);
+        }
+        uint32_t out[16];
+        if constexpr (!PAIRED) {
+            const uint32_t* v = va[ci & 1];
+            if constexpr ((MODE & 2) == 0) {
+                // y = bf16(acc) [+ residual, added in bf16 with one rounding like the reference's bf16 add]
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                    if constexpr (MODE & 1) {
+                        const uint32_t rw = reinterpret_cast<const uint32_t*>(rv)[j];
+                        t = __hadd2(t, *reinterpret_cast<const __nv_bfloat162*>(&rw));
+                    }
+                    out[j] = *reinterpret_cast<uint32_t*>(&t);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float a = bf16_round(__uint_as_float(v[2 * j]));
+                    float b = bf16_round(__uint_as_float(v[2 * j + 1]));
+                    if (p.bias) {
+                        const int cc = col + 2 * j;
+                        if (cc < p.n_out) {
+                            a = bf16_round(a + __bfloat162float(p.bias[cc]));
+                            b = bf16_round(b + __bfloat162float(p.bias[cc + 1]));
+                        }
+                    }
+                    if (p.act == ACT_RELU) {
+                        a = fmaxf(a, 0.f);
+                        b = fmaxf(b, 0.f);
+                    } else if (p.act == ACT_GELU) {
+                        a = bf16_round(gelu_erf_ref(a));
+                        b = bf16_round(gelu_erf_ref(b));
+                    }
+                    if constexpr (MODE & 1) {
+                        float r0, r1;
+                        unpack_bf16x2(reinterpret_cast<const uint32_t*>(rv)[j], r0, r1);
+                        a += r0;
+                        b += r1;
+                    }
+                    out[j] = pack_bf16x2(a, b);
+                }
+            }
+        } else {
+            const uint32_t* v = va[ci & 1];
+            const uint32_t* w = vg[ci & 1];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                // round both projections to bf16 (the reference materialises them), activate in f32, round,
+                // multiply in bf16 (one rounding)
+                __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                __nv_bfloat162 g2 = __floats2bfloat162_rn(__uint_as_float(w[2 * j]), __uint_as_float(w[2 * j + 1]));
+                const float a0 = __low2float(a2), a1 = __high2float(a2);
+                __nv_bfloat162 act2;
+                if constexpr (EPI == EPI_GEGLU) act2 = __floats2bfloat162_rn(gelu_erf_ref(a0), gelu_erf_ref(a1));
+                else act2 = __floats2bfloat162_rn(silu_ref(a0), silu_ref(a1));
+                __nv_bfloat162 o2 = __hmul2(act2, g2);
+                out[j] = *reinterpret_cast<uint32_t*>(&o2);
+            }
+        }
+        if (row0 < p.M && col < p.n_out && !(p.debug & 1)) {
+            const uint32_t buf = stage_buf + (nstore & 1u) * 2048u;
+            ++nstore;
+            // the staging tile written two stores ago must have been read out by its TMA store
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // 64-byte rows, 64B swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
+                const uint32_t addr = buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out[4 * j]),
+                             "r"(out[4 * j + 1]), "r"(out[4 * j + 2]), "r"(out[4 * j + 3])
+                             : "memory");
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(tmY, buf, col, row0);
+                tma_store_commit();
+            }
+        }
+    }
+}
+
+template <int BN, int EPI, int MODE, int CTAS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmY,
                const GemmParams p) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, CTAS>;
     constexpr int STAGES = Cfg::kStages;
     constexpr bool PAIRED = (EPI != EPI_NONE);
     constexpr int OUT_W = PAIRED ? BN / 2 : BN;  // output columns per tile
+    constexpr int CH = OUT_W / 64;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -94,8 +231,14 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;  // 0 = leader (issues the MMAs)
+    const int unit = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;   // scheduling unit: CTA or CTA pair
+    const int num_units = (CTAS == 2) ? (gridDim.x >> 1) : gridDim.x;
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int num_kb = (p.K + kBK - 1) / kBK;
+    // barriers of the leader CTA as seen from this CTA (cluster address space)
+    const uint32_t lead_full0 = (CTAS == 2) ? map_to_cta(full0, 0) : full0;
+    const uint32_t lead_tempty0 = (CTAS == 2) ? map_to_cta(tempty0, 0) : tempty0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -104,7 +247,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8u * a, 1);
-            mbar_init(tempty0 + 8u * a, 8);
+            mbar_init(tempty0 + 8u * a, 8 * CTAS);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -114,23 +257,29 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tma_prefetch_desc(&tmY);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
-        tmem_relinquish();
+        if constexpr (CTAS == 2) {
+            tmem_alloc_2cta(smem_u32(tmem_slot), Cfg::kTmemCols);
+            tmem_relinquish_2cta();
+        } else {
+            tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers exist before anything remote touches them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     int fail_role = 0, fail_tile = -1;
 
     if (warp == 0) {
-        // ------------------------------------------------------------- TMA producer
+        // ------------------------------------------------------------- TMA producer (both CTAs of a pair)
         if (lane == 0) {
             uint32_t cnt = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && !fail_role; tile += gridDim.x) {
+            for (int tile = unit; tile < num_tiles && !fail_role; tile += num_units) {
                 const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
-                const int m0 = tm * kBM;
+                const int m0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM;
                 const int r0 = tn * p.n_tile_stride;
                 const int r1 = r0 + p.half1_base;
                 for (int kb = 0; kb < num_kb; ++kb, ++cnt) {
@@ -141,21 +290,30 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         break;
                     }
                     const uint32_t sa = smem_base + s * Cfg::kStageBytes;
-                    const uint32_t fb = full0 + 8u * s;
-                    mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
-                    tma_load_2d(sa, &tmA, kb * kBK, m0, fb);
-                    tma_load_2d(sa + Cfg::kABytes, &tmB0, kb * kBK, r0, fb);
-                    tma_load_2d(sa + Cfg::kABytes + Cfg::kBHalfBytes, &tmB1, kb * kBK, r1, fb);
+                    if constexpr (CTAS == 1) {
+                        const uint32_t fb = full0 + 8u * s;
+                        mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
+                        tma_load_2d(sa, &tmA, kb * kBK, m0, fb);
+                        tma_load_2d(sa + Cfg::kABytes, &tmB0, kb * kBK, r0, fb);
+                        tma_load_2d(sa + Cfg::kABytes + Cfg::kBHalfBytes, &tmB1, kb * kBK, r1, fb);
+                    } else {
+                        // both CTAs' bytes are counted on the leader's barrier; only the leader arrives on it
+                        const uint32_t fb = lead_full0 + 8u * s;
+                        if (cta_rank == 0) mbar_arrive_expect_tx(full0 + 8u * s, 2 * Cfg::kStageBytes);
+                        tma_load_2d_pair(sa, &tmA, kb * kBK, m0, fb);
+                        if (cta_rank == 0) tma_load_2d_pair(sa + Cfg::kABytes, &tmB0, kb * kBK, r0, fb);
+                        else tma_load_2d_pair(sa + Cfg::kABytes, &tmB1, kb * kBK, r1, fb);
+                    }
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(1, kBM, BN);
+        // ------------------------------------------------------------- MMA issuer (leader CTA only)
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = make_idesc(1, kBM * CTAS, BN);
             uint32_t cnt = 0, it = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && !fail_role; tile += gridDim.x, ++it) {
+            for (int tile = unit; tile < num_tiles && !fail_role; tile += num_units, ++it) {
                 const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
                 if (!mbar_wait(tempty0 + 8u * acc, aph ^ 1u, abort_flag)) {
                     fail_role = 2;
@@ -178,27 +336,29 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k) {
                         // +32 bytes along K per instruction = +2 in the (addr >> 4) field
-                        umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) ? 1u : 0u);
+                        if constexpr (CTAS == 2) umma_bf16_2cta(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) ? 1u : 0u);
+                        else umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) ? 1u : 0u);
                     }
-                    umma_commit(empty0 + 8u * s);  // smem stage reusable once these MMAs retire
+                    // shared-memory stage reusable (in both CTAs of a pair) once these MMAs retire
+                    if constexpr (CTAS == 2) umma_commit_2cta(empty0 + 8u * s);
+                    else umma_commit(empty0 + 8u * s);
                 }
                 if (fail_role) break;
-                umma_commit(tfull0 + 8u * acc);  // accumulator complete
+                // accumulator complete (each CTA of a pair is told on its own barrier)
+                if constexpr (CTAS == 2) umma_commit_2cta(tfull0 + 8u * acc);
+                else umma_commit(tfull0 + 8u * acc);
             }
         }
         __syncwarp();
     } else {
         // ------------------------------------------------------------- epilogue warps
-        // Warp (q, hh): TMEM lane quarter q = warp % 4 (rows q*32 .. q*32+31 of the tile, one row per lane),
-        // column half hh. Work unit = 32 output columns: tcgen05.ld -> rounding / gating in registers ->
-        // 16-byte swizzled st.shared into a 32x32 bf16 staging tile -> one TMA store (clips rows >= M and
-        // columns >= n_out by itself). Two staging tiles per warp so a store drains while the next is built.
+        // Warp (q, hh): TMEM lane quarter q = warp % 4 (rows q*32 .. q*32+31 of this CTA's 128, one row per lane),
+        // column half hh.
         const int q = warp & 3;
         const int hh = (warp - kEpiWarp0) >> 2;
-        constexpr int CH = OUT_W / 64;  // 32-column work units per warp per tile
         const uint32_t stage_buf = smem_base + STAGES * Cfg::kStageBytes + (warp - kEpiWarp0) * 4096;
         uint32_t it = 0, nstore = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+        for (int tile = unit; tile < num_tiles; tile += num_units, ++it) {
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
             const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
             // the whole warp must agree before any .sync.aligned tcgen05 instruction
@@ -209,119 +369,24 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 break;
             }
             tc_fence_after();
-            const int row0 = tm * kBM + q * 32;
-            const int row = row0 + lane;
-            const bool row_ok = row < p.M;
-            const int col0 = tn * OUT_W + hh * (CH * 32);
-            const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + hh * (CH * 32);
-            const __nv_bfloat16* rrow = p.residual ? p.residual + static_cast<long long>(row) * p.ldr : nullptr;
-
+            const uint32_t tempty_bar = lead_tempty0 + 8u * acc;
             if (p.debug & 2) {
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+                if (lane == 0) mbar_arrive_cluster(tempty_bar);
                 continue;
             }
-            uint32_t va[2][32];
-            uint32_t vg[PAIRED ? 2 : 1][PAIRED ? 32 : 1];
-            tmem_ld_32x32b_x32(taddr, va[0]);
-            if constexpr (PAIRED) tmem_ld_32x32b_x32(taddr + BN / 2, vg[0]);
-#pragma unroll
-            for (int ci = 0; ci < CH; ++ci) {
-                const int col = col0 + ci * 32;
-                uint4 rv[4] = {};
-                if constexpr (!PAIRED) {
-                    if (rrow && row_ok) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (col + j * 8 < p.n_out)
-                                rv[j] = __ldg(reinterpret_cast<const uint4*>(rrow + col + j * 8));
-                    }
-                }
-                tmem_ld_wait();
-                if (ci + 1 < CH) {
-                    tmem_ld_32x32b_x32(taddr + (ci + 1) * 32, va[(ci + 1) & 1]);
-                    if constexpr (PAIRED) tmem_ld_32x32b_x32(taddr + BN / 2 + (ci + 1) * 32, vg[(ci + 1) & 1]);
-                } else {
-                    // every TMEM read of this accumulator has landed in registers: hand it back to the MMA warp
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
-                }
-                uint32_t out[16];
-                if constexpr (!PAIRED) {
-                    const uint32_t* v = va[ci & 1];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float a = bf16_round(__uint_as_float(v[2 * j]));
-                        float b = bf16_round(__uint_as_float(v[2 * j + 1]));
-                        if (p.bias) {
-                            const int cc = col + 2 * j;
-                            if (cc < p.n_out) {
-                                a = bf16_round(a + __bfloat162float(p.bias[cc]));
-                                b = bf16_round(b + __bfloat162float(p.bias[cc + 1]));
-                            }
-                        }
-                        if (p.act == ACT_RELU) {
-                            a = fmaxf(a, 0.f);
-                            b = fmaxf(b, 0.f);
-                        } else if (p.act == ACT_GELU) {
-                            a = bf16_round(gelu_erf_ref(a));
-                            b = bf16_round(gelu_erf_ref(b));
-                        }
-                        if (rrow) {
-                            float r0, r1;
-                            unpack_bf16x2(reinterpret_cast<const uint32_t*>(rv)[j], r0, r1);
-                            a += r0;
-                            b += r1;
-                        }
-                        out[j] = pack_bf16x2(a, b);
-                    }
-                } else {
-                    const uint32_t* v = va[ci & 1];
-                    const uint32_t* w = vg[ci & 1];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float o[2];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const float a = bf16_round(__uint_as_float(v[2 * j + e]));
-                            const float g = bf16_round(__uint_as_float(w[2 * j + e]));
-                            const float act = bf16_round(EPI == EPI_GEGLU ? gelu_erf_ref(a) : silu_ref(a));
-                            o[e] = act * g;
-                        }
-                        out[j] = pack_bf16x2(o[0], o[1]);
-                    }
-                }
-                if (row0 < p.M && col < p.n_out && !(p.debug & 1)) {
-                    const uint32_t buf = stage_buf + (nstore & 1u) * 2048u;
-                    ++nstore;
-                    // the staging tile written two stores ago must have been read out by its TMA store
-                    if (lane == 0) tma_store_wait_read<1>();
-                    __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        // 64-byte rows, 64B swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
-                        const uint32_t addr = buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out[4 * j]),
-                                     "r"(out[4 * j + 1]), "r"(out[4 * j + 2]), "r"(out[4 * j + 3])
-                                     : "memory");
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&tmY, buf, col, row0);
-                        tma_store_commit();
-                    }
-                }
-            }
+            const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + q * 32;
+            const int col0 = tn * OUT_W + hh * (CH * 32);
+            const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + hh * (CH * 32);
+            epilogue_tile<BN, EPI, MODE>(p, &tmY, taddr, row0, col0, stage_buf, nstore, tempty_bar, lane);
         }
-        if (lane == 0) tma_store_wait<0>();  // smem read and global writes of this warp's stores are complete
+        if (lane == 0) tma_store_wait<0>();  // smem reads and global writes of this warp's stores are complete
         __syncwarp();
     }
 
     if (fail_role) {
-        // first failing thread of the grid records where it gave up; host turns it into an error
+        // first failing thread of the grid records where it gave up; the host turns it into an error
         if (atomicCAS(p.status, 0, 1) == 0) {
             p.status[1] = blockIdx.x;
             p.status[2] = fail_role;
@@ -334,9 +399,12 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     tc_fence_before();
     __syncthreads();
+    // a pair leaves together: the leader's MMAs read the peer's shared memory, the peer arrives on the leader's barriers
+    if constexpr (CTAS == 2) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+        if constexpr (CTAS == 2) tmem_dealloc_2cta(tmem_base, Cfg::kTmemCols);
+        else tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
 }
 
