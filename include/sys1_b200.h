@@ -95,6 +95,34 @@ typedef struct s1_linear_desc {
 int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, const void* residual,
               long long ldr, void* y, long long ldy, int T);
 
+/*
+ * Gated delta rule over a token-packed batch; exact drop-in for `chunked_delta_rule(q, k, v, g, beta)`
+ * (src/archs/qwen35_text.rs:789-807; CUDA kernel src/kernels/qwen35.cu:53-97), all f32:
+ *     S *= exp(g_t);  r = S^T k_t;  delta = (v_t - r) * beta_t;  S += k_t delta^T;  o_t = S^T q_t,   S0 = 0
+ * per (sequence, head). q, k: [total_tokens, heads, key_dim] already L2-normalised / scaled as
+ * `delta_inputs` leaves them (src/archs/qwen35_text.rs:528-579); v, out: [total_tokens, heads, value_dim];
+ * g, beta: [total_tokens, heads]; cu_seqlens: DEVICE int32 [num_seqs + 1], the state restarts at every boundary.
+ * (The reference takes [batch, heads, length, dim]; a padded batch is the packed layout with equal lengths after
+ * swapping the head and token axes.) key_dim must be 128 (as in the reference's CUDA path, :747), value_dim a
+ * multiple of 4.
+ */
+int s1_delta_rule(s1_ctx* ctx, const float* q, const float* k, const float* v, const float* g, const float* beta,
+                  const int32_t* cu_seqlens, int num_seqs, int total_tokens, int heads, int key_dim, int value_dim,
+                  float* out);
+
+/*
+ * Packs the next sequences of a queue into one token-packed batch (host arrays, no GPU work).
+ * Takes sequences in order while the running token count stays within `token_budget`; a sequence longer than
+ * the budget forms a batch of its own. Writes cu_seqlens[0..num_taken] (cu_seqlens[0] = 0, last = total) and,
+ * if `positions_host` is not NULL, positions[t] = index of token t within its own sequence.
+ * `padded_tokens` = total rounded up to `pad_multiple` (rows total..padded are padding the caller zero-fills).
+ * Stands where the reference pads to [batch, max_len] (src/models/laya.rs:396-431) after its request batcher
+ * (src/batching.rs:83-102); cu_seqlens has the layout of src/archs/modernbert.rs:431-443.
+ */
+int s1_pack_batch(const int32_t* lengths_host, int num_sequences, int token_budget, int pad_multiple,
+                  int32_t* cu_seqlens_host, int32_t* positions_host, int* num_taken, int* total_tokens,
+                  int* padded_tokens);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,6 +46,9 @@ SIGNATURES = {
     "s1_sync": (C.c_int, [C.c_void_p]),
     "s1_launch_count": (C.c_longlong, [C.c_void_p]),
     "s1_set_option": (C.c_int, [C.c_void_p, C.c_char_p, C.c_longlong]),
+    "s1_pack_batch": (C.c_int, [C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int32),
+                                C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "s1_delta_rule": (C.c_int, [C.c_void_p] * 7 + [C.c_int] * 5 + [C.c_void_p]),
     "s1_linear": (C.c_int, [C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                             C.c_void_p, C.c_longlong, C.c_int]),
 }

@@ -1,0 +1,68 @@
+"""Projection side and linear-attention recurrence of the Qwen3.5 layer (`src/archs/qwen35_text.rs`).
+
+`Mlp` mirrors `Mlp { gate, up, down }` (:205-241); `chunked_delta_rule` mirrors the free function of the same
+name (:789-807). Norms, RoPE, attention and the causal conv stay with the caller.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import device
+from ._lib import EPI_SWIGLU
+from .linear import Linear, fused_linear
+
+
+class Mlp:
+    """`down( silu(gate(x)) * up(x) )` (src/archs/qwen35_text.rs:232-240); gate/up are one contraction with the
+    SwiGLU product in its epilogue; with `residual` the caller's `x + mlp(...)` (:939) is fused into `down`."""
+
+    def __init__(self, gate: Linear, up: Linear, down: Linear):
+        self.gate, self.up, self.down = gate, up, down
+
+    def gated(self, x: torch.Tensor) -> torch.Tensor:
+        return fused_linear(x, self.gate.weight, weight_up=self.up.weight, epilogue=EPI_SWIGLU)
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.down.forward(self.gated(x), residual=residual)
+
+    __call__ = forward
+
+
+def delta_rule_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                      cu_seqlens: torch.Tensor, ctx: Optional[device.Context] = None) -> torch.Tensor:
+    """Gated delta rule on the packed layout: q, k `[T, H, 128]`, v `[T, H, Dv]`, g, beta `[T, H]` (f32, CUDA,
+    contiguous), cu_seqlens int32 `[B+1]` on the same device. Returns `[T, H, Dv]` f32."""
+    for name, t in (("q", q), ("k", k), ("v", v), ("g", g), ("beta", beta)):
+        if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous f32 CUDA tensor (no CPU fallback)")
+    if cu_seqlens.dtype != torch.int32 or not cu_seqlens.is_cuda or not cu_seqlens.is_contiguous():
+        raise ValueError("cu_seqlens must be a contiguous int32 CUDA tensor")
+    T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    if k.shape != q.shape or v.shape[:2] != (T, H) or g.shape != (T, H) or beta.shape != (T, H):
+        raise ValueError("inconsistent shapes")
+    out = torch.empty((T, H, Dv), dtype=torch.float32, device=q.device)
+    if T == 0:
+        return out
+    if ctx is None:
+        ctx = device.load(q.device.index)
+    rc = ctx._lib.s1_delta_rule(ctx.handle, *(C.c_void_p(t.data_ptr()) for t in (q, k, v, g, beta, cu_seqlens)),
+                                int(cu_seqlens.numel() - 1), T, H, Dk, Dv, C.c_void_p(out.data_ptr()))
+    ctx.check(rc)
+    return out
+
+
+def chunked_delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+                       beta: torch.Tensor) -> torch.Tensor:
+    """Same signature and layouts as the reference (src/archs/qwen35_text.rs:789-795): q, k `[B, H, L, Dk]`,
+    v `[B, H, L, Dv]`, g, beta `[B, H, L]`; returns `[B, L, H, Dv]`."""
+    B, H, L, Dk = q.shape
+    Dv = v.shape[-1]
+    tok = lambda t: t.transpose(1, 2).reshape(B * L, H, -1).contiguous()
+    cu = torch.arange(0, (B + 1) * L, L, dtype=torch.int32, device=q.device)
+    out = delta_rule_packed(tok(q), tok(k), tok(v), g.transpose(1, 2).reshape(B * L, H).contiguous(),
+                            beta.transpose(1, 2).reshape(B * L, H).contiguous(), cu)
+    return out.reshape(B, L, H, Dv)

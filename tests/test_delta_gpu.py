@@ -1,0 +1,100 @@
+"""Parity of the gated delta rule (`s1_delta_rule`, through the C ABI) with the CPU oracle; f32, tolerance 1e-4
+absolute as in the reference's own kernel test (src/archs/qwen35_text.rs:1388)."""
+import pytest
+import torch
+
+import oracle
+from golden_io import load_delta_rule
+from sys1_b200 import qwen35
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _closed_form(count, width, factor):
+    return torch.tensor([((i * 13 % 29) - 14.0) * factor for i in range(count * width)], dtype=torch.float32)
+
+
+def test_reference_kernel_test_inputs(ctx):
+    """Inputs of `delta_cuda_matches_chunked_reference` (src/archs/qwen35_text.rs:1320-1389), same tolerance."""
+    B, H, L, Dk, Dv = 2, 2, 290, 128, 16
+    q = _closed_form(B * H * L, Dk, 0.001).reshape(B, H, L, Dk)
+    k = _closed_form(B * H * L, Dk, 0.006).reshape(B, H, L, Dk)
+    v = _closed_form(B * H * L, Dv, 0.008).reshape(B, H, L, Dv)
+    g = torch.full((B, H, L), -0.002)
+    beta = torch.full((B, H, L), 0.5)
+    out = qwen35.chunked_delta_rule(*(t.to(DEV) for t in (q, k, v, g, beta)))
+    assert out.shape == (B, L, H, Dv)
+    assert (out.cpu() - oracle.chunked_delta_rule(q, k, v, g, beta)).abs().max() < 1e-4
+    assert (out.cpu() - oracle.sequential_delta_rule(q, k, v, g, beta)).abs().max() < 1e-4
+
+
+def test_golden_packed_ragged(ctx):
+    d = load_delta_rule()
+    out = qwen35.delta_rule_packed(*(d[n].to(DEV) for n in ("q", "k", "v", "g", "beta")), d["cu_seqlens"].to(DEV))
+    assert (out.cpu() - d["out"]).abs().max() < 1e-4
+
+
+def test_large_negative_gates_stay_finite(ctx):
+    q = torch.ones(1, 1, 64, 128, device=DEV)
+    v = torch.ones(1, 1, 64, 32, device=DEV)
+    g = torch.full((1, 1, 64), -8.0, device=DEV)
+    beta = torch.full((1, 1, 64), 0.5, device=DEV)
+    assert torch.isfinite(qwen35.chunked_delta_rule(q, q, v, g, beta)).all()
+
+
+def _random_inputs(T, H, Dv, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(T, H, 128, generator=g)
+    k = torch.randn(T, H, 128, generator=g)
+    q = q / (q.square().sum(-1, keepdim=True) + 1e-6).sqrt() * 128 ** -0.5
+    k = k / (k.square().sum(-1, keepdim=True) + 1e-6).sqrt()
+    v = torch.randn(T, H, Dv, generator=g)
+    gate = -torch.nn.functional.softplus(torch.randn(T, H, generator=g)) * 0.3
+    beta = torch.sigmoid(torch.randn(T, H, generator=g))
+    return q, k, v, gate, beta
+
+
+def test_empty_and_single_token_sequences(ctx):
+    q, k, v, gate, beta = _random_inputs(40, 2, 128, 5)
+    cu = torch.tensor([0, 0, 1, 1, 17, 40, 40], dtype=torch.int32)
+    out = qwen35.delta_rule_packed(*(t.to(DEV) for t in (q, k, v, gate, beta)), cu.to(DEV)).cpu()
+    for s in range(len(cu) - 1):
+        a, b = int(cu[s]), int(cu[s + 1])
+        if a == b:
+            continue
+        tr = lambda t: t[a:b].transpose(0, 1).unsqueeze(0).contiguous()
+        want = oracle.sequential_delta_rule(tr(q), tr(k), tr(v), gate[a:b].t().unsqueeze(0).contiguous(),
+                                            beta[a:b].t().unsqueeze(0).contiguous())[0]
+        assert (out[a:b] - want).abs().max() < 1e-4
+
+
+def test_full_budget_sequences_are_independent(ctx):
+    """Qwen3.5-small shape at the 16384-token budget (16 heads x 128): the state restarts at every boundary, so a
+    sequence run alone gives bit-identical rows; sampled sequences match the oracle."""
+    from sys1_b200 import batching
+    lens = batching.synthetic_lengths(1004, 64, 2048, 16384)
+    cu = torch.tensor([0] + list(lens.cumsum()), dtype=torch.int32)
+    T, H, Dv = 16384, 16, 128
+    q, k, v, gate, beta = (t.to(DEV) for t in _random_inputs(T, H, Dv, 1004))
+    out = qwen35.delta_rule_packed(q, k, v, gate, beta, cu.to(DEV))
+    assert torch.isfinite(out).all()
+    for s in (0, len(lens) // 2, len(lens) - 1):
+        a, b = int(cu[s]), int(cu[s + 1])
+        alone = qwen35.delta_rule_packed(q[a:b].contiguous(), k[a:b].contiguous(), v[a:b].contiguous(),
+                                         gate[a:b].contiguous(), beta[a:b].contiguous(),
+                                         torch.tensor([0, b - a], dtype=torch.int32, device=DEV))
+        assert torch.equal(alone, out[a:b])
+    s = int(lens.argmin())
+    a, b = int(cu[s]), int(cu[s + 1])
+    tr = lambda t: t[a:b].cpu().transpose(0, 1).unsqueeze(0).contiguous()
+    want = oracle.sequential_delta_rule(tr(q), tr(k), tr(v), gate[a:b].cpu().t().unsqueeze(0).contiguous(),
+                                        beta[a:b].cpu().t().unsqueeze(0).contiguous())[0]
+    assert (out[a:b].cpu() - want).abs().max() < 1e-4
+
+
+def test_argument_errors(ctx):
+    f = torch.zeros(4, 1, 64, device=DEV)
+    with pytest.raises(Exception, match="key_dim"):
+        qwen35.delta_rule_packed(f, f, f, f[..., 0].contiguous(), f[..., 0].contiguous(),
+                                 torch.tensor([0, 4], dtype=torch.int32, device=DEV))

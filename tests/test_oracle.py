@@ -1,0 +1,153 @@
+"""Pins the CPU oracle: the reference's self-contained known-answer tests, replayed, plus the committed
+golden fixtures (which freeze the oracle's own outputs)."""
+import math
+
+import pytest
+import torch
+
+import oracle
+from golden_io import load_delta_rule, load_projections
+
+
+def _closed_form(count, width, factor):
+    # `((index * 13 % 29) as f32 - 14.) * factor` (src/archs/qwen35_text.rs:1398-1402, 1327-1331)
+    return torch.tensor([((i * 13 % 29) - 14.0) * factor for i in range(count * width)], dtype=torch.float32)
+
+
+def test_delta_rule_matches_scalar_recurrence_across_chunk_boundary():
+    """src/archs/qwen35_text.rs:1391-1439: L70, Dk4, Dv3, g=-0.1, beta=0.45, tolerance 1e-4; the expected values
+    come from the same scalar loop the reference test runs."""
+    L, Dk, Dv = 70, 4, 3
+    q = _closed_form(L, Dk, 0.01).reshape(1, 1, L, Dk)
+    k = _closed_form(L, Dk, 0.012).reshape(1, 1, L, Dk)
+    v = _closed_form(L, Dv, 0.02).reshape(1, 1, L, Dv)
+    g = torch.full((1, 1, L), -0.1)
+    beta = torch.full((1, 1, L), 0.45)
+    # in-test scalar loop, written out as in the reference test
+    state = [[0.0] * Dv for _ in range(Dk)]
+    expected = torch.zeros(L, Dv)
+    qf, kf, vf = q.flatten().tolist(), k.flatten().tolist(), v.flatten().tolist()
+    for step in range(L):
+        decay = math.exp(-0.1)
+        for row in range(Dk):
+            for col in range(Dv):
+                state[row][col] *= decay
+        for col in range(Dv):
+            remembered = sum(kf[step * Dk + row] * state[row][col] for row in range(Dk))
+            delta = (vf[step * Dv + col] - remembered) * 0.45
+            for row in range(Dk):
+                state[row][col] += kf[step * Dk + row] * delta
+            expected[step, col] = sum(qf[step * Dk + row] * state[row][col] for row in range(Dk))
+    for fn in (oracle.chunked_delta_rule, oracle.sequential_delta_rule,
+               lambda *a: oracle.sequential_delta_rule(*a, use_c=False)):
+        out = fn(q, k, v, g, beta)[0, :, 0, :]
+        assert (out - expected).abs().max() < 1e-4
+
+
+def test_delta_rule_kernel_shape_chunked_equals_sequential():
+    """Inputs of src/archs/qwen35_text.rs:1320-1389 (B2, H2, L290, Dk128, Dv16, g=-0.002, beta=0.5): the
+    reference compares its CUDA kernel with the chunked form at 1e-4; here the two oracle forms must agree."""
+    B, H, L, Dk, Dv = 2, 2, 290, 128, 16
+    q = _closed_form(B * H * L, Dk, 0.001).reshape(B, H, L, Dk)
+    k = _closed_form(B * H * L, Dk, 0.006).reshape(B, H, L, Dk)
+    v = _closed_form(B * H * L, Dv, 0.008).reshape(B, H, L, Dv)
+    g = torch.full((B, H, L), -0.002)
+    beta = torch.full((B, H, L), 0.5)
+    a = oracle.chunked_delta_rule(q, k, v, g, beta)
+    b = oracle.sequential_delta_rule(q, k, v, g, beta)
+    assert a.shape == (B, L, H, Dv)
+    assert (a - b).abs().max() < 1e-4
+
+
+def test_delta_rule_stays_finite_with_large_negative_gates():
+    """src/archs/qwen35_text.rs:1441-1462: ones, g=-8, L=64."""
+    q = torch.ones(1, 1, 64, 4)
+    v = torch.ones(1, 1, 64, 3)
+    g = torch.full((1, 1, 64), -8.0)
+    beta = torch.full((1, 1, 64), 0.5)
+    for fn in (oracle.chunked_delta_rule, oracle.sequential_delta_rule):
+        assert torch.isfinite(fn(q, q, v, g, beta)).all()
+
+
+def test_geglu_sixteen_values():
+    """src/archs/modernbert.rs:743-766: 2x8 input, first half activated with exact-erf GELU, second half
+    multiplies; tolerance 1e-5 for f32, 0.04 for bf16. Expected values from the closed form in float64."""
+    values = [-4.0, -1.5, -0.25, 0.0, 0.5, 1.25, 3.0, 5.0, 2.0, -0.75, 0.125, -3.5, 1.0, 0.5, -2.0, 4.5]
+    x = torch.tensor(values).reshape(2, 8)
+    expected = torch.tensor([[0.5 * a * (1 + math.erf(a / math.sqrt(2))) * b
+                              for a, b in zip(row[:4], row[4:])] for row in x.tolist()])
+    assert (oracle.geglu(x, dtype="f32") - expected).abs().max() <= 1e-5
+    assert (oracle.geglu(x, dtype="bf16") - expected).abs().max() <= 0.04
+
+
+def test_linear_definition_small_integers():
+    """`Linear::forward(x) = x W^T + b` on integers small enough to be exact in every precision."""
+    x = torch.tensor([[1., 2., 3.], [0., -1., 4.]])
+    w = torch.tensor([[1., 0., -1.], [2., 2., 2.]])
+    b = torch.tensor([10., -10.])
+    want = torch.tensor([[8., 2.], [6., -4.]])
+    for dt in ("f32", "bf16"):
+        assert torch.equal(oracle.linear(x, w, b, dtype=dt), want)
+        assert torch.equal(oracle.linear(x, w, b, act="relu", residual=torch.ones(2, 2), dtype=dt),
+                           torch.relu(want) + 1)
+
+
+def test_swiglu_and_mlp_shapes():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(5, 8, generator=g)
+    wg, wu, wd = torch.randn(6, 8, generator=g), torch.randn(6, 8, generator=g), torch.randn(8, 6, generator=g)
+    y = oracle.mlp_qwen35(x, wg, wu, wd, residual=x, dtype="f32")
+    ref = x + (torch.nn.functional.silu(x @ wg.t()) * (x @ wu.t())) @ wd.t()
+    assert torch.allclose(y, ref, atol=1e-5)
+    wi = torch.randn(12, 8, generator=g)
+    y = oracle.mlp_modernbert(x, wi, wd, residual=x, dtype="f32")
+    p = x @ wi.t()
+    ref = x + (torch.nn.functional.gelu(p[:, :6]) * p[:, 6:]) @ wd.t()
+    assert torch.allclose(y, ref, atol=1e-5)
+
+
+def test_delta_inputs_and_finish_follow_the_reference_conventions():
+    """q/k heads repeat as [Hk, repeat] (key head h_k serves value heads h_k*r .. h_k*r+r-1,
+    src/archs/qwen35_text.rs:552-559); the output norm multiplies by `weight`, not 1+weight (:622)."""
+    g = torch.Generator().manual_seed(1)
+    B, L, Hk, Hv, Dk, Dv = 1, 3, 2, 4, 8, 4
+    mixed = torch.randn(B, L, 2 * Hk * Dk + Hv * Dv, generator=g)
+    b, a = torch.randn(B, L, Hv, generator=g), torch.randn(B, L, Hv, generator=g)
+    dt_bias, neg_a = torch.randn(Hv, generator=g), -torch.rand(Hv, generator=g)
+    q, k, v, gate, beta = oracle.delta_inputs(mixed, b, a, dt_bias, neg_a, Hk, Hv, Dk, Dv)
+    assert q.shape == (B, Hv, L, Dk) and v.shape == (B, Hv, L, Dv) and gate.shape == (B, Hv, L)
+    assert torch.equal(q[:, 0], q[:, 1]) and torch.equal(k[:, 2], k[:, 3]) and not torch.equal(q[:, 1], q[:, 2])
+    assert torch.allclose(k.square().sum(-1), torch.ones(B, Hv, L), atol=1e-4)
+    assert (gate <= 0).all() and ((beta > 0) & (beta < 1)).all()
+    o = torch.randn(B, L, Hv, Dv, generator=g)
+    z = torch.randn(B, L, Hv * Dv, generator=g)
+    w = torch.zeros(Dv)
+    assert torch.equal(oracle.finish_delta(o, z, w, 1e-6), torch.zeros(B, L, Hv * Dv))
+
+
+def test_golden_projections_frozen():
+    for case, d in load_projections().items():
+        assert torch.equal(oracle.linear(d["x"], d["w"]), d["plain"]), case
+        assert torch.allclose(oracle.linear(d["x"], d["w"], dtype="f32"), d["plain_f32"], rtol=1e-5, atol=1e-6), case
+        assert torch.equal(oracle.linear(d["x"], d["w"], residual=d["res"]), d["res_out"]), case
+        # activations go through libm-dependent erf / exp: allow one bf16 step on a handful of elements
+        for name, got in (("geglu", oracle.geglu(oracle.linear(d["x"], d["w"]))),
+                          ("swiglu", oracle.swiglu(oracle.linear(d["x"], d["w"]), oracle.linear(d["x"], d["w2"]))),
+                          ("bias_gelu_res", oracle.linear(d["x"], d["w"], d["bias"], act="gelu", residual=d["res"]))):
+            diff = (got - d[name]).abs()
+            assert diff.max() <= 2 ** -7 * d[name].abs().max(), (case, name)
+            assert (diff > 0).float().mean() < 1e-3, (case, name)
+
+
+def test_golden_delta_rule_frozen():
+    d = load_delta_rule()
+    cu = d["cu_seqlens"].tolist()
+    for s in range(len(cu) - 1):
+        sl = slice(cu[s], cu[s + 1])
+        tr = lambda t: t[sl].transpose(0, 1).unsqueeze(0).contiguous()
+        o = oracle.sequential_delta_rule(tr(d["q"]), tr(d["k"]), tr(d["v"]), d["g"][sl].t().unsqueeze(0).contiguous(),
+                                         d["beta"][sl].t().unsqueeze(0).contiguous())
+        assert torch.allclose(o[0], d["out"][sl], atol=1e-6)
+        c = oracle.chunked_delta_rule(tr(d["q"]), tr(d["k"]), tr(d["v"]), d["g"][sl].t().unsqueeze(0).contiguous(),
+                                      d["beta"][sl].t().unsqueeze(0).contiguous())
+        assert (c[0] - d["out"][sl]).abs().max() < 1e-4
