@@ -1,0 +1,315 @@
+#!/usr/bin/env python
+"""Benchmark of the projection hot path: the four ModernBERT-base projections with their fused epilogues over a
+token-packed ragged batch (sequence lengths uniform in [16, 512] packed to a 32768-token budget).
+
+One step = one pass of the path over one batch:
+    qkv = x Wqkv^T                      (768 -> 2304)
+    h   = x + attn Wo^T                 (768 -> 768, residual fused)
+    m   = geglu(h Wi^T)                 (768 -> 2 x 1152, GeGLU fused)
+    y   = h + m Wout^T                  (1152 -> 768, residual fused)
+Work counted per step: 2 * T * sum(K * N) flops (epilogue flops not counted).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl reference]
+
+Under torchrun (N > 1) every rank runs the same workload on its own GPU (independent replicas, no collective on
+the data path); the reported value is the whole-job rate: N * work / max-over-ranks time.
+`--impl reference` times the CPU oracle (the restatement of the reference's CPU path) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# ModernBERT-base projections: (name, K, N rows of the weight, output width, epilogue)
+HIDDEN, QKV, INTER = 768, 2304, 1152
+PROJECTIONS = [
+    ("wqkv", HIDDEN, QKV, QKV, "none"),
+    ("wo+residual", HIDDEN, HIDDEN, HIDDEN, "residual"),
+    ("wi+geglu", HIDDEN, 2 * INTER, INTER, "geglu"),
+    ("mlp_out+residual", INTER, HIDDEN, HIDDEN, "residual"),
+]
+FLOPS_PER_TOKEN = sum(2 * k * n for _, k, n, _, _ in PROJECTIONS)  # 10,027,008
+SEED = 1002
+# DRAM bytes (read + write) per launch of the dominant kernel, from the ncu capture summarised under profiles/;
+# None until a capture of the current kernel exists.
+NCU_TRAFFIC_BYTES = {"wi+geglu": None, "wqkv": None}
+FALLBACK_PEAK_TFLOPS = 1590.0
+
+
+def algorithmic_bytes(name: str, T: int) -> int:
+    for n, k, nw, nout, epi in PROJECTIONS:
+        if n == name:
+            b = 2 * (T * k + k * nw + T * nout)
+            return b + (2 * T * nout if epi == "residual" else 0)
+    raise KeyError(name)
+
+
+def make_weights(device, dtype):
+    g = torch.Generator().manual_seed(SEED)
+    mk = lambda n, k: (torch.randn(n, k, generator=g) * 0.02).to(dtype).to(device)
+    return {"wqkv": mk(QKV, HIDDEN), "wo": mk(HIDDEN, HIDDEN), "wi": mk(2 * INTER, HIDDEN), "wout": mk(HIDDEN, INTER)}
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+        except Exception:
+            pass
+    return FALLBACK_PEAK_TFLOPS, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index), "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 - 0.05 <= t <= t1 + 0.1 and len(r) >= 6] or [r for _, r in self.rows if len(r) >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        mhz = sorted(int(r[0]) for r in rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": int(rows[0][1]) if rows[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(rows)}
+
+
+def run_cpu_arm(tokens: int, steps: int, warmup: int, budget_s: float = 20.0):
+    """The oracle's CPU path (f32, all host threads) on a bounded sample of the same workload: `tokens` rows."""
+    import oracle
+    torch.manual_seed(SEED)
+    W = {k: v.float() for k, v in make_weights("cpu", torch.float32).items()}
+    g = torch.Generator().manual_seed(SEED + 1)
+    x = torch.randn(tokens, HIDDEN, generator=g)
+    attn = torch.randn(tokens, HIDDEN, generator=g)
+
+    def step():
+        qkv = oracle.linear(x, W["wqkv"], dtype="f32")
+        h = oracle.linear(attn, W["wo"], residual=x, dtype="f32")
+        m = oracle.geglu(oracle.linear(h, W["wi"], dtype="f32"), dtype="f32")
+        return qkv, oracle.linear(m, W["wout"], residual=h, dtype="f32")
+
+    for _ in range(max(1, warmup)):
+        step()
+    times = []
+    t_start = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_start > budget_s:
+            break
+    dt = sum(times) / len(times)
+    return FLOPS_PER_TOKEN * tokens / dt / 1e12, dt, len(times), torch.get_num_threads()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=32768)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    T = args.tokens
+    warmup = max(args.warmup, 3)
+    config = {"workload": f"ModernBERT-base projection microbench, packed ragged batch, T={T} tokens "
+                          "(lengths U[16,512]), Wqkv / Wo+residual / Wi+GeGLU / MLP-out+residual",
+              "tokens": T, "hidden": HIDDEN, "intermediate": INTER, "parallelism": f"replicas x{world}",
+              "l2": "4 rotating input sets + 326 MB of outputs per step exceed the 126 MB L2"}
+
+    if args.impl == "reference":
+        # rank 0 alone runs the CPU arm; the other ranks leave without work
+        if rank != 0:
+            return
+        val, dt, n, cores = run_cpu_arm(args.cpu_sample_tokens, max(1, args.steps), warmup, budget_s=60.0)
+        line = {"impl": "reference", "metric": "projection GEMM TFLOP/s", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+                "steps": n, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                 "sample": f"{args.cpu_sample_tokens} of the {T} packed token rows per step, same four projections, "
+                                           "torch CPU f32 oracle (restatement of the reference's candle CPU path; the Rust "
+                                           "reference itself cannot be built here: no cargo/rustc)"},
+                "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback for the product path (use --impl reference for the CPU arm)")
+    from sys1_b200 import batching, device, linear, modernbert
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = device.load(local_rank)
+
+    # the batch: packed layout from the batcher (the projections ignore sequence boundaries, attention would not)
+    lens = batching.synthetic_lengths(SEED + rank, 16, 512, T)
+    batch, taken = batching.pack_next(lens, batching.BatcherConfig(token_budget=T))
+    assert batch.total_tokens == T and taken == len(lens)
+    W = make_weights(dev, torch.bfloat16)
+    proj = modernbert.AttentionProjections(linear.linear_no_bias(W["wqkv"]), linear.linear_no_bias(W["wo"]))
+    mlp = modernbert.Mlp(linear.linear_no_bias(W["wi"]), linear.linear_no_bias(W["wout"]))
+
+    NSETS = 4
+    g = torch.Generator().manual_seed(SEED + 100 + rank)
+    host_x = [torch.randn(T, HIDDEN, generator=g).to(torch.bfloat16).pin_memory() for _ in range(NSETS)]
+    host_a = [torch.randn(T, HIDDEN, generator=g).to(torch.bfloat16).pin_memory() for _ in range(NSETS)]
+    xs = [t.to(dev) for t in host_x]
+    atts = [t.to(dev) for t in host_a]
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    qkv, h, m, y = (torch.empty(T, n, **bf) for n in (QKV, HIDDEN, INTER, HIDDEN))
+    host_y = torch.empty(T, HIDDEN, dtype=torch.bfloat16).pin_memory()
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    names = [p[0] for p in PROJECTIONS]
+
+    def step(x, a, marks=None):
+        """marks: list of 5 events recorded between the launches (on the launching stream)."""
+        if marks: marks[0].record()
+        proj.wqkv.forward(x, out=qkv)
+        if marks: marks[1].record()
+        proj.wo.forward(a, residual=x, out=h)
+        if marks: marks[2].record()
+        linear.fused_linear(h, mlp.input.weight, epilogue=linear.EPI_GEGLU, out=m)
+        if marks: marks[3].record()
+        mlp.output.forward(m, residual=h, out=y)
+        if marks: marks[4].record()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident arm ---------------------------------------------------------------------------------
+    for i in range(warmup):
+        step(xs[i % NSETS], atts[i % NSETS])
+    ctx.sync()
+    launches0 = ctx.launch_count()
+    marks = [[ev() for _ in range(5)] for _ in range(args.steps)]
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.15)
+    barrier()
+    t0w = time.time()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for i in range(args.steps):
+        step(xs[i % NSETS], atts[i % NSETS], marks[i])
+    e1.record()
+    barrier()
+    t1w = time.time()
+    ctx.sync()
+    launches = ctx.launch_count() - launches0
+    ms_total = e0.elapsed_time(e1)
+    per = {n: sum(marks[i][j].elapsed_time(marks[i][j + 1]) for i in range(args.steps)) / args.steps
+           for j, n in enumerate(names)}
+
+    # ---- end-to-end arm: host buffers in, host buffer out, copies inside the timed region ----------------------
+    xd, ad = torch.empty(T, HIDDEN, **bf), torch.empty(T, HIDDEN, **bf)
+
+    def e2e_step(i):
+        xd.copy_(host_x[i % NSETS], non_blocking=True)
+        ad.copy_(host_a[i % NSETS], non_blocking=True)
+        step(xd, ad)
+        host_y.copy_(y, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    f0, f1 = ev(), ev()
+    f0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    f1.record()
+    barrier()
+    clocks = sampler.stop(t0w, t1w)
+    ctx.sync()
+    ms_e2e = f0.elapsed_time(f1)
+
+    ms_step, ms_step_e2e = ms_total / args.steps, ms_e2e / e2e_steps
+    if world > 1:
+        t = torch.tensor([ms_step, ms_step_e2e], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_step, ms_step_e2e = float(t[0]), float(t[1])
+    flops_step = FLOPS_PER_TOKEN * T
+    value = world * flops_step / (ms_step * 1e-3) / 1e12
+    e2e_value = world * flops_step / (ms_step_e2e * 1e-3) / 1e12
+
+    if rank == 0:
+        burst, sustained, peak_kind = measured_peak()
+        dom = max(per, key=per.get)
+        dom_proj = next(p for p in PROJECTIONS if p[0] == dom)
+        dom_flops = 2 * T * dom_proj[1] * dom_proj[2]
+        achieved = dom_flops / (per[dom] * 1e-3) / 1e12
+        # a kernel timed alone between events in a run of a few tens of milliseconds: the burst figure applies
+        line = {"metric": "projection GEMM TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic", "config": config,
+                "roofline": {"bound": "tensor", "kernel": f"s1_gemm_kernel ({dom})", "achieved": achieved, "peak": burst,
+                             "unit": "TFLOP/s", "frac": achieved / burst, "peak_source": f"{peak_kind} bf16 burst",
+                             "frac_of_sustained": achieved / sustained, "flops_per_launch": dom_flops,
+                             "us_per_launch": per[dom] * 1e3, "algorithmic_bytes": algorithmic_bytes(dom, T),
+                             "traffic": NCU_TRAFFIC_BYTES.get(dom)},
+                "per_projection": {n: {"us": per[n] * 1e3,
+                                       "tflops": 2 * T * p[1] * p[2] / (per[n] * 1e-3) / 1e12,
+                                       "gbs": algorithmic_bytes(n, T) / (per[n] * 1e-3) / 1e9}
+                                   for n, p in zip(names, PROJECTIONS)},
+                "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_step_e2e,
+                        "h2d_bytes_per_step": 2 * T * HIDDEN * 2, "d2h_bytes_per_step": T * HIDDEN * 2},
+                "gpu_launches": launches, "clocks": clocks}
+        if not args.no_cpu_baseline:
+            val, dt, n, cores = run_cpu_arm(args.cpu_sample_tokens, 1000, 1, budget_s=12.0)
+            line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"{args.cpu_sample_tokens} of the {T} token rows, same four projections, "
+                                              f"torch CPU f32 oracle, {n} timed passes"}
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
