@@ -41,9 +41,10 @@ PROJECTIONS = [
 ]
 FLOPS_PER_TOKEN = sum(2 * k * n for _, k, n, _, _ in PROJECTIONS)  # 10,027,008
 SEED = 1002
-# DRAM bytes (read + write) per launch of the dominant kernel, from the ncu capture summarised under profiles/;
-# None until a capture of the current kernel exists.
-NCU_TRAFFIC_BYTES = {"wi+geglu": None, "wqkv": None}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch at T = 32768, from the ncu capture
+# summarised in profiles/gemm_projections_T32768.md (scaled by T / 32768 for other sizes).
+NCU_TRAFFIC_BYTES = {"wi+geglu": 89_369_088, "wqkv": 153_107_456, "wo+residual": 125_161_216,
+                     "mlp_out+residual": 152_696_576}
 FALLBACK_PEAK_TFLOPS = 1590.0
 
 
@@ -292,7 +293,7 @@ def main():
                              "unit": "TFLOP/s", "frac": achieved / burst, "peak_source": f"{peak_kind} bf16 burst",
                              "frac_of_sustained": achieved / sustained, "flops_per_launch": dom_flops,
                              "us_per_launch": per[dom] * 1e3, "algorithmic_bytes": algorithmic_bytes(dom, T),
-                             "traffic": NCU_TRAFFIC_BYTES.get(dom)},
+                             "traffic": (NCU_TRAFFIC_BYTES[dom] * T // 32768) if dom in NCU_TRAFFIC_BYTES else None},
                 "per_projection": {n: {"us": per[n] * 1e3,
                                        "tflops": 2 * T * p[1] * p[2] / (per[n] * 1e-3) / 1e12,
                                        "gbs": algorithmic_bytes(n, T) / (per[n] * 1e-3) / 1e9}
