@@ -90,3 +90,51 @@ def load(ordinal: Optional[int] = None) -> Context:
         ctx = Context(ordinal, stream)
         _contexts[key] = ctx
     return ctx
+
+
+# ------------------------------------------------------------------------------------------------ multi-GPU
+def shard_sequences(lengths, world_size: int, rank: int):
+    """Indices of the sequences replica `rank` serves: whole sequences, assigned longest-first to the replica with
+    the fewest tokens so far (sequences never interact, so replicas need no collective). Deterministic on every
+    rank; ties go to the lower rank."""
+    import numpy as np
+    lengths = np.asarray(lengths, dtype=np.int64)
+    order = np.argsort(-lengths, kind="stable")
+    loads = [0] * world_size
+    mine = []
+    for idx in order:
+        r = min(range(world_size), key=lambda i: (loads[i], i))
+        loads[r] += int(lengths[idx])
+        if r == rank:
+            mine.append(int(idx))
+    return sorted(mine)
+
+
+def column_parallel_shard(weight: torch.Tensor, rank: int, world_size: int, pairs: int = 1) -> torch.Tensor:
+    """Row range of `weight [N, K]` owned by `rank` (its share of the output features). With `pairs = 2` the matrix
+    is two stacked halves (GeGLU's activated / gate rows) and the rank takes the same range of each half.
+    Single-half shards are views (passed to the library through `ldw`, no copy)."""
+    n = weight.shape[0] // pairs
+    if n % world_size:
+        raise ValueError(f"{n} output features do not split over {world_size} ranks")
+    lo, hi = rank * n // world_size, (rank + 1) * n // world_size
+    if pairs == 1:
+        return weight[lo:hi]
+    return torch.cat([weight[h * n + lo:h * n + hi] for h in range(pairs)])
+
+
+def row_parallel_shard(weight: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
+    """K range of `weight [N, K]` owned by `rank` (a strided view; its partial product needs a sum over ranks)."""
+    k = weight.shape[1]
+    if k % (8 * world_size):
+        raise ValueError(f"K={k} does not split over {world_size} ranks in multiples of 8")
+    return weight[:, rank * k // world_size:(rank + 1) * k // world_size]
+
+
+def all_reduce_sum_(t: torch.Tensor) -> torch.Tensor:
+    """Sum over the ranks of the default process group (NCCL on GPUs, gloo on CPU): the exchange step that follows
+    a row-parallel projection."""
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return t
