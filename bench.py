@@ -113,6 +113,8 @@ class ClockSampler:
 def run_cpu_arm(tokens: int, steps: int, warmup: int, budget_s: float = 20.0):
     """The oracle's CPU path (f32, all host threads) on a bounded sample of the same workload: `tokens` rows."""
     import oracle
+    # torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every core the process may run on
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     torch.manual_seed(SEED)
     W = {k: v.float() for k, v in make_weights("cpu", torch.float32).items()}
     g = torch.Generator().manual_seed(SEED + 1)

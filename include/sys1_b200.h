@@ -91,6 +91,8 @@ typedef struct s1_linear_desc {
  * (:521-533), qwen35 `Mlp::forward` (src/archs/qwen35_text.rs:232-240), q/k/v/o_proj (:314-339,410),
  * in_proj_* / out_proj (:516,567-568,605-628) and the biased head Linears (src/models/laya.rs:133-155).
  * T is the packed token count (any value >= 1); K and N_out must be multiples of 8.
+ * `residual` may be the same buffer as `y` (same leading dimension): the residual stream is then updated in
+ * place, `y += x W^T`, which is what the reference's `xs = (xs + ...)` amounts to once the old value is dead.
  */
 int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, const void* residual,
               long long ldr, void* y, long long ldy, int T);

@@ -141,7 +141,7 @@ static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0,
     const int grid = (tiles < units ? tiles : units) * CTAS;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.blockDim = dim3(gemm_threads<BN, EPI>(), 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -248,7 +248,9 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
         p.half1_base = bn / 2;
     }
 
-    const int mode = (residual ? 1 : 0) | ((lin->bias || lin->act != S1_ACT_NONE) ? 2 : 0);
+    int mode = (residual ? 1 : 0) | ((lin->bias || lin->act != S1_ACT_NONE) ? 2 : 0);
+    // residual stream updated in place (y is the residual buffer): no residual reads, the add happens in memory
+    if (mode == 1 && residual == y && ldr == ldy) mode = 4;
 #define S1_LAUNCH(BN_, CTAS_)                                                                            \
     do {                                                                                                 \
         if (epi == S1_EPI_GEGLU) return launch_gemm<BN_, EPI_GEGLU, 0, CTAS_>(ctx, ta, tb0, tb1, ty, p);   \
@@ -257,6 +259,7 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
             case 0: return launch_gemm<BN_, EPI_NONE, 0, CTAS_>(ctx, ta, tb0, tb1, ty, p);                \
             case 1: return launch_gemm<BN_, EPI_NONE, 1, CTAS_>(ctx, ta, tb0, tb1, ty, p);                \
             case 2: return launch_gemm<BN_, EPI_NONE, 2, CTAS_>(ctx, ta, tb0, tb1, ty, p);                \
+            case 4: return launch_gemm<BN_, EPI_NONE, 4, CTAS_>(ctx, ta, tb0, tb1, ty, p);                \
             default: return launch_gemm<BN_, EPI_NONE, 3, CTAS_>(ctx, ta, tb0, tb1, ty, p);               \
         }                                                                                                \
     } while (0)

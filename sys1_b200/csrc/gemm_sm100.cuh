@@ -16,13 +16,13 @@
 //             ends up with the accumulator of its own 128 rows in its own TMEM. No TMA multicast is used:
 //             every CTA issues its own loads; only tcgen05.commit is multicast to the two CTAs' barriers.
 //
-// Roles inside a CTA (320 threads, static round-robin tile schedule, tile index n-fastest so the CTAs that
+// Roles inside a CTA (320 threads, 576 for the gated epilogues, static round-robin tile schedule, tile index n-fastest so the CTAs that
 // run together share X rows and the whole (small) W through L2):
 //   warp 0      : TMA producer  - 128-byte-swizzled boxes {64 x 128 rows} of X and {64 x BN/2 rows} of W into a
 //                 ring of STAGES buffers guarded by full/empty mbarriers
 //   warp 1      : TMEM allocation + single-thread tcgen05.mma issue (K = 16 per instruction), two TMEM
 //                 accumulators so the epilogue of tile i overlaps the MMAs of tile i+1
-//   warps 2..9  : epilogue - tcgen05.ld of the warp's TMEM lane quarter, rounding/gating in registers,
+//   warps 2..   : epilogue (8 or 16 warps) - tcgen05.ld of the warp's TMEM lane quarter, rounding/gating in registers,
 //                 swizzled staging tile in shared memory, TMA store (full-line writes, clipped at the edges)
 // Every wait is bounded (see mbar_wait); a wait that runs out raises a status word the host reads.
 #pragma once
@@ -52,8 +52,16 @@ struct GemmParams {
 
 constexpr int kBM = 128;  // rows per CTA
 constexpr int kBK = 64;   // 64 bf16 = 128 bytes = one swizzle row
-constexpr int kGemmThreads = 320;  // TMA warp + MMA warp + 8 epilogue warps
 constexpr int kEpiWarp0 = 2;
+
+// Epilogue warps: 8 for the plain epilogues; 16 for the gated ones, whose erf / exp evaluation is latency-bound and
+// needs the extra warps to keep the issue slots busy.
+template <int BN, int EPI>
+struct EpiWarps {
+    static constexpr int value = (EPI != EPI_NONE && BN == 256) ? 16 : 8;
+};
+template <int BN, int EPI>
+constexpr int gemm_threads() { return 64 + 32 * EpiWarps<BN, EPI>::value; }
 
 template <int BN, int CTAS>
 struct GemmCfg {
@@ -64,14 +72,43 @@ struct GemmCfg {
     static constexpr int kStageBytes = kABytes + (CTAS == 1 ? 2 : 1) * kBHalfBytes;
     static constexpr int kStages = (192 * 1024) / kStageBytes;  // 4 (48 KB stages) or 6 (32 KB stages)
     static constexpr int kTmemCols = 2 * BN;            // two accumulators; 256 or 512, powers of two
-    static constexpr int kEpiStagingBytes = 8 * 4096;   // per epilogue warp: two 32x32 bf16 tiles
+    static constexpr int kEpiStagingBytes = 8 * 4096;   // 8 warps x two 32x32 bf16 tiles, or 16 warps x one
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiStagingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
-// Exact-erf GELU x * Phi(x) (src/kernels/modernbert.cu:11-12 writes it as value * normcdff(value)); erff is the
-// cheaper of the two library routes and agrees with it to within an f32 ulp of Phi before the bf16 rounding.
-__device__ __forceinline__ float gelu_erf_ref(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
-__device__ __forceinline__ float silu_ref(float v) { return v / (1.f + __expf(-v)); }
+// Special-function unit forms (relative error about 2^-22, far below the bf16 rounding that follows).
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// Exact-erf GELU x * Phi(x) (src/kernels/modernbert.cu:11-12 writes it as value * normcdff(value)),
+// with Phi through erfc(|z|) = t exp(-z^2 + P(t)), t = 1 / (1 + |z| / 2), the Chebyshev fit of
+// Numerical Recipes (erfcc): FRACTIONAL error below 1.2e-7 everywhere, so the tail (negative inputs) keeps full
+// relative accuracy; evaluated on the tail side, nothing cancels. Two special-function ops and eleven FMAs.
+__device__ __forceinline__ float gelu_erf_ref(float v) {
+    const float z = fabsf(v) * 0.70710678118654752f;
+    const float t = rcp_approx(fmaf(0.5f, z, 1.f));
+    float u = fmaf(t, 0.17087277f, -0.82215223f);
+    u = fmaf(t, u, 1.48851587f);
+    u = fmaf(t, u, -1.13520398f);
+    u = fmaf(t, u, 0.27886807f);
+    u = fmaf(t, u, -0.18628806f);
+    u = fmaf(t, u, 0.09678418f);
+    u = fmaf(t, u, 0.37409196f);
+    u = fmaf(t, u, 1.00002368f);
+    u = fmaf(t, u, -1.26551223f);
+    u = fmaf(-z, z, u);
+    const float half_erfc = 0.5f * t * ex2_approx(1.4426950408889634f * u);  // Phi(-|v|)
+    return v * (v >= 0.f ? 1.f - half_erfc : half_erfc);
+}
+__device__ __forceinline__ float silu_ref(float v) { return v * rcp_approx(1.f + ex2_approx(-1.4426950408889634f * v)); }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
@@ -83,20 +120,32 @@ __device__ __forceinline__ void unpack_bf16x2(uint32_t v, float& lo, float& hi) 
     hi = __high2float(t);
 }
 
+// Residual values of one epilogue warp's part of a tile (32 rows x CH*32 columns, one row per lane), fetched
+// before the warp waits for the accumulator so that the memory latency hides behind the MMAs.
+template <int CH>
+__device__ __forceinline__ void fetch_residual(const GemmParams& p, int row0, int col0, int lane, uint4 (&res)[CH * 4]) {
+    const int row = row0 + lane;
+    const __nv_bfloat16* rrow = p.residual + static_cast<long long>(row) * p.ldr;
+#pragma unroll
+    for (int j = 0; j < CH * 4; ++j) {
+        res[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (row < p.M && col0 + j * 8 < p.n_out) res[j] = __ldg(reinterpret_cast<const uint4*>(rrow + col0 + j * 8));
+    }
+}
+
 // One epilogue warp, one tile: reads its 32 rows x (CH*32) accumulator columns out of TMEM, applies the epilogue
 // and stores. `tempty_bar` is the (cluster-space) address of the barrier that hands the accumulator back.
-// MODE (plain epilogue only): bit0 = residual add, bit1 = bias and/or activation present (general path).
-template <int BN, int EPI, int MODE>
+// MODE (plain epilogue only): bit0 = residual add, bit1 = bias and/or activation present (general path);
+// 4 = the output buffer already holds the residual: the tile is added to it by a TMA reduction.
+template <int BN, int EPI, int MODE, int EW>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap* tmY, uint32_t taddr, int row0,
                                               int col0, uint32_t stage_buf, uint32_t& nstore, uint32_t tempty_bar,
-                                              int lane) {
+                                              int lane, const uint4* res) {
     constexpr bool PAIRED = (EPI != EPI_NONE);
     constexpr int OUT_W = PAIRED ? BN / 2 : BN;
-    constexpr int CH = OUT_W / 64;  // 32-column work units per warp per tile
-    const int row = row0 + lane;
-    const bool row_ok = row < p.M;
-    const __nv_bfloat16* rrow = (MODE & 1) ? p.residual + static_cast<long long>(row) * p.ldr : nullptr;
-
+    constexpr int CH = OUT_W / (EW * 8);  // 32-column work units per warp per tile
+    constexpr int NBUF = (EW == 8) ? 2 : 1;  // staging tiles per warp
+    static_assert(CH >= 1, "tile too narrow for this many epilogue warps");
     uint32_t va[2][32];
     uint32_t vg[PAIRED ? 2 : 1][PAIRED ? 32 : 1];
     tmem_ld_32x32b_x32(taddr, va[0]);
@@ -104,14 +153,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
 #pragma unroll
     for (int ci = 0; ci < CH; ++ci) {
         const int col = col0 + ci * 32;
-        uint4 rv[4] = {};
-        if constexpr (!PAIRED && (MODE & 1)) {
-            if (row_ok) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (col + j * 8 < p.n_out) rv[j] = __ldg(reinterpret_cast<const uint4*>(rrow + col + j * 8));
-            }
-        }
+        const uint4* rv = &res[(MODE & 1) ? ci * 4 : 0];
         tmem_ld_wait();
         if (ci + 1 < CH) {
             tmem_ld_32x32b_x32(taddr + (ci + 1) * 32, va[(ci + 1) & 1]);
@@ -175,17 +217,18 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                 __nv_bfloat162 g2 = __floats2bfloat162_rn(__uint_as_float(w[2 * j]), __uint_as_float(w[2 * j + 1]));
                 const float a0 = __low2float(a2), a1 = __high2float(a2);
                 __nv_bfloat162 act2;
-                if constexpr (EPI == EPI_GEGLU) act2 = __floats2bfloat162_rn(gelu_erf_ref(a0), gelu_erf_ref(a1));
+                if (p.debug & 8) act2 = a2;  // measurement aid: no activation
+                else if constexpr (EPI == EPI_GEGLU) act2 = __floats2bfloat162_rn(gelu_erf_ref(a0), gelu_erf_ref(a1));
                 else act2 = __floats2bfloat162_rn(silu_ref(a0), silu_ref(a1));
                 __nv_bfloat162 o2 = __hmul2(act2, g2);
                 out[j] = *reinterpret_cast<uint32_t*>(&o2);
             }
         }
         if (row0 < p.M && col < p.n_out && !(p.debug & 1)) {
-            const uint32_t buf = stage_buf + (nstore & 1u) * 2048u;
+            const uint32_t buf = stage_buf + (nstore % NBUF) * 2048u;
             ++nstore;
-            // the staging tile written two stores ago must have been read out by its TMA store
-            if (lane == 0) tma_store_wait_read<1>();
+            // the staging tile about to be overwritten must have been read out by its TMA store
+            if (lane == 0) tma_store_wait_read<NBUF - 1>();
             __syncwarp();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -198,7 +241,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                tma_store_2d(tmY, buf, col, row0);
+                if constexpr (MODE == 4) tma_reduce_add_2d(tmY, buf, col, row0);  // y already holds the residual
+                else tma_store_2d(tmY, buf, col, row0);
                 tma_store_commit();
             }
         }
@@ -206,7 +250,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
 }
 
 template <int BN, int EPI, int MODE, int CTAS>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads<BN, EPI>(), 1)
 s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmY,
                const GemmParams p) {
@@ -214,7 +258,8 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int STAGES = Cfg::kStages;
     constexpr bool PAIRED = (EPI != EPI_NONE);
     constexpr int OUT_W = PAIRED ? BN / 2 : BN;  // output columns per tile
-    constexpr int CH = OUT_W / 64;
+    constexpr int EW = EpiWarps<BN, EPI>::value;
+    constexpr int CH = OUT_W / (EW * 8);  // 32-column work units per epilogue warp per tile
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -247,7 +292,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8u * a, 1);
-            mbar_init(tempty0 + 8u * a, 8 * CTAS);
+            mbar_init(tempty0 + 8u * a, EW * CTAS);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -356,11 +401,15 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // column half hh.
         const int q = warp & 3;
         const int hh = (warp - kEpiWarp0) >> 2;
-        const uint32_t stage_buf = smem_base + STAGES * Cfg::kStageBytes + (warp - kEpiWarp0) * 4096;
+        const uint32_t stage_buf = smem_base + STAGES * Cfg::kStageBytes + (warp - kEpiWarp0) * (Cfg::kEpiStagingBytes / EW);
         uint32_t it = 0, nstore = 0;
         for (int tile = unit; tile < num_tiles; tile += num_units, ++it) {
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
             const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
+            const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + q * 32;
+            const int col0 = tn * OUT_W + hh * (CH * 32);
+            uint4 res[(MODE & 1) ? CH * 4 : 1];
+            if constexpr (!PAIRED && (MODE & 1)) fetch_residual<CH>(p, row0, col0, lane, res);
             // the whole warp must agree before any .sync.aligned tcgen05 instruction
             const bool ready = mbar_wait(tfull0 + 8u * acc, aph, abort_flag);
             if (!__all_sync(0xffffffffu, ready)) {
@@ -376,10 +425,8 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (lane == 0) mbar_arrive_cluster(tempty_bar);
                 continue;
             }
-            const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + q * 32;
-            const int col0 = tn * OUT_W + hh * (CH * 32);
             const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + hh * (CH * 32);
-            epilogue_tile<BN, EPI, MODE>(p, &tmY, taddr, row0, col0, stage_buf, nstore, tempty_bar, lane);
+            epilogue_tile<BN, EPI, MODE, EW>(p, &tmY, taddr, row0, col0, stage_buf, nstore, tempty_bar, lane, res);
         }
         if (lane == 0) tma_store_wait<0>();  // smem reads and global writes of this warp's stores are complete
         __syncwarp();

@@ -29,7 +29,9 @@ def assert_matches_bf16_oracle(y, want, what=""):
     diff = (y - want).abs()
     scale = want.abs().max().clamp_min(1e-6)
     assert diff.max() <= 2 ** -6 * scale, f"{what}: max diff {diff.max():.3e} vs scale {scale:.3e}"
-    frac = (diff > 0).float().mean().item()
+    # elements deep in the GELU tail (|want| below 1e-3 of the scale) are left out of the count: there the f32
+    # oracle's 1 + erf cancels to zero while x * Phi(x) evaluated on the tail side does not; both are ~0
+    frac = ((diff > 0) & (want.abs() >= 1e-3 * scale)).float().mean().item()
     assert frac < 0.05, f"{what}: {frac:.4f} of the elements differ from the bf16 oracle"
 
 
@@ -204,3 +206,19 @@ def test_raw_c_abi_call_and_error_codes(ctx):
     d.epilogue = 0
     assert lib.s1_linear(ctx.handle, C.byref(d), x.data_ptr(), K, None, 0, y.data_ptr(), N, 0) == _lib.S1_EINVAL
     assert lib.s1_set_option(ctx.handle, b"nonsense", 1) == _lib.S1_EINVAL
+
+
+def test_residual_stream_updated_in_place(ctx):
+    """`y` aliasing `residual`: the tile is added to the buffer in memory; same values as the out-of-place form."""
+    g = torch.Generator().manual_seed(11)
+    T, N, K = 1000, 768, 1152
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    res = torch.randn(T, N, generator=g).to(torch.bfloat16).to(DEV)
+    want = linear.fused_linear(x, w, residual=res)
+    stream = res.clone()
+    got = linear.fused_linear(x, w, residual=stream, out=stream)
+    ctx.sync()
+    assert got.data_ptr() == stream.data_ptr()
+    assert_matches_bf16_oracle(got, oracle.linear(x.cpu(), w.cpu(), residual=res.cpu()), "in-place residual")
+    assert (got.float() - want.float()).abs().max() <= 2 ** -7 * want.float().abs().max()
