@@ -33,7 +33,8 @@ enum {
     S1_ECUDA = -2,    /* a CUDA runtime / driver call failed */
     S1_EDEVICE = -3,  /* not an sm_100 device, or no device */
     S1_EKERNEL = -4,  /* a kernel recorded an error status (bounded wait ran out) */
-    S1_ENOMEM = -5
+    S1_ENOMEM = -5,
+    S1_ELIMIT = -6    /* s1_linear_static only: the problem is larger than that entry point supports */
 };
 
 /* Epilogue fused behind the contraction. */
@@ -96,6 +97,32 @@ typedef struct s1_linear_desc {
  */
 int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, const void* residual,
               long long ldr, void* y, long long ldy, int T);
+
+/*
+ * The projection for callers that cannot allocate device memory. It has no counterpart in the reference: it
+ * exists for hosts whose GPU memory is owned by another allocator (sys1's Rust side takes every buffer from
+ * candle's pool), and for code running while a stream is captured or inside a latency-critical loop, where
+ * cudaMalloc is forbidden or stalls the device. `s1_linear` needs a context, and `s1_ctx_create` allocates the
+ * kernels' status block; this entry point needs neither. Its only scratch - that status block - is a 256-byte
+ * `__device__` array inside the library (one per GPU that loads it, held until the process exits), and it
+ * calls no cudaMalloc / cudaFree or any other allocating routine; tensor maps are encoded on the stack per call.
+ *
+ * Same arguments and results as `s1_linear` for S1_EPI_NONE (with or without `residual`, in place or not),
+ * S1_EPI_GEGLU and S1_EPI_SWIGLU; `bias` and `act` are not offered here. `cuda_stream` is the stream to enqueue
+ * on (NULL = default stream). `wait` != 0 makes the call join the stream and return S1_EKERNEL if the kernel
+ * recorded an error; with `wait` == 0 the call is asynchronous and a kernel-side error goes unreported.
+ * `err` / `err_len`: optional buffer that receives the message of a failing call.
+ * Limits: T <= S1_STATIC_MAX_TOKENS, N and K <= S1_STATIC_MAX_FEATURES; beyond them the call returns S1_ELIMIT.
+ * The first call on a GPU looks up the array's device address and sets kernel attributes: make that first call
+ * outside any stream capture. Every call shares the one array (each call clears the status words it needs
+ * zeroed), so calls whose kernels may overlap on the GPU - other streams, other threads - race on it: keep the
+ * calls of this entry point on one stream at a time.
+ */
+#define S1_STATIC_MAX_TOKENS 262144
+#define S1_STATIC_MAX_FEATURES 32768
+int s1_linear_static(int device_ordinal, void* cuda_stream, const s1_linear_desc* lin, const void* x, long long ldx,
+                     const void* residual, long long ldr, void* y, long long ldy, int T, int wait, char* err,
+                     size_t err_len);
 
 /*
  * Gated delta rule over a token-packed batch; exact drop-in for `chunked_delta_rule(q, k, v, g, beta)`

@@ -13,11 +13,12 @@ PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "libsys1_b200.so"
 
 S1_OK = 0
-S1_EINVAL, S1_ECUDA, S1_EDEVICE, S1_EKERNEL, S1_ENOMEM = -1, -2, -3, -4, -5
+S1_EINVAL, S1_ECUDA, S1_EDEVICE, S1_EKERNEL, S1_ENOMEM, S1_ELIMIT = -1, -2, -3, -4, -5, -6
+STATIC_MAX_TOKENS, STATIC_MAX_FEATURES = 262144, 32768
 EPI_NONE, EPI_GEGLU, EPI_SWIGLU = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
 
-_ERR_NAMES = {-1: "S1_EINVAL", -2: "S1_ECUDA", -3: "S1_EDEVICE", -4: "S1_EKERNEL", -5: "S1_ENOMEM"}
+_ERR_NAMES = {-1: "S1_EINVAL", -2: "S1_ECUDA", -3: "S1_EDEVICE", -4: "S1_EKERNEL", -5: "S1_ENOMEM", -6: "S1_ELIMIT"}
 
 
 class S1Error(RuntimeError):
@@ -48,6 +49,8 @@ SIGNATURES = {
     "s1_set_option": (C.c_int, [C.c_void_p, C.c_char_p, C.c_longlong]),
     "s1_pack_batch": (C.c_int, [C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int32),
                                 C.POINTER(C.c_int32), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "s1_linear_static": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p,
+                                   C.c_longlong, C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_char_p, C.c_size_t]),
     "s1_delta_rule": (C.c_int, [C.c_void_p] * 7 + [C.c_int] * 5 + [C.c_void_p]),
     "s1_linear": (C.c_int, [C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                             C.c_void_p, C.c_longlong, C.c_int]),
