@@ -61,7 +61,7 @@ int s1_sync(s1_ctx* ctx);
 int s1_device_count(int* out);
 /* Number of kernels this context has launched so far. */
 long long s1_launch_count(const s1_ctx* ctx);
-/* Tuning knobs: "gemm_bn" = 0 (auto), 512 (CTA-pair 256x256 tiles), 256 or 128 (single-CTA 128xBN tiles);
+/* Tuning knobs: "gemm_bn" = 0 (auto), 512 / 384 (CTA-pair 256x256 / 256x192 tiles), 256 or 128 (single-CTA 128xBN tiles);
  * "debug" = measurement aids of the GEMM epilogue (0 in production). */
 int s1_set_option(s1_ctx* ctx, const char* name, long long value);
 

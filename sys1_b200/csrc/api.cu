@@ -71,8 +71,8 @@ extern "C" long long s1_launch_count(const s1_ctx* ctx) { return ctx ? ctx->laun
 extern "C" int s1_set_option(s1_ctx* ctx, const char* name, long long value) {
     if (!ctx || !name) return S1_EINVAL;
     if (strcmp(name, "gemm_bn") == 0) {
-        if (value != 0 && value != 128 && value != 256 && value != 512)
-            return s1_fail(ctx, S1_EINVAL, "gemm_bn must be 0, 128, 256 or 512 (got %lld)", value);
+        if (value != 0 && value != 128 && value != 256 && value != 512 && value != 384)
+            return s1_fail(ctx, S1_EINVAL, "gemm_bn must be 0, 128, 256, 384 or 512 (got %lld)", value);
         ctx->opt_gemm_bn = static_cast<int>(value);
         return S1_OK;
     }
@@ -133,7 +133,7 @@ static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0,
     auto kern = s1_gemm_kernel<BN, EPI, MODE, CTAS>;
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
-        S1_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        S1_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::smem_bytes(StoreCfg<BN, EPI, CTAS>::kStagingBytes)));
         configured_device = ctx->device;
     }
     const int tiles = p.tiles_m * p.tiles_n;
@@ -142,7 +142,7 @@ static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0,
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(gemm_threads<BN, EPI>(), 1, 1);
-    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.dynamicSmemBytes = Cfg::smem_bytes(StoreCfg<BN, EPI, CTAS>::kStagingBytes);
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -197,8 +197,18 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
     int ctas = 1, bn = 256;
     const long long pair_tiles = static_cast<long long>((T + 2 * kBM - 1) / (2 * kBM)) * n_tiles256;
     const int tiles_m1 = (T + kBM - 1) / kBM;
-    if (ctx->opt_gemm_bn == 512 || (ctx->opt_gemm_bn == 0 && pair_tiles >= ctx->sm_count / 2)) {
+    if (ctx->opt_gemm_bn == 512 || ctx->opt_gemm_bn == 384 || (ctx->opt_gemm_bn == 0 && pair_tiles >= ctx->sm_count / 2)) {
         ctas = 2;
+        // 192-wide pair tiles fill the waves of CTA pairs better for N = 768 (4 x 192 instead of 3 x 256)
+        if (epi == S1_EPI_NONE) {
+            const long long m2 = (T + 2 * kBM - 1) / (2 * kBM);
+            const long long t192 = m2 * ((n_out + 191) / 192);
+            const int pairs = ctx->sm_count / 2;
+            // (measured: no faster than 256-wide tiles on the N = 768 projections, so only on request)
+            (void)t192;
+            (void)pairs;
+            if (ctx->opt_gemm_bn == 384) bn = 192;
+        }
     } else if (ctx->opt_gemm_bn == 128 || ctx->opt_gemm_bn == 256) {
         bn = ctx->opt_gemm_bn;
     } else {
@@ -229,7 +239,8 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
     CUtensorMap ta, tb0, tb1, ty;
     int rc = s1_get_tmap(ctx, x, T, lin->K, ldx, kBM, kBK, 2, 128, &ta);
     if (rc) return rc;
-    rc = s1_get_tmap(ctx, y, T, n_out, ldy, 32, 32, 2, 64, &ty);
+    const bool wide_store = (epi == S1_EPI_NONE && bn == 256 && ctas == 2);  // StoreCfg::kWide
+    rc = s1_get_tmap(ctx, y, T, n_out, ldy, 32, wide_store ? 64 : 32, 2, wide_store ? 128 : 64, &ty);
     if (rc) return rc;
     rc = s1_get_tmap(ctx, lin->w, lin->N, lin->K, lin->ldw, bn / 2, kBK, 2, 128, &tb0);
     if (rc) return rc;
@@ -263,6 +274,15 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
             default: return launch_gemm<BN_, EPI_NONE, 3, CTAS_>(ctx, ta, tb0, tb1, ty, p);               \
         }                                                                                                \
     } while (0)
+    if (ctas == 2 && bn == 192) {
+        switch (mode) {
+            case 0: return launch_gemm<192, EPI_NONE, 0, 2>(ctx, ta, tb0, tb1, ty, p);
+            case 1: return launch_gemm<192, EPI_NONE, 1, 2>(ctx, ta, tb0, tb1, ty, p);
+            case 2: return launch_gemm<192, EPI_NONE, 2, 2>(ctx, ta, tb0, tb1, ty, p);
+            case 4: return launch_gemm<192, EPI_NONE, 4, 2>(ctx, ta, tb0, tb1, ty, p);
+            default: return launch_gemm<192, EPI_NONE, 3, 2>(ctx, ta, tb0, tb1, ty, p);
+        }
+    }
     if (ctas == 2) S1_LAUNCH(256, 2);
     if (bn == 256) S1_LAUNCH(256, 1);
     S1_LAUNCH(128, 1);

@@ -10,7 +10,7 @@
 //
 // Two shapes of the same kernel (template parameter CTAS):
 //   CTAS = 1  one CTA per SM computes a 128 x BN tile (tcgen05.mma cta_group::1, M = 128).
-//   CTAS = 2  a cluster of two CTAs (two SMs) computes a 256 x 256 tile with cta_group::2 MMAs (M = 256):
+//   CTAS = 2  a cluster of two CTAs (two SMs) computes a 256 x 256 (or 256 x 192) tile with cta_group::2 MMAs (M = 256):
 //             each CTA stages its own 128 rows of X and its own 128-row half of the W tile, so the
 //             L2 -> shared-memory traffic per SM drops by a third; the leader CTA issues the MMAs and each CTA
 //             ends up with the accumulator of its own 128 rows in its own TMEM. No TMA multicast is used:
@@ -63,17 +63,29 @@ struct EpiWarps {
 template <int BN, int EPI>
 constexpr int gemm_threads() { return 64 + 32 * EpiWarps<BN, EPI>::value; }
 
+// Width of one TMA store of the epilogue: 64 columns (128-byte rows, two staging tiles of 4 KB per warp) for the
+// plain 256-wide pair tile, whose output volume is the largest; 32 columns (64-byte rows) elsewhere.
+template <int BN, int EPI, int CTAS>
+struct StoreCfg {
+    static constexpr bool kWide = (EPI == EPI_NONE && BN == 256 && CTAS == 2);
+    static constexpr int kCols = kWide ? 64 : 32;
+    static constexpr int kTileBytes = 32 * kCols * 2;
+    static constexpr int kStagingBytes = kWide ? 64 * 1024 : 32 * 1024;  // all epilogue warps together
+};
+
 template <int BN, int CTAS>
 struct GemmCfg {
-    static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "the CTA-pair kernel is 256 x 256 only");
+    static_assert(CTAS == 1 || (CTAS == 2 && (BN == 256 || BN == 192)), "the CTA-pair kernel is 256 x 256 or 256 x 192");
     static constexpr int kABytes = kBM * kBK * 2;
     static constexpr int kBHalfBytes = (BN / 2) * kBK * 2;
     // one CTA stages both halves of the W tile; in a pair each CTA stages one
     static constexpr int kStageBytes = kABytes + (CTAS == 1 ? 2 : 1) * kBHalfBytes;
-    static constexpr int kStages = (192 * 1024) / kStageBytes;  // 4 (48 KB stages) or 6 (32 KB stages)
-    static constexpr int kTmemCols = 2 * BN;            // two accumulators; 256 or 512, powers of two
-    static constexpr int kEpiStagingBytes = 8 * 4096;   // 8 warps x two 32x32 bf16 tiles, or 16 warps x one
-    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiStagingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int kTmemCols = (2 * BN <= 256) ? 256 : 512;  // two accumulators, rounded up to a power of two
+    // 224 KB of operand ring + epilogue staging: 6 (or 4) stages beside 32 KB of staging, 5 beside 64 KB
+    static constexpr int stages(int staging_bytes) { return (224 * 1024 - staging_bytes) / kStageBytes; }
+    static constexpr int smem_bytes(int staging_bytes) {
+        return stages(staging_bytes) * kStageBytes + staging_bytes + 1024 /*align slack*/ + 256 /*barriers*/;
+    }
 };
 
 // Special-function unit forms (relative error about 2^-22, far below the bf16 rounding that follows).
@@ -137,14 +149,16 @@ __device__ __forceinline__ void fetch_residual(const GemmParams& p, int row0, in
 // and stores. `tempty_bar` is the (cluster-space) address of the barrier that hands the accumulator back.
 // MODE (plain epilogue only): bit0 = residual add, bit1 = bias and/or activation present (general path);
 // 4 = the output buffer already holds the residual: the tile is added to it by a TMA reduction.
-template <int BN, int EPI, int MODE, int EW>
+template <int BN, int EPI, int MODE, int EW, int SW, int NBUF>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap* tmY, uint32_t taddr, int row0,
                                               int col0, uint32_t stage_buf, uint32_t& nstore, uint32_t tempty_bar,
                                               int lane, const uint4* res) {
     constexpr bool PAIRED = (EPI != EPI_NONE);
     constexpr int OUT_W = PAIRED ? BN / 2 : BN;
     constexpr int CH = OUT_W / (EW * 8);  // 32-column work units per warp per tile
-    constexpr int NBUF = (EW == 8) ? 2 : 1;  // staging tiles per warp
+    constexpr int UNIT = SW / 32;             // 32-column chunks per TMA store
+    constexpr uint32_t TILE_BYTES = 32u * SW * 2u;
+    static_assert(CH % UNIT == 0, "store width must divide the warp's columns");
     static_assert(CH >= 1, "tile too narrow for this many epilogue warps");
     uint32_t va[2][32];
     uint32_t vg[PAIRED ? 2 : 1][PAIRED ? 32 : 1];
@@ -224,26 +238,37 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                 out[j] = *reinterpret_cast<uint32_t*>(&o2);
             }
         }
-        if (row0 < p.M && col < p.n_out && !(p.debug & 1)) {
-            const uint32_t buf = stage_buf + (nstore % NBUF) * 2048u;
-            ++nstore;
-            // the staging tile about to be overwritten must have been read out by its TMA store
-            if (lane == 0) tma_store_wait_read<NBUF - 1>();
-            __syncwarp();
+        const int ucol = col0 + (ci / UNIT) * SW;  // first column of the store this chunk belongs to
+        if (row0 < p.M && ucol < p.n_out && !(p.debug & 1)) {
+            const uint32_t buf = stage_buf + (nstore % NBUF) * TILE_BYTES;
+            if (ci % UNIT == 0) {
+                // the staging tile about to be overwritten must have been read out by its TMA store
+                if (lane == 0) tma_store_wait_read<NBUF - 1>();
+                __syncwarp();
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                // 64-byte rows, 64B swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
-                const uint32_t addr = buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+                uint32_t addr;
+                if constexpr (SW == 64) {
+                    // 128-byte rows, 128B swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+                    addr = buf + lane * 128 + ((((ci % UNIT) * 4 + j) ^ (lane & 7)) << 4);
+                } else {
+                    // 64-byte rows, 64B swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
+                    addr = buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+                }
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out[4 * j]),
                              "r"(out[4 * j + 1]), "r"(out[4 * j + 2]), "r"(out[4 * j + 3])
                              : "memory");
             }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                if constexpr (MODE == 4) tma_reduce_add_2d(tmY, buf, col, row0);  // y already holds the residual
-                else tma_store_2d(tmY, buf, col, row0);
-                tma_store_commit();
+            if (ci % UNIT == UNIT - 1) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (MODE == 4) tma_reduce_add_2d(tmY, buf, ucol, row0);  // y already holds the residual
+                    else tma_store_2d(tmY, buf, ucol, row0);
+                    tma_store_commit();
+                }
+                ++nstore;
             }
         }
     }
@@ -255,7 +280,8 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmY,
                const GemmParams p) {
     using Cfg = GemmCfg<BN, CTAS>;
-    constexpr int STAGES = Cfg::kStages;
+    using Store = StoreCfg<BN, EPI, CTAS>;
+    constexpr int STAGES = Cfg::stages(Store::kStagingBytes);
     constexpr bool PAIRED = (EPI != EPI_NONE);
     constexpr int OUT_W = PAIRED ? BN / 2 : BN;  // output columns per tile
     constexpr int EW = EpiWarps<BN, EPI>::value;
@@ -264,7 +290,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * Cfg::kStageBytes + Cfg::kEpiStagingBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * Cfg::kStageBytes + Store::kStagingBytes);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -401,7 +427,8 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // column half hh.
         const int q = warp & 3;
         const int hh = (warp - kEpiWarp0) >> 2;
-        const uint32_t stage_buf = smem_base + STAGES * Cfg::kStageBytes + (warp - kEpiWarp0) * (Cfg::kEpiStagingBytes / EW);
+        constexpr int NBUF = Store::kStagingBytes / (EW * Store::kTileBytes);  // staging tiles per warp
+        const uint32_t stage_buf = smem_base + STAGES * Cfg::kStageBytes + (warp - kEpiWarp0) * (Store::kStagingBytes / EW);
         uint32_t it = 0, nstore = 0;
         for (int tile = unit; tile < num_tiles; tile += num_units, ++it) {
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
@@ -426,7 +453,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 continue;
             }
             const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + hh * (CH * 32);
-            epilogue_tile<BN, EPI, MODE, EW>(p, &tmY, taddr, row0, col0, stage_buf, nstore, tempty_bar, lane, res);
+            epilogue_tile<BN, EPI, MODE, EW, Store::kCols, NBUF>(p, &tmY, taddr, row0, col0, stage_buf, nstore, tempty_bar, lane, res);
         }
         if (lane == 0) tma_store_wait<0>();  // smem reads and global writes of this warp's stores are complete
         __syncwarp();

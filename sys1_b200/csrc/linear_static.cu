@@ -55,7 +55,7 @@ int fail(char* err, size_t err_len, int code, const char* fmt, ...) {
 template <int EPI, int MODE, int CTAS>
 cudaError_t set_smem_attr() {
     return cudaFuncSetAttribute(s1_gemm_kernel<256, EPI, MODE, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                GemmCfg<256, CTAS>::kSmemBytes);
+                                GemmCfg<256, CTAS>::smem_bytes(StoreCfg<256, EPI, CTAS>::kStagingBytes));
 }
 
 // Once per device, with that device current. Not to be run for the first time under stream capture.
@@ -110,7 +110,7 @@ cudaError_t launch(const PerDevice& d, cudaStream_t stream, const CUtensorMap& a
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((tiles < units ? tiles : units) * CTAS, 1, 1);
     cfg.blockDim = dim3(gemm_threads<256, EPI>(), 1, 1);
-    cfg.dynamicSmemBytes = GemmCfg<256, CTAS>::kSmemBytes;
+    cfg.dynamicSmemBytes = GemmCfg<256, CTAS>::smem_bytes(StoreCfg<256, EPI, CTAS>::kStagingBytes);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -194,7 +194,7 @@ extern "C" int s1_linear_static(int device_ordinal, void* cuda_stream, const s1_
     }
 
     CUtensorMap ta, tb0, tb1, ty;  // on the stack, re-encoded every call: no cache, no heap
-    if (!encode_map(d, &ta, x, T, lin->K, ldx, kBM, kBK, true) || !encode_map(d, &ty, y, T, n_out, ldy, 32, 32, false) ||
+    if (!encode_map(d, &ta, x, T, lin->K, ldx, kBM, kBK, true) || !encode_map(d, &ty, y, T, n_out, ldy, 32, (epi == S1_EPI_NONE && ctas == 2) ? 64 : 32, epi == S1_EPI_NONE && ctas == 2) ||
         !encode_map(d, &tb0, lin->w, lin->N, lin->K, lin->ldw, 128, kBK, true))
         return fail(err, err_len, S1_ECUDA, "s1_linear_static: cuTensorMapEncodeTiled failed");
     tb1 = tb0;

@@ -35,7 +35,7 @@ def assert_matches_bf16_oracle(y, want, what=""):
     assert frac < 0.05, f"{what}: {frac:.4f} of the elements differ from the bf16 oracle"
 
 
-@pytest.mark.parametrize("bn", [0, 128, 256, 512])
+@pytest.mark.parametrize("bn", [0, 128, 256, 384, 512])
 def test_golden_fixtures(ctx, bn):
     ctx.set_option("gemm_bn", bn)
     try:
