@@ -140,6 +140,19 @@ int s1_delta_rule(s1_ctx* ctx, const float* q, const float* k, const float* v, c
                   float* out);
 
 /*
+ * The same recurrence in chunk form on the tensor cores (64-token chunks, bf16 operands, f32 accumulation and f32
+ * state): the form of the reference's CPU fallback (src/archs/qwen35_text.rs:809-880), which it evaluates in f32.
+ * Results agree with `s1_delta_rule` to bf16 operand precision (relative 2e-2 of the output scale is the bound the
+ * tests hold it to), not to 1e-4. key_dim = value_dim = 128 only. `cu_seqlens_host` is a HOST array here (the chunk
+ * tables are built on the host); `workspace` is device memory, 1024-byte aligned, of at least
+ * `s1_delta_rule_chunked_workspace(num_seqs, total_tokens, heads)` bytes, owned by the caller.
+ */
+size_t s1_delta_rule_chunked_workspace(int num_seqs, int total_tokens, int heads);
+int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const float* v, const float* g,
+                          const float* beta, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens, int heads,
+                          int key_dim, int value_dim, float* out, void* workspace, size_t workspace_bytes);
+
+/*
  * Packs the next sequences of a queue into one token-packed batch (host arrays, no GPU work).
  * Takes sequences in order while the running token count stays within `token_budget`; a sequence longer than
  * the budget forms a batch of its own. Writes cu_seqlens[0..num_taken] (cu_seqlens[0] = 0, last = total) and,

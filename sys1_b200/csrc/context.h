@@ -8,6 +8,7 @@
 #include <stdio.h>
 
 #include <unordered_map>
+#include <vector>
 
 #include "../../include/sys1_b200.h"
 
@@ -44,6 +45,7 @@ struct s1_ctx {
     int opt_debug = 0;
     PFN_cuTensorMapEncodeTiled encode = nullptr;
     std::unordered_map<S1TmapKey, CUtensorMap, S1TmapKeyHash> tmaps;
+    std::vector<unsigned char> host_scratch;  // host staging for small tables copied to the device
     char err[512] = {0};
 };
 

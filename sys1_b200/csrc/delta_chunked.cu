@@ -1,0 +1,648 @@
+// Chunked gated delta rule on the 5th-generation tensor cores (tcgen05 / TMEM / TMA), chunk = 64 tokens,
+// key dim = value dim = 128, bf16 operands with f32 accumulation, f32 state.
+//
+// Same function as `chunked_delta_rule` (src/archs/qwen35_text.rs:789-880), in the chunk form of its CPU
+// fallback (:809-880) with 64-token chunks instead of 32 and the triangular inverse by forward substitution
+// instead of Neumann doubling:
+//     G = cumsum(g) inside the chunk,  A_ij = beta_i (k_i . k_j) e^{G_i - G_j}  (j < i),  Tm = (I + A)^-1
+//     W = Tm (beta e^G K),  U = Tm (beta V),  P_ij = (q_i . k_j) e^{G_i - G_j}  (j <= i)
+//     V' = U - W S,   O = (Q e^G) S + P V',   S <- e^{G_last} S + (K e^{G_last - G})^T V'
+//
+// Two kernels:
+//  * s1_delta_prep_kernel  - everything that does not involve the state S, for all chunks in parallel
+//    (one CTA per pair of chunks of one head: the two chunks are stacked into M = 128 MMAs; K K^T, Q K^T and
+//    Tm [beta e^G K | beta V] run on tcgen05, the 64 x 64 triangular solves in f32 on the CUDA cores). It writes
+//    W, Q e^G, U^T, (K e^{G_last - G})^T and P as bf16 into a workspace, already in the operand layouts the second
+//    kernel feeds to the tensor cores.
+//  * s1_delta_scan_kernel  - one CTA per (sequence, head) walks the chunks in order. The state lives in f32
+//    registers (thread = value row, 128 key columns); per chunk it issues three MMAs in transposed form so that
+//    M = Dv = 128:  [V'^T | O^T] = S^T [W ; Q e^G]^T,  O^T += V'^T P^T,  dS^T = V'^T K~ ; operands arrive by TMA
+//    (two-stage ring), V'^T and the bf16 copy of S^T are rewritten in shared memory by the warps between MMAs.
+// Every mbarrier wait is bounded; a wait that runs out raises the context's status word.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "context.h"
+#include "ptx.cuh"
+
+using namespace s1;
+
+namespace {
+
+constexpr int kC = 64;     // chunk length (tokens)
+constexpr int kD = 128;    // key dim = value dim
+constexpr int kTileBytes = 128 * 64 * 2;  // one operand tile: 128 rows x 64 bf16, 128-byte swizzle
+
+struct SlotInfo {  // one chunk slot of the workspace
+    int tok_start;  // first token (row of the packed batch)
+    int len;        // valid tokens in the chunk (1..64)
+};
+struct SeqInfo {
+    int first_slot;
+    int num_chunks;
+};
+
+// Byte offset of element (row, col) inside a [rows x 64] bf16 tile with 128-byte rows and the 128B swizzle.
+__device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t col) {
+    return row * 128u + ((((col >> 3) ^ (row & 7u)) << 4) | ((col & 7u) << 1));
+}
+
+__device__ __forceinline__ void st_shared_b16(uint32_t addr, __nv_bfloat16 v) {
+    asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(*reinterpret_cast<unsigned short*>(&v)) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+}
+
+struct PrepParams {
+    const float* q;
+    const float* k;
+    const float* v;
+    const float* g;
+    const float* beta;
+    const SlotInfo* slots;
+    int num_slots, H;
+    __nv_bfloat16* wq;   // [H * slots * 128, 128]: rows 0..63 of a slot block = W, rows 64..127 = Q e^G
+    __nv_bfloat16* ut;   // [H * slots * 128 (dv), 64 (token)]
+    __nv_bfloat16* kt;   // [H * slots * 128 (dk), 64 (token)]
+    __nv_bfloat16* p;    // [H * slots * 64 (i), 64 (j)]
+    float* decay;        // [H * slots]  e^{G_last}
+    int* status;
+};
+
+constexpr int kAStride = 68;  // floats per row of the f32 A matrix in shared memory (16-byte rows, conflict-free)
+constexpr int kPrepSmem = 2 * kTileBytes /*Kop*/ + 2 * kTileBytes /*Qop*/ + 2 * 2 * kTileBytes /*XT*/ +
+                          2 * kTileBytes /*Top*/ + 128 * kAStride * 4 /*A*/ + 128 * 4 * 2 /*G, beta*/ + 1024 + 64;
+
+__global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t kop = base;                       // 2 tiles [128 rows x 64 dk]
+    const uint32_t qop = kop + 2 * kTileBytes;       // 2 tiles
+    const uint32_t xt = qop + 2 * kTileBytes;        // 2 tiles (token halves) of [256 rows (dk | dv) x 64 tokens]
+    const uint32_t top = xt + 4 * kTileBytes;        // 2 tiles [128 rows (i) x 64 (j)]
+    float* amat = reinterpret_cast<float*>(al + 10 * kTileBytes);  // [128][kAStride]
+    float* gsh = amat + 128 * kAStride;              // cumulative gate per stacked row
+    float* bsh = gsh + 128;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(bsh + 128);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int r = threadIdx.x;           // stacked token row = TMEM lane
+    const int warp = r >> 5, lane = r & 31;
+    const int half = r >> 6, i = r & 63;  // which of the two chunks, row inside it
+    const int head = blockIdx.y;
+    const int slot = 2 * blockIdx.x + half;
+    const bool slot_ok = slot < p.num_slots;
+    const SlotInfo si = slot_ok ? p.slots[slot] : SlotInfo{0, 0};
+    const bool valid = i < si.len;
+    const long long tok = si.tok_start + i;
+    const long long hs = static_cast<long long>(head) * p.num_slots + slot;  // (head, slot) block index
+
+    if (r == 0) {
+        mbar_init(smem_u32(bar), 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(tmem_slot), 256);
+        tmem_relinquish();
+    }
+
+    // ---- gates: inclusive cumulative sum inside each chunk (two warps per chunk)
+    const float gi = valid ? p.g[tok * p.H + head] : 0.f;
+    const float bi = valid ? p.beta[tok * p.H + head] : 0.f;
+    float G = gi;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, G, o);
+        if (lane >= o) G += t;
+    }
+    if (lane == 31) gsh[r] = G;  // warp total, parked in the slot of the warp's last row
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp & 1) G += gsh[r - lane - 1];  // second warp of a chunk adds the first warp's total
+    __syncthreads();
+    gsh[r] = G;
+    bsh[r] = bi;
+    __syncthreads();
+    const uint32_t tmem = *tmem_slot;
+    const float Glast = gsh[half * 64 + 63];
+    const float eG = __expf(G);
+    const float eGl = __expf(Glast - G);
+    if (slot_ok && i == 0) p.decay[hs] = __expf(Glast);
+
+    // ---- operands: K, Q as bf16 row tiles; [beta e^G K | beta V]^T as token-contiguous tiles; K~^T, Q e^G to workspace
+    const float* krow = p.k + (tok * p.H + head) * kD;
+    const float* qrow = p.q + (tok * p.H + head) * kD;
+    const float* vrow = p.v + (tok * p.H + head) * kD;
+    const uint32_t xt_tile = xt + half * (2 * kTileBytes);  // token half -> k-tile of XT (256 rows x 64 tokens)
+#pragma unroll 1
+    for (int b = 0; b < 4; ++b) {  // 32 features at a time
+        float kv[32], qv[32], vv[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 a = valid ? __ldg(reinterpret_cast<const float4*>(krow + b * 32) + c) : z;
+            const float4 q4 = valid ? __ldg(reinterpret_cast<const float4*>(qrow + b * 32) + c) : z;
+            const float4 v4 = valid ? __ldg(reinterpret_cast<const float4*>(vrow + b * 32) + c) : z;
+            kv[4 * c] = a.x, kv[4 * c + 1] = a.y, kv[4 * c + 2] = a.z, kv[4 * c + 3] = a.w;
+            qv[4 * c] = q4.x, qv[4 * c + 1] = q4.y, qv[4 * c + 2] = q4.z, qv[4 * c + 3] = q4.w;
+            vv[4 * c] = v4.x, vv[4 * c + 1] = v4.y, vv[4 * c + 2] = v4.z, vv[4 * c + 3] = v4.w;
+        }
+        const int kt = b >> 1, cbase = (b & 1) * 32;  // feature k-tile and column inside it
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t off = sw128(r, cbase + 8 * c);
+            st_shared_v4(kop + kt * kTileBytes + off, make_uint4(pack2(kv[8 * c], kv[8 * c + 1]), pack2(kv[8 * c + 2], kv[8 * c + 3]),
+                                                                pack2(kv[8 * c + 4], kv[8 * c + 5]), pack2(kv[8 * c + 6], kv[8 * c + 7])));
+            st_shared_v4(qop + kt * kTileBytes + off, make_uint4(pack2(qv[8 * c], qv[8 * c + 1]), pack2(qv[8 * c + 2], qv[8 * c + 3]),
+                                                                pack2(qv[8 * c + 4], qv[8 * c + 5]), pack2(qv[8 * c + 6], qv[8 * c + 7])));
+            if (slot_ok) {  // Q e^G, row 64 + i of the slot's WQ block
+                const uint4 qe = make_uint4(pack2(qv[8 * c] * eG, qv[8 * c + 1] * eG), pack2(qv[8 * c + 2] * eG, qv[8 * c + 3] * eG),
+                                            pack2(qv[8 * c + 4] * eG, qv[8 * c + 5] * eG), pack2(qv[8 * c + 6] * eG, qv[8 * c + 7] * eG));
+                *reinterpret_cast<uint4*>(p.wq + (hs * 128 + 64 + i) * kD + b * 32 + 8 * c) = qe;
+            }
+        }
+        const float sk = bi * eG;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+            const int f = b * 32 + e;  // feature index
+            st_shared_b16(xt_tile + sw128(f, i), __float2bfloat16_rn(kv[e] * sk));
+            st_shared_b16(xt_tile + sw128(128 + f, i), __float2bfloat16_rn(vv[e] * bi));
+            if (slot_ok) p.kt[(hs * 128 + f) * kC + i] = __float2bfloat16_rn(kv[e] * eGl);
+        }
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- K K^T -> TMEM columns 0..127, Q K^T -> 128..255 (both chunks at once; cross-chunk blocks are ignored)
+    if (r == 0) {
+        tc_fence_after();
+        constexpr uint32_t idesc = make_idesc(1, 128, 128);
+#pragma unroll
+        for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const uint64_t dk = make_sw128_kmajor_desc(kop + kt * kTileBytes) + 2u * kk;
+                const uint64_t dq = make_sw128_kmajor_desc(qop + kt * kTileBytes) + 2u * kk;
+                umma_bf16(tmem, dk, dk, idesc, (kt | kk) ? 1u : 0u);
+                umma_bf16(tmem + 128, dq, dk, idesc, (kt | kk) ? 1u : 0u);
+            }
+        umma_commit(smem_u32(bar));
+    }
+    __syncwarp();
+    bool ok = mbar_wait(smem_u32(bar), 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    if (ok) {
+        tc_fence_after();
+        // own chunk's 64 columns of row r
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            uint32_t kk[32], qk[32];
+            tmem_ld_32x32b_x32(lane_addr + half * 64 + c * 32, kk);
+            tmem_ld_32x32b_x32(lane_addr + 128 + half * 64 + c * 32, qk);
+            tmem_ld_wait();
+            uint32_t pp[16];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                const int j = c * 32 + e;
+                const float dec = __expf(G - gsh[half * 64 + j]);  // <= 1 wherever it is used (j <= i)
+                amat[r * kAStride + j] = (j < i) ? bi * __uint_as_float(kk[e]) * dec : 0.f;
+                const float pv = (j <= i) ? __uint_as_float(qk[e]) * dec : 0.f;
+                if (e & 1) pp[e >> 1] = pack2(__uint_as_float(pp[e >> 1]), pv);
+                else pp[e >> 1] = __float_as_uint(pv);
+            }
+            if (slot_ok) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    *reinterpret_cast<uint4*>(p.p + (hs * 64 + i) * kC + c * 32 + 8 * e) =
+                        make_uint4(pp[4 * e], pp[4 * e + 1], pp[4 * e + 2], pp[4 * e + 3]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    // ---- Tm = (I + A)^-1 by forward substitution, one column per thread (columns are independent)
+    {
+        float t[64];
+        const float* arow = amat + (half * 64) * kAStride;
+#pragma unroll
+        for (int ii = 0; ii < 64; ++ii) {
+            float a0 = (ii == i) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int j = 0; j + 3 < ii; j += 4) {
+                const float4 a = *reinterpret_cast<const float4*>(arow + ii * kAStride + j);
+                a0 = fmaf(-a.x, t[j], a0);
+                a1 = fmaf(-a.y, t[j + 1], a1);
+                a2 = fmaf(-a.z, t[j + 2], a2);
+                a3 = fmaf(-a.w, t[j + 3], a3);
+            }
+#pragma unroll
+            for (int j = ii & ~3; j < ii; ++j) a0 = fmaf(-arow[ii * kAStride + j], t[j], a0);
+            t[ii] = (a0 + a1) + (a2 + a3);
+        }
+        // column i of this chunk's Tm -> k-tile `half` of the block-diagonal A operand; the other chunk's rows are zero
+        const uint32_t ttile = top + half * kTileBytes;
+#pragma unroll
+        for (int ii = 0; ii < 64; ++ii) {
+            st_shared_b16(ttile + sw128(half * 64 + ii, i), __float2bfloat16_rn(t[ii]));
+            st_shared_b16(ttile + sw128((1 - half) * 64 + ii, i), __float2bfloat16_rn(0.f));
+        }
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- [W | U] = Tm [beta e^G K | beta V]  (M = 128 stacked rows, N = 256, K = 128 stacked tokens)
+    if (r == 0) {
+        tc_fence_after();
+        constexpr uint32_t idesc = make_idesc(1, 128, 256);
+#pragma unroll
+        for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+                umma_bf16(tmem, make_sw128_kmajor_desc(top + kt * kTileBytes) + 2u * kk,
+                          make_sw128_kmajor_desc(xt + kt * (2 * kTileBytes)) + 2u * kk, idesc, (kt | kk) ? 1u : 0u);
+        umma_commit(smem_u32(bar));
+    }
+    __syncwarp();
+    ok = mbar_wait(smem_u32(bar), 1, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // W row: 128 key features
+            uint32_t w[32];
+            tmem_ld_32x32b_x32(lane_addr + c * 32, w);
+            tmem_ld_wait();
+            if (slot_ok) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    *reinterpret_cast<uint4*>(p.wq + (hs * 128 + i) * kD + c * 32 + 8 * e) = make_uint4(
+                        pack2(__uint_as_float(w[8 * e]), __uint_as_float(w[8 * e + 1])), pack2(__uint_as_float(w[8 * e + 2]), __uint_as_float(w[8 * e + 3])),
+                        pack2(__uint_as_float(w[8 * e + 4]), __uint_as_float(w[8 * e + 5])), pack2(__uint_as_float(w[8 * e + 6]), __uint_as_float(w[8 * e + 7])));
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // U row -> transposed: ut[dv][token]
+            uint32_t u[32];
+            tmem_ld_32x32b_x32(lane_addr + 128 + c * 32, u);
+            tmem_ld_wait();
+            if (slot_ok) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) p.ut[(hs * 128 + c * 32 + e) * kC + i] = __float2bfloat16_rn(__uint_as_float(u[e]));
+            }
+        }
+    } else if (atomicCAS(p.status, 0, 2) == 0) {
+        p.status[1] = blockIdx.x;
+        p.status[2] = 10;
+        p.status[3] = blockIdx.y;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 256);
+    }
+}
+
+// =====================================================================================================================
+struct ScanParams {
+    const SeqInfo* seqs;
+    const SlotInfo* slots;
+    const float* decay;
+    float* out;  // [T, H, 128]
+    int num_slots, H;
+    int* status;
+};
+
+constexpr int kStageBytes = 2 * kTileBytes /*WQ*/ + kTileBytes /*UT*/ + kTileBytes /*KT*/ + kTileBytes / 2 /*P*/;  // 73728
+constexpr int kScanSmem = 2 * kStageBytes + 2 * kTileBytes /*S^T*/ + 1024 + 128;
+
+__global__ void __launch_bounds__(160, 1)
+s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_constant__ CUtensorMap tmUT,
+                     const __grid_constant__ CUtensorMap tmKT, const __grid_constant__ CUtensorMap tmP, const ScanParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sop = base + 2 * kStageBytes;  // S^T as bf16 A operand: 2 tiles [128 dv x 64 dk]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(al + 2 * kStageBytes + 2 * kTileBytes);
+    // bars: 0,1 full; 2,3 empty; 4 mma1 done; 5 V' ready; 6 mma2/3 done; 7 S ready
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t b0 = smem_u32(bars);
+    const uint32_t full0 = b0, empty0 = b0 + 16, bar_m1 = b0 + 32, bar_v = b0 + 40, bar_m2 = b0 + 48, bar_s = b0 + 56;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y;
+    const SeqInfo sq = p.seqs[blockIdx.x];
+    const int n = sq.num_chunks;
+    if (n <= 0) return;
+
+    if (threadIdx.x == 0) {
+        mbar_init(full0, 1);
+        mbar_init(full0 + 8, 1);
+        mbar_init(empty0, 1);
+        mbar_init(empty0 + 8, 1);
+        mbar_init(bar_m1, 1);
+        mbar_init(bar_v, 4);
+        mbar_init(bar_m2, 1);
+        mbar_init(bar_s, 4);
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmWQ);
+        tma_prefetch_desc(&tmUT);
+        tma_prefetch_desc(&tmKT);
+        tma_prefetch_desc(&tmP);
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(tmem_slot), 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    int fail = 0;
+
+    if (warp == 4) {
+        // ------------------------------------------------ TMA producer + MMA issuer (one thread)
+        if (lane == 0) {
+            auto load = [&](int c) {
+                const int st = c & 1;
+                const uint32_t sb = base + st * kStageBytes, fb = full0 + 8u * st;
+                const int hs = head * p.num_slots + sq.first_slot + c;
+                mbar_arrive_expect_tx(fb, kStageBytes);
+                tma_load_2d(sb, &tmWQ, 0, hs * 128, fb);
+                tma_load_2d(sb + kTileBytes, &tmWQ, 64, hs * 128, fb);
+                tma_load_2d(sb + 2 * kTileBytes, &tmUT, 0, hs * 128, fb);
+                tma_load_2d(sb + 3 * kTileBytes, &tmKT, 0, hs * 128, fb);
+                tma_load_2d(sb + 4 * kTileBytes, &tmP, 0, hs * 64, fb);
+            };
+            load(0);
+            for (int c = 0; c < n && !fail; ++c) {
+                const int st = c & 1;
+                const uint32_t sb = base + st * kStageBytes;
+                if (c + 1 < n) {
+                    if (c >= 1 && !mbar_wait(empty0 + 8u * ((c + 1) & 1), ((c - 1) >> 1) & 1, abort_flag)) { fail = 1; break; }
+                    load(c + 1);
+                }
+                if (!mbar_wait(full0 + 8u * st, (c >> 1) & 1, abort_flag)) { fail = 2; break; }
+                if (!mbar_wait(bar_s, c & 1, abort_flag)) { fail = 3; break; }
+                tc_fence_after();
+                {   // [V'^T | O^T] partial = S^T [W ; Q e^G]^T : M = 128 (dv), N = 128 (64 W rows, 64 Q rows), K = 128 (dk)
+                    constexpr uint32_t idesc = make_idesc(1, 128, 128);
+#pragma unroll
+                    for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma_bf16(tmem, make_sw128_kmajor_desc(sop + kt * kTileBytes) + 2u * kk,
+                                      make_sw128_kmajor_desc(sb + kt * kTileBytes) + 2u * kk, idesc, (kt | kk) ? 1u : 0u);
+                    umma_commit(bar_m1);
+                }
+                if (!mbar_wait(bar_v, c & 1, abort_flag)) { fail = 4; break; }
+                tc_fence_after();
+                {
+                    constexpr uint32_t idesc_p = make_idesc(1, 128, 64), idesc_k = make_idesc(1, 128, 128);
+                    const uint32_t vt = sb + 2 * kTileBytes, ktile = sb + 3 * kTileBytes, ptile = sb + 4 * kTileBytes;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)  // O^T += V'^T P^T  (K = 64 tokens j)
+                        umma_bf16(tmem + 64, make_sw128_kmajor_desc(vt) + 2u * kk, make_sw128_kmajor_desc(ptile) + 2u * kk, idesc_p, 1u);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)  // dS^T = V'^T K~
+                        umma_bf16(tmem + 128, make_sw128_kmajor_desc(vt) + 2u * kk, make_sw128_kmajor_desc(ktile) + 2u * kk, idesc_k, kk ? 1u : 0u);
+                    umma_commit(bar_m2);
+                    umma_commit(empty0 + 8u * st);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------ state / V' / output warps: thread = value row d
+        const int d = threadIdx.x;  // 0..127 = TMEM lane
+        const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        float S[kD];
+#pragma unroll
+        for (int j = 0; j < kD; ++j) S[j] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) st_shared_v4(sop + (c >> 3) * kTileBytes + sw128(d, (c & 7) * 8), make_uint4(0u, 0u, 0u, 0u));
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_s);
+
+        for (int c = 0; c < n; ++c) {
+            const int st = c & 1;
+            const uint32_t sb = base + st * kStageBytes;
+            const int slot = sq.first_slot + c;
+            const SlotInfo si = p.slots[slot];
+            const float dec = p.decay[head * p.num_slots + slot];
+            bool ok = mbar_wait(full0 + 8u * st, (c >> 1) & 1, abort_flag);
+            ok = ok && mbar_wait(bar_m1, c & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) { fail = 5; break; }
+            tc_fence_after();
+            // V'^T row: U^T row (shared memory) minus (W S)^T row (TMEM columns 0..63), back in place as bf16
+            {
+                uint32_t ws[2][32];
+                tmem_ld_32x32b_x32(lane_addr, ws[0]);
+                tmem_ld_32x32b_x32(lane_addr + 32, ws[1]);
+                tmem_ld_wait();
+                const uint32_t ut = sb + 2 * kTileBytes;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                    const uint32_t addr = ut + sw128(d, ch * 8);
+                    const uint4 u = ld_shared_v4(addr);
+                    const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(&uu[e]);
+                        const int j = ch * 8 + 2 * e;
+                        o[e] = pack2(__low2float(t) - __uint_as_float(ws[j >> 5][j & 31]), __high2float(t) - __uint_as_float(ws[(j + 1) >> 5][(j + 1) & 31]));
+                    }
+                    st_shared_v4(addr, make_uint4(o[0], o[1], o[2], o[3]));
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_v);
+
+            ok = mbar_wait(bar_m2, c & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) { fail = 6; break; }
+            tc_fence_after();
+            {   // O^T row (TMEM columns 64..127): out[token j][head][d]
+                uint32_t o[2][32];
+                tmem_ld_32x32b_x32(lane_addr + 64, o[0]);
+                tmem_ld_32x32b_x32(lane_addr + 96, o[1]);
+                tmem_ld_wait();
+                float* obase = p.out + (static_cast<long long>(si.tok_start) * p.H + head) * kD + d;
+#pragma unroll
+                for (int j = 0; j < 64; ++j)
+                    if (j < si.len) obase[static_cast<long long>(j) * p.H * kD] = __uint_as_float(o[j >> 5][j & 31]);
+            }
+            // state: S <- e^{G_last} S + dS ; refresh the bf16 operand copy
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) {
+                uint32_t ds[32];
+                tmem_ld_32x32b_x32(lane_addr + 128 + cb * 32, ds);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) S[cb * 32 + e] = fmaf(dec, S[cb * 32 + e], __uint_as_float(ds[e]));
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = cb * 32 + 8 * e;
+                    st_shared_v4(sop + (j >> 6) * kTileBytes + sw128(d, j & 63),
+                                 make_uint4(pack2(S[j], S[j + 1]), pack2(S[j + 2], S[j + 3]), pack2(S[j + 4], S[j + 5]), pack2(S[j + 6], S[j + 7])));
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_s);
+        }
+        __syncwarp();
+    }
+    if (fail && atomicCAS(p.status, 0, 3) == 0) {
+        p.status[1] = blockIdx.x;
+        p.status[2] = 20 + fail;
+        p.status[3] = blockIdx.y;
+    }
+    if (*abort_flag) __nanosleep(200000);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 256);
+    }
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct WorkspaceLayout {
+    size_t slots_off, seqs_off, decay_off, wq_off, ut_off, kt_off, p_off, total;
+};
+WorkspaceLayout layout(int num_seqs, int max_slots, int heads) {
+    WorkspaceLayout L;
+    size_t o = 0;
+    L.slots_off = o, o = align_up(o + sizeof(SlotInfo) * max_slots, 256);
+    L.seqs_off = o, o = align_up(o + sizeof(SeqInfo) * (num_seqs > 0 ? num_seqs : 1), 256);
+    L.decay_off = o, o = align_up(o + sizeof(float) * static_cast<size_t>(heads) * max_slots, 256);
+    const size_t hs = static_cast<size_t>(heads) * max_slots;
+    L.wq_off = o, o = align_up(o + hs * 128 * 128 * 2, 1024);
+    L.ut_off = o, o = align_up(o + hs * 128 * 64 * 2, 1024);
+    L.kt_off = o, o = align_up(o + hs * 128 * 64 * 2, 1024);
+    L.p_off = o, o = align_up(o + hs * 64 * 64 * 2, 1024);
+    L.total = o;
+    return L;
+}
+
+}  // namespace
+
+extern "C" size_t s1_delta_rule_chunked_workspace(int num_seqs, int total_tokens, int heads) {
+    if (num_seqs < 0 || total_tokens < 0 || heads < 1) return 0;
+    const int max_slots = total_tokens / kC + num_seqs + 1;  // every sequence may end in a partial chunk
+    return layout(num_seqs, max_slots, heads).total;
+}
+
+extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const float* v, const float* g,
+                                     const float* beta, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens,
+                                     int heads, int key_dim, int value_dim, float* out, void* workspace,
+                                     size_t workspace_bytes) {
+    if (!ctx) return S1_EINVAL;
+    if (!q || !k || !v || !g || !beta || !cu_seqlens_host || !out || !workspace)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: null pointer");
+    if (key_dim != kD || value_dim != kD)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: key_dim and value_dim must be 128 (got %d, %d); use s1_delta_rule", key_dim, value_dim);
+    if (num_seqs < 0 || heads < 1 || total_tokens < 0) return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: bad sizes");
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+         reinterpret_cast<uintptr_t>(workspace)) & 15u)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: q, k, v and the workspace must be 16-byte aligned");
+    if (num_seqs == 0 || total_tokens == 0) return S1_OK;
+    if (cu_seqlens_host[0] != 0 || cu_seqlens_host[num_seqs] != total_tokens)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: cu_seqlens must run from 0 to total_tokens");
+    const int max_slots = total_tokens / kC + num_seqs + 1;
+    const WorkspaceLayout L = layout(num_seqs, max_slots, heads);
+    if (workspace_bytes < L.total)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: workspace of %zu bytes, %zu needed", workspace_bytes, L.total);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: the workspace must be 1024-byte aligned");
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+
+    // chunk tables, built on the host from the host copy of the offsets
+    ctx->host_scratch.resize(sizeof(SlotInfo) * max_slots + sizeof(SeqInfo) * num_seqs);
+    SlotInfo* slots = reinterpret_cast<SlotInfo*>(ctx->host_scratch.data());
+    SeqInfo* seqs = reinterpret_cast<SeqInfo*>(ctx->host_scratch.data() + sizeof(SlotInfo) * max_slots);
+    int num_slots = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+        const int a = cu_seqlens_host[s], b = cu_seqlens_host[s + 1];
+        if (b < a) return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: cu_seqlens must not decrease");
+        seqs[s].first_slot = num_slots;
+        seqs[s].num_chunks = (b - a + kC - 1) / kC;
+        for (int t = a; t < b; t += kC) slots[num_slots++] = SlotInfo{t, (b - t < kC) ? b - t : kC};
+    }
+    if (num_slots == 0) return S1_OK;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.slots_off, slots, sizeof(SlotInfo) * num_slots, cudaMemcpyHostToDevice, ctx->stream));
+    S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.seqs_off, seqs, sizeof(SeqInfo) * num_seqs, cudaMemcpyHostToDevice, ctx->stream));
+    // the tables are read by the kernels after these copies on the same stream; the host buffer is reused by the
+    // next call only after the copies were issued from pageable memory (which stages them before returning)
+
+    PrepParams pp;
+    pp.q = q, pp.k = k, pp.v = v, pp.g = g, pp.beta = beta;
+    pp.slots = reinterpret_cast<const SlotInfo*>(ws + L.slots_off);
+    pp.num_slots = num_slots, pp.H = heads;
+    pp.wq = reinterpret_cast<__nv_bfloat16*>(ws + L.wq_off);
+    pp.ut = reinterpret_cast<__nv_bfloat16*>(ws + L.ut_off);
+    pp.kt = reinterpret_cast<__nv_bfloat16*>(ws + L.kt_off);
+    pp.p = reinterpret_cast<__nv_bfloat16*>(ws + L.p_off);
+    pp.decay = reinterpret_cast<float*>(ws + L.decay_off);
+    pp.status = ctx->status_dev;
+    static thread_local int configured_device = -1;
+    if (configured_device != ctx->device) {
+        S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem));
+        S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmem));
+        configured_device = ctx->device;
+    }
+    s1_delta_prep_kernel<<<dim3((num_slots + 1) / 2, heads), 128, kPrepSmem, ctx->stream>>>(pp);
+    S1_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+
+    const long long hs_rows = static_cast<long long>(heads) * num_slots;
+    CUtensorMap tWQ, tUT, tKT, tP;
+    int rc = s1_get_tmap(ctx, pp.wq, hs_rows * 128, 128, 128, 128, 64, 2, 128, &tWQ);
+    if (rc) return rc;
+    rc = s1_get_tmap(ctx, pp.ut, hs_rows * 128, 64, 64, 128, 64, 2, 128, &tUT);
+    if (rc) return rc;
+    rc = s1_get_tmap(ctx, pp.kt, hs_rows * 128, 64, 64, 128, 64, 2, 128, &tKT);
+    if (rc) return rc;
+    rc = s1_get_tmap(ctx, pp.p, hs_rows * 64, 64, 64, 64, 64, 2, 128, &tP);
+    if (rc) return rc;
+    ScanParams sp;
+    sp.seqs = reinterpret_cast<const SeqInfo*>(ws + L.seqs_off);
+    sp.slots = pp.slots;
+    sp.decay = pp.decay;
+    sp.out = out;
+    sp.num_slots = num_slots, sp.H = heads;
+    sp.status = ctx->status_dev;
+    s1_delta_scan_kernel<<<dim3(num_seqs, heads), 160, kScanSmem, ctx->stream>>>(tWQ, tUT, tKT, tP, sp);
+    S1_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return S1_OK;
+}

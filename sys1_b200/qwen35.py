@@ -31,10 +31,51 @@ class Mlp:
     __call__ = forward
 
 
+_workspaces = {}
+
+
+def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """Device scratch for the chunked kernels, grown on demand and kept per device (the library itself never
+    allocates; a Rust caller would hand it a buffer from candle's pool the same way)."""
+    ws = _workspaces.get(dev)
+    if ws is None or ws.numel() < nbytes + 1024:
+        ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
+        _workspaces[dev] = ws
+    return ws
+
+
+def delta_rule_chunked_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                              cu_seqlens_host, ctx: Optional[device.Context] = None) -> torch.Tensor:
+    """The recurrence in 64-token chunks on the tensor cores (`s1_delta_rule_chunked`): bf16 operand precision,
+    f32 state; q, k, v `[T, H, 128]`. `cu_seqlens_host`: int32 offsets on the HOST (numpy array or CPU tensor)."""
+    import numpy as np
+    for name, t in (("q", q), ("k", k), ("v", v), ("g", g), ("beta", beta)):
+        if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous f32 CUDA tensor (no CPU fallback)")
+    cu = np.ascontiguousarray(cu_seqlens_host.cpu().numpy() if isinstance(cu_seqlens_host, torch.Tensor) else cu_seqlens_host,
+                              dtype=np.int32)
+    T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    out = torch.empty((T, H, Dv), dtype=torch.float32, device=q.device)
+    if T == 0:
+        return out
+    if ctx is None:
+        ctx = device.load(q.device.index)
+    nseq = int(cu.shape[0] - 1)
+    need = int(ctx._lib.s1_delta_rule_chunked_workspace(nseq, T, H))
+    ws = _workspace(q.device, need)
+    ptr = (ws.data_ptr() + 1023) // 1024 * 1024
+    rc = ctx._lib.s1_delta_rule_chunked(ctx.handle, *(C.c_void_p(t.data_ptr()) for t in (q, k, v, g, beta)),
+                                        cu.ctypes.data_as(C.POINTER(C.c_int32)), nseq, T, H, Dk, Dv,
+                                        C.c_void_p(out.data_ptr()), C.c_void_p(ptr), need)
+    ctx.check(rc)
+    return out
+
+
 def delta_rule_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
                       cu_seqlens: torch.Tensor, ctx: Optional[device.Context] = None) -> torch.Tensor:
-    """Gated delta rule on the packed layout: q, k `[T, H, 128]`, v `[T, H, Dv]`, g, beta `[T, H]` (f32, CUDA,
-    contiguous), cu_seqlens int32 `[B+1]` on the same device. Returns `[T, H, Dv]` f32."""
+    """Gated delta rule on the packed layout, exact f32 token-by-token form: q, k `[T, H, 128]`, v `[T, H, Dv]`,
+    g, beta `[T, H]` (f32, CUDA, contiguous), cu_seqlens int32 `[B+1]` on the same device. Returns `[T, H, Dv]`."""
     for name, t in (("q", q), ("k", k), ("v", v), ("g", g), ("beta", beta)):
         if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
             raise ValueError(f"{name} must be a contiguous f32 CUDA tensor (no CPU fallback)")

@@ -98,3 +98,73 @@ def test_argument_errors(ctx):
     with pytest.raises(Exception, match="key_dim"):
         qwen35.delta_rule_packed(f, f, f, f[..., 0].contiguous(), f[..., 0].contiguous(),
                                  torch.tensor([0, 4], dtype=torch.int32, device=DEV))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# chunked tensor-core form (`s1_delta_rule_chunked`): bf16 operand precision, bound 2e-2 of the output scale
+def _oracle_packed(q, k, v, gate, beta, cu):
+    out = torch.empty_like(v)
+    for s in range(len(cu) - 1):
+        a, b = int(cu[s]), int(cu[s + 1])
+        if a == b:
+            continue
+        tr = lambda t: t[a:b].transpose(0, 1).unsqueeze(0).contiguous()
+        out[a:b] = oracle.sequential_delta_rule(tr(q), tr(k), tr(v), gate[a:b].t().unsqueeze(0).contiguous(),
+                                                beta[a:b].t().unsqueeze(0).contiguous())[0]
+    return out
+
+
+@pytest.mark.parametrize("lens,H", [([64], 1), ([5], 1), ([128], 2), ([70, 1, 33, 130, 64, 200], 2), ([0, 1000, 0, 24], 3)])
+def test_chunked_matches_the_oracle(ctx, lens, H):
+    import numpy as np
+    cu = np.cumsum([0] + lens).astype(np.int32)
+    q, k, v, gate, beta = _random_inputs(int(cu[-1]), H, 128, 7 * len(lens) + H)
+    want = _oracle_packed(q, k, v, gate, beta, cu)
+    got = qwen35.delta_rule_chunked_packed(*(t.to(DEV) for t in (q, k, v, gate, beta)), cu).cpu()
+    ctx.sync()
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+
+
+def test_chunked_golden_needs_dv_128(ctx):
+    d = load_delta_rule()  # the fixture has Dv = 32: the chunked form refuses it, the exact form takes it
+    with pytest.raises(Exception, match="128"):
+        qwen35.delta_rule_chunked_packed(*(d[n].to(DEV) for n in ("q", "k", "v", "g", "beta")), d["cu_seqlens"])
+
+
+def test_chunked_large_negative_gates_and_reference_inputs(ctx):
+    import numpy as np
+    # finiteness with g = -8 (src/archs/qwen35_text.rs:1441-1462)
+    one = torch.ones(64, 1, 128, device=DEV)
+    out = qwen35.delta_rule_chunked_packed(one, one, one, torch.full((64, 1), -8.0, device=DEV),
+                                           torch.full((64, 1), 0.5, device=DEV), np.array([0, 64], dtype=np.int32))
+    assert torch.isfinite(out).all()
+    # closed-form inputs of the reference's kernel test, widened to Dv = 128 (:1320-1389)
+    L, H = 290, 2
+    q = _closed_form(L * H, 128, 0.001).reshape(L, H, 128)
+    k = _closed_form(L * H, 128, 0.006).reshape(L, H, 128)
+    v = _closed_form(L * H, 128, 0.008).reshape(L, H, 128)
+    g = torch.full((L, H), -0.002)
+    beta = torch.full((L, H), 0.5)
+    cu = np.array([0, L], dtype=np.int32)
+    want = _oracle_packed(q, k, v, g, beta, cu)
+    got = qwen35.delta_rule_chunked_packed(*(t.to(DEV) for t in (q, k, v, g, beta)), cu).cpu()
+    assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+
+
+def test_chunked_full_budget_agrees_with_the_exact_kernel(ctx):
+    from sys1_b200 import batching
+    import numpy as np
+    lens = batching.synthetic_lengths(1004, 64, 2048, 16384)
+    cu = np.concatenate([[0], lens.cumsum()]).astype(np.int32)
+    q, k, v, gate, beta = (t.to(DEV) for t in _random_inputs(16384, 16, 128, 1004))
+    exact = qwen35.delta_rule_packed(q, k, v, gate, beta, torch.tensor(cu, device=DEV))
+    chunked = qwen35.delta_rule_chunked_packed(q, k, v, gate, beta, cu)
+    ctx.sync()
+    assert (chunked - exact).abs().max() <= 2e-2 * exact.abs().max()
+    # a sequence run alone gives the same rows (chunk boundaries are per sequence)
+    s = 3
+    a, b = int(cu[s]), int(cu[s + 1])
+    alone = qwen35.delta_rule_chunked_packed(q[a:b].contiguous(), k[a:b].contiguous(), v[a:b].contiguous(),
+                                             gate[a:b].contiguous(), beta[a:b].contiguous(), np.array([0, b - a], dtype=np.int32))
+    assert torch.equal(alone, chunked[a:b])
