@@ -12,7 +12,7 @@
 //  * s1_delta_prep_kernel  - everything that does not involve the state S, for all chunks in parallel
 //    (one CTA per pair of chunks of one head: the two chunks are stacked into M = 128 MMAs; K K^T, Q K^T and
 //    Tm [beta e^G K | beta V] run on tcgen05, the 64 x 64 triangular solves in f32 on the CUDA cores). It writes
-//    W, Q e^G, U^T, (K e^{G_last - G})^T and P as bf16 into a workspace, already in the operand layouts the second
+//    W, Q e^G, U^T, K e^{G_last - G} and P as bf16 into a workspace, already in the operand layouts the second
 //    kernel feeds to the tensor cores.
 //  * s1_delta_scan_kernel  - one CTA per (sequence, head) walks the chunks in order. The state lives in f32
 //    registers (thread = value row, 128 key columns); per chunk it issues three MMAs in transposed form so that
@@ -22,6 +22,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <algorithm>
 
 #include "context.h"
 #include "ptx.cuh"
@@ -48,6 +50,23 @@ __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t col) {
     return row * 128u + ((((col >> 3) ^ (row & 7u)) << 4) | ((col & 7u) << 1));
 }
 
+// Shared-memory descriptor of an MN-major bf16 operand stored as tiles of [K rows x 64 MN elements] (128-byte rows,
+// 128B swizzle): 8 K-rows form a 1024-byte swizzle atom (SBO = 1024, the K direction), the next 64 MN elements
+// are `tile_stride` bytes further (LBO). An MMA consumes 16 K-rows: advance the address by 2048 bytes (+128 here).
+__device__ __forceinline__ uint64_t make_sw128_mnmajor_desc(uint32_t smem_addr, uint32_t tile_stride) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((tile_stride >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+constexpr uint32_t kBMnMajor = 1u << 16;  // instruction-descriptor bit: B operand is MN-major
+
+__device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
 __device__ __forceinline__ void st_shared_b16(uint32_t addr, __nv_bfloat16 v) {
     asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(*reinterpret_cast<unsigned short*>(&v)) : "memory");
 }
@@ -74,7 +93,7 @@ struct PrepParams {
     int num_slots, H;
     __nv_bfloat16* wq;   // [H * slots * 128, 128]: rows 0..63 of a slot block = W, rows 64..127 = Q e^G
     __nv_bfloat16* ut;   // [H * slots * 128 (dv), 64 (token)]
-    __nv_bfloat16* kt;   // [H * slots * 128 (dk), 64 (token)]
+    __nv_bfloat16* kn;   // [H * slots * 64 (token), 128 (dk)]: K e^{G_last - G}
     __nv_bfloat16* p;    // [H * slots * 64 (i), 64 (j)]
     float* decay;        // [H * slots]  e^{G_last}
     int* status;
@@ -82,25 +101,31 @@ struct PrepParams {
 
 constexpr int kAStride = 68;  // floats per row of the f32 A matrix in shared memory (16-byte rows, conflict-free)
 constexpr int kPrepSmem = 2 * kTileBytes /*Kop*/ + 2 * kTileBytes /*Qop*/ + 2 * 2 * kTileBytes /*XT*/ +
-                          2 * kTileBytes /*Top*/ + 128 * kAStride * 4 /*A*/ + 128 * 4 * 2 /*G, beta*/ + 1024 + 64;
+                          2 * kTileBytes /*Top*/ + 128 * kAStride * 4 /*A*/ + 128 * 4 * 4 /*G, beta, e^G, e^(Glast-G)*/ + 1024 + 64;
 
-__global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams p) {
+constexpr int kPrepThreads = 256;  // two threads per stacked token row: each owns one half of the features / columns
+
+__global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const PrepParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t kop = base;                       // 2 tiles [128 rows x 64 dk]
     const uint32_t qop = kop + 2 * kTileBytes;       // 2 tiles
-    const uint32_t xt = qop + 2 * kTileBytes;        // 2 tiles (token halves) of [256 rows (dk | dv) x 64 tokens]
+    const uint32_t xt = qop + 2 * kTileBytes;        // 4 tiles [128 tokens x 64 features]: beta e^G K (2), beta V (2)
     const uint32_t top = xt + 4 * kTileBytes;        // 2 tiles [128 rows (i) x 64 (j)]
     float* amat = reinterpret_cast<float*>(al + 10 * kTileBytes);  // [128][kAStride]
     float* gsh = amat + 128 * kAStride;              // cumulative gate per stacked row
     float* bsh = gsh + 128;
-    uint64_t* bar = reinterpret_cast<uint64_t*>(bsh + 128);
+    float* egs = bsh + 128;   // e^G per stacked row
+    float* egl = egs + 128;   // e^{G_last - G}
+    uint64_t* bar = reinterpret_cast<uint64_t*>(egl + 128);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int r = threadIdx.x;           // stacked token row = TMEM lane
-    const int warp = r >> 5, lane = r & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q4 = warp & 3;             // TMEM lane quarter of this warp
+    const int fh = warp >> 2;            // which half of the features / of the chunk's columns this thread handles
+    const int r = q4 * 32 + lane;        // stacked token row = TMEM lane
     const int half = r >> 6, i = r & 63;  // which of the two chunks, row inside it
     const int head = blockIdx.y;
     const int slot = 2 * blockIdx.x + half;
@@ -110,7 +135,7 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
     const long long tok = si.tok_start + i;
     const long long hs = static_cast<long long>(head) * p.num_slots + slot;  // (head, slot) block index
 
-    if (r == 0) {
+    if (threadIdx.x == 0) {
         mbar_init(smem_u32(bar), 1);
         *abort_flag = 0;
         fence_mbar_init();
@@ -133,7 +158,7 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp & 1) G += gsh[r - lane - 1];  // second warp of a chunk adds the first warp's total
+    if (q4 & 1) G += gsh[r - lane - 1];  // second warp of a chunk adds the first warp's total
     __syncthreads();
     gsh[r] = G;
     bsh[r] = bi;
@@ -142,47 +167,52 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
     const float Glast = gsh[half * 64 + 63];
     const float eG = __expf(G);
     const float eGl = __expf(Glast - G);
-    if (slot_ok && i == 0) p.decay[hs] = __expf(Glast);
+    if (slot_ok && i == 0 && fh == 0) p.decay[hs] = __expf(Glast);
 
-    // ---- operands: K, Q as bf16 row tiles; [beta e^G K | beta V]^T as token-contiguous tiles; K~^T, Q e^G to workspace
-    const float* krow = p.k + (tok * p.H + head) * kD;
-    const float* qrow = p.q + (tok * p.H + head) * kD;
-    const float* vrow = p.v + (tok * p.H + head) * kD;
-    const uint32_t xt_tile = xt + half * (2 * kTileBytes);  // token half -> k-tile of XT (256 rows x 64 tokens)
+    // ---- operands, one warp per row at a time (coalesced 512-byte rows, lane = 4 consecutive features):
+    //      K, Q, beta e^G K, beta V as bf16 [token x feature] tiles; Q e^G and K e^{G_last - G} to the workspace
+    if (fh == 0) {
+        egs[r] = eG;
+        egl[r] = eGl;
+    }
+    __syncthreads();
+    {
+        const SlotInfo s0 = p.slots[min(2 * static_cast<int>(blockIdx.x), p.num_slots - 1)];
+        const SlotInfo s1 = (2 * blockIdx.x + 1 < p.num_slots) ? p.slots[2 * blockIdx.x + 1] : SlotInfo{0, 0};
+        const int tile = lane >> 4, col = (4 * lane) & 63;
 #pragma unroll 1
-    for (int b = 0; b < 4; ++b) {  // 32 features at a time
-        float kv[32], qv[32], vv[32];
+        for (int rr = 0; rr < 16; rr += 4) {
+            float4 kk[4], qq[4], vv[4];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float4 a = valid ? __ldg(reinterpret_cast<const float4*>(krow + b * 32) + c) : z;
-            const float4 q4 = valid ? __ldg(reinterpret_cast<const float4*>(qrow + b * 32) + c) : z;
-            const float4 v4 = valid ? __ldg(reinterpret_cast<const float4*>(vrow + b * 32) + c) : z;
-            kv[4 * c] = a.x, kv[4 * c + 1] = a.y, kv[4 * c + 2] = a.z, kv[4 * c + 3] = a.w;
-            qv[4 * c] = q4.x, qv[4 * c + 1] = q4.y, qv[4 * c + 2] = q4.z, qv[4 * c + 3] = q4.w;
-            vv[4 * c] = v4.x, vv[4 * c + 1] = v4.y, vv[4 * c + 2] = v4.z, vv[4 * c + 3] = v4.w;
-        }
-        const int kt = b >> 1, cbase = (b & 1) * 32;  // feature k-tile and column inside it
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const uint32_t off = sw128(r, cbase + 8 * c);
-            st_shared_v4(kop + kt * kTileBytes + off, make_uint4(pack2(kv[8 * c], kv[8 * c + 1]), pack2(kv[8 * c + 2], kv[8 * c + 3]),
-                                                                pack2(kv[8 * c + 4], kv[8 * c + 5]), pack2(kv[8 * c + 6], kv[8 * c + 7])));
-            st_shared_v4(qop + kt * kTileBytes + off, make_uint4(pack2(qv[8 * c], qv[8 * c + 1]), pack2(qv[8 * c + 2], qv[8 * c + 3]),
-                                                                pack2(qv[8 * c + 4], qv[8 * c + 5]), pack2(qv[8 * c + 6], qv[8 * c + 7])));
-            if (slot_ok) {  // Q e^G, row 64 + i of the slot's WQ block
-                const uint4 qe = make_uint4(pack2(qv[8 * c] * eG, qv[8 * c + 1] * eG), pack2(qv[8 * c + 2] * eG, qv[8 * c + 3] * eG),
-                                            pack2(qv[8 * c + 4] * eG, qv[8 * c + 5] * eG), pack2(qv[8 * c + 6] * eG, qv[8 * c + 7] * eG));
-                *reinterpret_cast<uint4*>(p.wq + (hs * 128 + 64 + i) * kD + b * 32 + 8 * c) = qe;
+            for (int u = 0; u < 4; ++u) {
+                const int row = warp * 16 + rr + u, ri = row & 63;
+                const SlotInfo sr = (row >> 6) ? s1 : s0;
+                const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                const long long base_f = (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane;
+                const bool rv = ri < sr.len;
+                kk[u] = rv ? __ldg(reinterpret_cast<const float4*>(p.k + base_f)) : z;
+                qq[u] = rv ? __ldg(reinterpret_cast<const float4*>(p.q + base_f)) : z;
+                vv[u] = rv ? __ldg(reinterpret_cast<const float4*>(p.v + base_f)) : z;
             }
-        }
-        const float sk = bi * eG;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-            const int f = b * 32 + e;  // feature index
-            st_shared_b16(xt_tile + sw128(f, i), __float2bfloat16_rn(kv[e] * sk));
-            st_shared_b16(xt_tile + sw128(128 + f, i), __float2bfloat16_rn(vv[e] * bi));
-            if (slot_ok) p.kt[(hs * 128 + f) * kC + i] = __float2bfloat16_rn(kv[e] * eGl);
+            for (int u = 0; u < 4; ++u) {
+                const int row = warp * 16 + rr + u, ri = row & 63;
+                const int rslot = 2 * blockIdx.x + (row >> 6);
+                const float be = bsh[row], eg = egs[row], el = egl[row];
+                const float sk = be * eg;
+                const uint32_t off = tile * kTileBytes + sw128(row, col);
+                st_shared_v2(kop + off, pack2(kk[u].x, kk[u].y), pack2(kk[u].z, kk[u].w));
+                st_shared_v2(qop + off, pack2(qq[u].x, qq[u].y), pack2(qq[u].z, qq[u].w));
+                st_shared_v2(xt + off, pack2(kk[u].x * sk, kk[u].y * sk), pack2(kk[u].z * sk, kk[u].w * sk));
+                st_shared_v2(xt + 2 * kTileBytes + off, pack2(vv[u].x * be, vv[u].y * be), pack2(vv[u].z * be, vv[u].w * be));
+                if (rslot < p.num_slots) {
+                    const long long hsr = static_cast<long long>(head) * p.num_slots + rslot;
+                    *reinterpret_cast<uint2*>(p.wq + (hsr * 128 + 64 + ri) * kD + 4 * lane) =
+                        make_uint2(pack2(qq[u].x * eg, qq[u].y * eg), pack2(qq[u].z * eg, qq[u].w * eg));
+                    *reinterpret_cast<uint2*>(p.kn + (hsr * 64 + ri) * kD + 4 * lane) =
+                        make_uint2(pack2(kk[u].x * el, kk[u].y * el), pack2(kk[u].z * el, kk[u].w * el));
+                }
+            }
         }
     }
     fence_proxy_async_smem();
@@ -190,7 +220,7 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
     __syncthreads();
 
     // ---- K K^T -> TMEM columns 0..127, Q K^T -> 128..255 (both chunks at once; cross-chunk blocks are ignored)
-    if (r == 0) {
+    if (threadIdx.x == 0) {
         tc_fence_after();
         constexpr uint32_t idesc = make_idesc(1, 128, 128);
 #pragma unroll
@@ -207,12 +237,12 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
     __syncwarp();
     bool ok = mbar_wait(smem_u32(bar), 0, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
-    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
     if (ok) {
         tc_fence_after();
-        // own chunk's 64 columns of row r
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        // this thread's 32 of the own chunk's 64 columns of row r
+        {
+            const int c = fh;
             uint32_t kk[32], qk[32];
             tmem_ld_32x32b_x32(lane_addr + half * 64 + c * 32, kk);
             tmem_ld_32x32b_x32(lane_addr + 128 + half * 64 + c * 32, qk);
@@ -239,8 +269,13 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
     __syncthreads();
     tc_fence_after();
 
-    // ---- Tm = (I + A)^-1 by forward substitution, one column per thread (columns are independent)
-    {
+    // ---- Tm = (I + A)^-1 by forward substitution, one column per thread (columns are independent); the second
+    //      thread of each row fills the zero blocks of the block-diagonal operand meanwhile
+    if (fh == 1) {
+        const uint32_t ttile = top + half * kTileBytes;
+#pragma unroll
+        for (int ii = 0; ii < 64; ++ii) st_shared_b16(ttile + sw128((1 - half) * 64 + ii, i), __float2bfloat16_rn(0.f));
+    } else {
         float t[64];
         const float* arow = amat + (half * 64) * kAStride;
 #pragma unroll
@@ -258,12 +293,11 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
             for (int j = ii & ~3; j < ii; ++j) a0 = fmaf(-arow[ii * kAStride + j], t[j], a0);
             t[ii] = (a0 + a1) + (a2 + a3);
         }
-        // column i of this chunk's Tm -> k-tile `half` of the block-diagonal A operand; the other chunk's rows are zero
+        // column i of this chunk's Tm -> k-tile `half` of the block-diagonal A operand
         const uint32_t ttile = top + half * kTileBytes;
 #pragma unroll
         for (int ii = 0; ii < 64; ++ii) {
             st_shared_b16(ttile + sw128(half * 64 + ii, i), __float2bfloat16_rn(t[ii]));
-            st_shared_b16(ttile + sw128((1 - half) * 64 + ii, i), __float2bfloat16_rn(0.f));
         }
     }
     fence_proxy_async_smem();
@@ -271,15 +305,17 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
     __syncthreads();
 
     // ---- [W | U] = Tm [beta e^G K | beta V]  (M = 128 stacked rows, N = 256, K = 128 stacked tokens)
-    if (r == 0) {
+    if (threadIdx.x == 0) {
         tc_fence_after();
-        constexpr uint32_t idesc = make_idesc(1, 128, 256);
+        // A = Tm (K-major: rows i, 64 j per tile); B = [beta e^G K | beta V] as stored, token rows x features (MN-major)
+        constexpr uint32_t idesc = make_idesc(1, 128, 256) | kBMnMajor;
+        const uint64_t bdesc = make_sw128_mnmajor_desc(xt, kTileBytes);
 #pragma unroll
         for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
-                umma_bf16(tmem, make_sw128_kmajor_desc(top + kt * kTileBytes) + 2u * kk,
-                          make_sw128_kmajor_desc(xt + kt * (2 * kTileBytes)) + 2u * kk, idesc, (kt | kk) ? 1u : 0u);
+                umma_bf16(tmem, make_sw128_kmajor_desc(top + kt * kTileBytes) + 2u * kk, bdesc + 128u * (kt * 4 + kk), idesc,
+                          (kt | kk) ? 1u : 0u);
         umma_commit(smem_u32(bar));
     }
     __syncwarp();
@@ -288,7 +324,7 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
     if (ok) {
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {  // W row: 128 key features
+        for (int c = 2 * fh; c < 2 * fh + 2; ++c) {  // W row: this thread's 64 of the 128 key features
             uint32_t w[32];
             tmem_ld_32x32b_x32(lane_addr + c * 32, w);
             tmem_ld_wait();
@@ -301,7 +337,7 @@ __global__ void __launch_bounds__(128, 1) s1_delta_prep_kernel(const PrepParams 
             }
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {  // U row -> transposed: ut[dv][token]
+        for (int c = 2 * fh; c < 2 * fh + 2; ++c) {  // U row -> transposed: ut[dv][token]
             uint32_t u[32];
             tmem_ld_32x32b_x32(lane_addr + 128 + c * 32, u);
             tmem_ld_wait();
@@ -333,12 +369,12 @@ struct ScanParams {
     int* status;
 };
 
-constexpr int kStageBytes = 2 * kTileBytes /*WQ*/ + kTileBytes /*UT*/ + kTileBytes /*KT*/ + kTileBytes / 2 /*P*/;  // 73728
+constexpr int kStageBytes = 2 * kTileBytes /*WQ*/ + kTileBytes /*UT*/ + kTileBytes /*K~*/ + kTileBytes / 2 /*P*/;  // 73728
 constexpr int kScanSmem = 2 * kStageBytes + 2 * kTileBytes /*S^T*/ + 1024 + 128;
 
 __global__ void __launch_bounds__(160, 1)
 s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_constant__ CUtensorMap tmUT,
-                     const __grid_constant__ CUtensorMap tmKT, const __grid_constant__ CUtensorMap tmP, const ScanParams p) {
+                     const __grid_constant__ CUtensorMap tmKN, const __grid_constant__ CUtensorMap tmP, const ScanParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
@@ -369,7 +405,7 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
         fence_mbar_init();
         tma_prefetch_desc(&tmWQ);
         tma_prefetch_desc(&tmUT);
-        tma_prefetch_desc(&tmKT);
+        tma_prefetch_desc(&tmKN);
         tma_prefetch_desc(&tmP);
     }
     if (warp == 4) {
@@ -393,7 +429,8 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
                 tma_load_2d(sb, &tmWQ, 0, hs * 128, fb);
                 tma_load_2d(sb + kTileBytes, &tmWQ, 64, hs * 128, fb);
                 tma_load_2d(sb + 2 * kTileBytes, &tmUT, 0, hs * 128, fb);
-                tma_load_2d(sb + 3 * kTileBytes, &tmKT, 0, hs * 128, fb);
+                tma_load_2d(sb + 3 * kTileBytes, &tmKN, 0, hs * 64, fb);               // dk 0..63  of 64 tokens (8 KB)
+                tma_load_2d(sb + 3 * kTileBytes + kTileBytes / 2, &tmKN, 64, hs * 64, fb);  // dk 64..127
                 tma_load_2d(sb + 4 * kTileBytes, &tmP, 0, hs * 64, fb);
             };
             load(0);
@@ -420,14 +457,15 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
                 if (!mbar_wait(bar_v, c & 1, abort_flag)) { fail = 4; break; }
                 tc_fence_after();
                 {
-                    constexpr uint32_t idesc_p = make_idesc(1, 128, 64), idesc_k = make_idesc(1, 128, 128);
+                    constexpr uint32_t idesc_p = make_idesc(1, 128, 64), idesc_k = make_idesc(1, 128, 128) | kBMnMajor;
                     const uint32_t vt = sb + 2 * kTileBytes, ktile = sb + 3 * kTileBytes, ptile = sb + 4 * kTileBytes;
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)  // O^T += V'^T P^T  (K = 64 tokens j)
                         umma_bf16(tmem + 64, make_sw128_kmajor_desc(vt) + 2u * kk, make_sw128_kmajor_desc(ptile) + 2u * kk, idesc_p, 1u);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)  // dS^T = V'^T K~
-                        umma_bf16(tmem + 128, make_sw128_kmajor_desc(vt) + 2u * kk, make_sw128_kmajor_desc(ktile) + 2u * kk, idesc_k, kk ? 1u : 0u);
+                    for (int kk = 0; kk < 4; ++kk)  // dS^T = V'^T K~ ; K~ as stored: token rows x dk (MN-major B, two 8 KB tiles)
+                        umma_bf16(tmem + 128, make_sw128_kmajor_desc(vt) + 2u * kk,
+                                  make_sw128_mnmajor_desc(ktile, kTileBytes / 2) + 128u * kk, idesc_k, kk ? 1u : 0u);
                     umma_commit(bar_m2);
                     umma_commit(empty0 + 8u * st);
                 }
@@ -536,7 +574,7 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-    size_t slots_off, seqs_off, decay_off, wq_off, ut_off, kt_off, p_off, total;
+    size_t slots_off, seqs_off, decay_off, wq_off, ut_off, kn_off, p_off, total;
 };
 WorkspaceLayout layout(int num_seqs, int max_slots, int heads) {
     WorkspaceLayout L;
@@ -547,7 +585,7 @@ WorkspaceLayout layout(int num_seqs, int max_slots, int heads) {
     const size_t hs = static_cast<size_t>(heads) * max_slots;
     L.wq_off = o, o = align_up(o + hs * 128 * 128 * 2, 1024);
     L.ut_off = o, o = align_up(o + hs * 128 * 64 * 2, 1024);
-    L.kt_off = o, o = align_up(o + hs * 128 * 64 * 2, 1024);
+    L.kn_off = o, o = align_up(o + hs * 64 * 128 * 2, 1024);
     L.p_off = o, o = align_up(o + hs * 64 * 64 * 2, 1024);
     L.total = o;
     return L;
@@ -598,6 +636,8 @@ extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k
         for (int t = a; t < b; t += kC) slots[num_slots++] = SlotInfo{t, (b - t < kC) ? b - t : kC};
     }
     if (num_slots == 0) return S1_OK;
+    // the scan kernel runs one CTA per (sequence, head): start the longest sequences first
+    std::stable_sort(seqs, seqs + num_seqs, [](const SeqInfo& a, const SeqInfo& b) { return a.num_chunks > b.num_chunks; });
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.slots_off, slots, sizeof(SlotInfo) * num_slots, cudaMemcpyHostToDevice, ctx->stream));
     S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.seqs_off, seqs, sizeof(SeqInfo) * num_seqs, cudaMemcpyHostToDevice, ctx->stream));
@@ -610,7 +650,7 @@ extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k
     pp.num_slots = num_slots, pp.H = heads;
     pp.wq = reinterpret_cast<__nv_bfloat16*>(ws + L.wq_off);
     pp.ut = reinterpret_cast<__nv_bfloat16*>(ws + L.ut_off);
-    pp.kt = reinterpret_cast<__nv_bfloat16*>(ws + L.kt_off);
+    pp.kn = reinterpret_cast<__nv_bfloat16*>(ws + L.kn_off);
     pp.p = reinterpret_cast<__nv_bfloat16*>(ws + L.p_off);
     pp.decay = reinterpret_cast<float*>(ws + L.decay_off);
     pp.status = ctx->status_dev;
@@ -620,17 +660,17 @@ extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k
         S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmem));
         configured_device = ctx->device;
     }
-    s1_delta_prep_kernel<<<dim3((num_slots + 1) / 2, heads), 128, kPrepSmem, ctx->stream>>>(pp);
+    s1_delta_prep_kernel<<<dim3((num_slots + 1) / 2, heads), kPrepThreads, kPrepSmem, ctx->stream>>>(pp);
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
 
     const long long hs_rows = static_cast<long long>(heads) * num_slots;
-    CUtensorMap tWQ, tUT, tKT, tP;
+    CUtensorMap tWQ, tUT, tKN, tP;
     int rc = s1_get_tmap(ctx, pp.wq, hs_rows * 128, 128, 128, 128, 64, 2, 128, &tWQ);
     if (rc) return rc;
     rc = s1_get_tmap(ctx, pp.ut, hs_rows * 128, 64, 64, 128, 64, 2, 128, &tUT);
     if (rc) return rc;
-    rc = s1_get_tmap(ctx, pp.kt, hs_rows * 128, 64, 64, 128, 64, 2, 128, &tKT);
+    rc = s1_get_tmap(ctx, pp.kn, hs_rows * 64, 128, 128, 64, 64, 2, 128, &tKN);
     if (rc) return rc;
     rc = s1_get_tmap(ctx, pp.p, hs_rows * 64, 64, 64, 64, 64, 2, 128, &tP);
     if (rc) return rc;
@@ -641,7 +681,7 @@ extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k
     sp.out = out;
     sp.num_slots = num_slots, sp.H = heads;
     sp.status = ctx->status_dev;
-    s1_delta_scan_kernel<<<dim3(num_seqs, heads), 160, kScanSmem, ctx->stream>>>(tWQ, tUT, tKT, tP, sp);
+    s1_delta_scan_kernel<<<dim3(num_seqs, heads), 160, kScanSmem, ctx->stream>>>(tWQ, tUT, tKN, tP, sp);
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return S1_OK;
