@@ -16,7 +16,7 @@
 //    kernel feeds to the tensor cores.
 //  * s1_delta_scan_kernel  - one CTA per (sequence, head) walks the chunks in order. The state lives in f32
 //    registers (thread = value row, 128 key columns); per chunk it issues three MMAs in transposed form so that
-//    M = Dv = 128:  [V'^T | O^T] = S^T [W ; Q e^G]^T,  O^T += V'^T P^T,  dS^T = V'^T K~ ; operands arrive by TMA
+//    M = Dv = 128:  (W S)^T = S^T W^T,  O^T = S^T (Q e^G)^T + V'^T P^T,  dS^T = V'^T K~ ; operands arrive by TMA
 //    (two-stage ring), V'^T and the bf16 copy of S^T are rewritten in shared memory by the warps between MMAs.
 // Every mbarrier wait is bounded; a wait that runs out raises the context's status word.
 #include <cuda_bf16.h>
@@ -170,19 +170,20 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     if (slot_ok && i == 0 && fh == 0) p.decay[hs] = __expf(Glast);
 
     // ---- operands, one warp per row at a time (coalesced 512-byte rows, lane = 4 consecutive features):
-    //      K, Q, beta e^G K, beta V as bf16 [token x feature] tiles; Q e^G and K e^{G_last - G} to the workspace
+    //      K, Q, beta e^G K as bf16 [token x feature] tiles; Q e^G and K e^{G_last - G} to the workspace
+    //      (beta V is staged later, by the warps that are idle during the triangular solve)
     if (fh == 0) {
         egs[r] = eG;
         egl[r] = eGl;
     }
     __syncthreads();
+    const SlotInfo s0 = p.slots[min(2 * static_cast<int>(blockIdx.x), p.num_slots - 1)];
+    const SlotInfo s1 = (2 * blockIdx.x + 1 < p.num_slots) ? p.slots[2 * blockIdx.x + 1] : SlotInfo{0, 0};
+    const int tile = lane >> 4, col = (4 * lane) & 63;
     {
-        const SlotInfo s0 = p.slots[min(2 * static_cast<int>(blockIdx.x), p.num_slots - 1)];
-        const SlotInfo s1 = (2 * blockIdx.x + 1 < p.num_slots) ? p.slots[2 * blockIdx.x + 1] : SlotInfo{0, 0};
-        const int tile = lane >> 4, col = (4 * lane) & 63;
 #pragma unroll 1
         for (int rr = 0; rr < 16; rr += 4) {
-            float4 kk[4], qq[4], vv[4];
+            float4 kk[4], qq[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int row = warp * 16 + rr + u, ri = row & 63;
@@ -192,7 +193,6 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
                 const bool rv = ri < sr.len;
                 kk[u] = rv ? __ldg(reinterpret_cast<const float4*>(p.k + base_f)) : z;
                 qq[u] = rv ? __ldg(reinterpret_cast<const float4*>(p.q + base_f)) : z;
-                vv[u] = rv ? __ldg(reinterpret_cast<const float4*>(p.v + base_f)) : z;
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -204,7 +204,6 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
                 st_shared_v2(kop + off, pack2(kk[u].x, kk[u].y), pack2(kk[u].z, kk[u].w));
                 st_shared_v2(qop + off, pack2(qq[u].x, qq[u].y), pack2(qq[u].z, qq[u].w));
                 st_shared_v2(xt + off, pack2(kk[u].x * sk, kk[u].y * sk), pack2(kk[u].z * sk, kk[u].w * sk));
-                st_shared_v2(xt + 2 * kTileBytes + off, pack2(vv[u].x * be, vv[u].y * be), pack2(vv[u].z * be, vv[u].w * be));
                 if (rslot < p.num_slots) {
                     const long long hsr = static_cast<long long>(head) * p.num_slots + rslot;
                     *reinterpret_cast<uint2*>(p.wq + (hsr * 128 + 64 + ri) * kD + 4 * lane) =
@@ -269,12 +268,31 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     __syncthreads();
     tc_fence_after();
 
-    // ---- Tm = (I + A)^-1 by forward substitution, one column per thread (columns are independent); the second
-    //      thread of each row fills the zero blocks of the block-diagonal operand meanwhile
+    // ---- Tm = (I + A)^-1 by forward substitution, one column per thread (columns are independent); the other half
+    //      of the warps meanwhile fills the zero blocks of the block-diagonal operand and stages beta V
     if (fh == 1) {
         const uint32_t ttile = top + half * kTileBytes;
 #pragma unroll
         for (int ii = 0; ii < 64; ++ii) st_shared_b16(ttile + sw128((1 - half) * 64 + ii, i), __float2bfloat16_rn(0.f));
+        // beta V rows -> tiles 2, 3 of the B operand: 4 warps x 32 rows, one coalesced 512-byte row per warp load
+#pragma unroll 1
+        for (int rr = 0; rr < 32; rr += 8) {
+            float4 vv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int row = q4 * 32 + rr + u, ri = row & 63;
+                const SlotInfo sr = (row >> 6) ? s1 : s0;
+                const long long base_f = (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane;
+                vv[u] = (ri < sr.len) ? __ldg(reinterpret_cast<const float4*>(p.v + base_f)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int row = q4 * 32 + rr + u;
+                const float be = bsh[row];
+                st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(vv[u].x * be, vv[u].y * be),
+                             pack2(vv[u].z * be, vv[u].w * be));
+            }
+        }
     } else {
         float t[64];
         const float* arow = amat + (half * 64) * kAStride;
@@ -370,7 +388,7 @@ struct ScanParams {
 };
 
 constexpr int kStageBytes = 2 * kTileBytes /*WQ*/ + kTileBytes /*UT*/ + kTileBytes /*K~*/ + kTileBytes / 2 /*P*/;  // 73728
-constexpr int kScanSmem = 2 * kStageBytes + 2 * kTileBytes /*S^T*/ + 1024 + 128;
+constexpr int kScanSmem = 2 * kStageBytes + 2 * kTileBytes /*S^T*/ + 1024 + 160;
 
 __global__ void __launch_bounds__(160, 1)
 s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_constant__ CUtensorMap tmUT,
@@ -380,11 +398,14 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
     uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t sop = base + 2 * kStageBytes;  // S^T as bf16 A operand: 2 tiles [128 dv x 64 dk]
     uint64_t* bars = reinterpret_cast<uint64_t*>(al + 2 * kStageBytes + 2 * kTileBytes);
-    // bars: 0,1 full; 2,3 empty; 4 mma1 done; 5 V' ready; 6 mma2/3 done; 7 S ready
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    // bars: 0,1 full; 2,3 empty; 4 (W S)^T done; 5 V' ready; 6 O^T done; 7 S ready; 8 dS^T done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t b0 = smem_u32(bars);
-    const uint32_t full0 = b0, empty0 = b0 + 16, bar_m1 = b0 + 32, bar_v = b0 + 40, bar_m2 = b0 + 48, bar_s = b0 + 56;
+    const uint32_t full0 = b0, empty0 = b0 + 16, bar_m1 = b0 + 32, bar_v = b0 + 40, bar_m2 = b0 + 48, bar_s = b0 + 56,
+                   bar_m3 = b0 + 64;
+    // TMEM columns: 0..63 (W S)^T, 64..127 / 128..191 O^T of even / odd chunks, 192..319 dS^T
+    constexpr uint32_t kColO = 64, kColDS = 192;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y;
@@ -401,6 +422,7 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
         mbar_init(bar_v, 4);
         mbar_init(bar_m2, 1);
         mbar_init(bar_s, 4);
+        mbar_init(bar_m3, 1);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmWQ);
@@ -409,7 +431,7 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
         tma_prefetch_desc(&tmP);
     }
     if (warp == 4) {
-        tmem_alloc(smem_u32(tmem_slot), 256);
+        tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -444,8 +466,9 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
                 if (!mbar_wait(full0 + 8u * st, (c >> 1) & 1, abort_flag)) { fail = 2; break; }
                 if (!mbar_wait(bar_s, c & 1, abort_flag)) { fail = 3; break; }
                 tc_fence_after();
-                {   // [V'^T | O^T] partial = S^T [W ; Q e^G]^T : M = 128 (dv), N = 128 (64 W rows, 64 Q rows), K = 128 (dk)
-                    constexpr uint32_t idesc = make_idesc(1, 128, 128);
+                const uint32_t o_col = kColO + 64u * (c & 1);
+                {   // (W S)^T = S^T W^T, then the state part of the output O^T = S^T (Q e^G)^T : M = 128 (dv), N = 64, K = 128 (dk)
+                    constexpr uint32_t idesc = make_idesc(1, 128, 64);
 #pragma unroll
                     for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
@@ -453,6 +476,12 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
                             umma_bf16(tmem, make_sw128_kmajor_desc(sop + kt * kTileBytes) + 2u * kk,
                                       make_sw128_kmajor_desc(sb + kt * kTileBytes) + 2u * kk, idesc, (kt | kk) ? 1u : 0u);
                     umma_commit(bar_m1);
+#pragma unroll
+                    for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)  // rows 64..127 of the tile hold Q e^G (8192 bytes further)
+                            umma_bf16(tmem + o_col, make_sw128_kmajor_desc(sop + kt * kTileBytes) + 2u * kk,
+                                      make_sw128_kmajor_desc(sb + kt * kTileBytes + 8192) + 2u * kk, idesc, (kt | kk) ? 1u : 0u);
                 }
                 if (!mbar_wait(bar_v, c & 1, abort_flag)) { fail = 4; break; }
                 tc_fence_after();
@@ -460,12 +489,13 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
                     constexpr uint32_t idesc_p = make_idesc(1, 128, 64), idesc_k = make_idesc(1, 128, 128) | kBMnMajor;
                     const uint32_t vt = sb + 2 * kTileBytes, ktile = sb + 3 * kTileBytes, ptile = sb + 4 * kTileBytes;
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)  // O^T += V'^T P^T  (K = 64 tokens j)
-                        umma_bf16(tmem + 64, make_sw128_kmajor_desc(vt) + 2u * kk, make_sw128_kmajor_desc(ptile) + 2u * kk, idesc_p, 1u);
-#pragma unroll
                     for (int kk = 0; kk < 4; ++kk)  // dS^T = V'^T K~ ; K~ as stored: token rows x dk (MN-major B, two 8 KB tiles)
-                        umma_bf16(tmem + 128, make_sw128_kmajor_desc(vt) + 2u * kk,
+                        umma_bf16(tmem + kColDS, make_sw128_kmajor_desc(vt) + 2u * kk,
                                   make_sw128_mnmajor_desc(ktile, kTileBytes / 2) + 128u * kk, idesc_k, kk ? 1u : 0u);
+                    umma_commit(bar_m3);  // the state update (the critical path) can start
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)  // O^T += V'^T P^T  (K = 64 tokens j)
+                        umma_bf16(tmem + o_col, make_sw128_kmajor_desc(vt) + 2u * kk, make_sw128_kmajor_desc(ptile) + 2u * kk, idesc_p, 1u);
                     umma_commit(bar_m2);
                     umma_commit(empty0 + 8u * st);
                 }
@@ -522,24 +552,14 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_v);
 
-            ok = mbar_wait(bar_m2, c & 1, abort_flag);
+            ok = mbar_wait(bar_m3, c & 1, abort_flag);
             if (!__all_sync(0xffffffffu, ok)) { fail = 6; break; }
             tc_fence_after();
-            {   // O^T row (TMEM columns 64..127): out[token j][head][d]
-                uint32_t o[2][32];
-                tmem_ld_32x32b_x32(lane_addr + 64, o[0]);
-                tmem_ld_32x32b_x32(lane_addr + 96, o[1]);
-                tmem_ld_wait();
-                float* obase = p.out + (static_cast<long long>(si.tok_start) * p.H + head) * kD + d;
-#pragma unroll
-                for (int j = 0; j < 64; ++j)
-                    if (j < si.len) obase[static_cast<long long>(j) * p.H * kD] = __uint_as_float(o[j >> 5][j & 31]);
-            }
-            // state: S <- e^{G_last} S + dS ; refresh the bf16 operand copy
+            // state: S <- e^{G_last} S + dS ; refresh the bf16 operand copy (this is the chain the next chunk waits on)
 #pragma unroll
             for (int cb = 0; cb < 4; ++cb) {
                 uint32_t ds[32];
-                tmem_ld_32x32b_x32(lane_addr + 128 + cb * 32, ds);
+                tmem_ld_32x32b_x32(lane_addr + kColDS + cb * 32, ds);
                 tmem_ld_wait();
 #pragma unroll
                 for (int e = 0; e < 32; ++e) S[cb * 32 + e] = fmaf(dec, S[cb * 32 + e], __uint_as_float(ds[e]));
@@ -554,6 +574,23 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_s);
+
+            // output of this chunk, off the critical path: O^T row -> out[token j][head][d]
+            ok = mbar_wait(bar_m2, c & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) { fail = 7; break; }
+            tc_fence_after();
+            {
+                uint32_t o[2][32];
+                const uint32_t o_col = kColO + 64u * (c & 1);
+                tmem_ld_32x32b_x32(lane_addr + o_col, o[0]);
+                tmem_ld_32x32b_x32(lane_addr + o_col + 32, o[1]);
+                tmem_ld_wait();
+                float* obase = p.out + (static_cast<long long>(si.tok_start) * p.H + head) * kD + d;
+#pragma unroll
+                for (int j = 0; j < 64; ++j)
+                    if (j < si.len) obase[static_cast<long long>(j) * p.H * kD] = __uint_as_float(o[j >> 5][j & 31]);
+            }
+            tc_fence_before();
         }
         __syncwarp();
     }
@@ -567,7 +604,7 @@ s1_delta_scan_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_cons
     __syncthreads();
     if (warp == 4) {
         tc_fence_after();
-        tmem_dealloc(tmem, 256);
+        tmem_dealloc(tmem, 512);
     }
 }
 
