@@ -64,6 +64,13 @@ __device__ __forceinline__ uint64_t make_sw128_mnmajor_desc(uint32_t smem_addr, 
 }
 constexpr uint32_t kBMnMajor = 1u << 16;  // instruction-descriptor bit: B operand is MN-major
 
+// 16-byte asynchronous copy global -> shared; `bytes` = 16, or 0 to write zeros without reading.
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t b) {
     asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
@@ -145,6 +152,23 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
         tmem_relinquish();
     }
 
+    // ---- raw f32 rows of Q and K: all 128 KB requested at once with cp.async (rows past a chunk's end are
+    //      zero-filled), into staging areas that alias buffers which are not in use yet:
+    //      Q over the B-operand tiles (xt), K over the Tm operand and the A matrix (top, amat)
+    const SlotInfo s0 = p.slots[min(2 * static_cast<int>(blockIdx.x), p.num_slots - 1)];
+    const SlotInfo s1 = (2 * blockIdx.x + 1 < p.num_slots) ? p.slots[2 * blockIdx.x + 1] : SlotInfo{0, 0};
+    const uint32_t stage_q = xt, stage_k = top, stage_v = kop;
+#pragma unroll 4
+    for (int u = 0; u < 16; ++u) {
+        const int row = warp * 16 + u, ri = row & 63;
+        const SlotInfo sr = (row >> 6) ? s1 : s0;
+        const bool rv = ri < sr.len;
+        const long long base_f = rv ? (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane : 0;
+        cp_async16_zfill(stage_q + row * 512 + lane * 16, p.q + base_f, rv ? 16u : 0u);
+        cp_async16_zfill(stage_k + row * 512 + lane * 16, p.k + base_f, rv ? 16u : 0u);
+    }
+    cp_async_commit_group();
+
     // ---- gates: inclusive cumulative sum inside each chunk (two warps per chunk)
     const float gi = valid ? p.g[tok * p.H + head] : 0.f;
     const float bi = valid ? p.beta[tok * p.H + head] : 0.f;
@@ -169,49 +193,45 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     const float eGl = __expf(Glast - G);
     if (slot_ok && i == 0 && fh == 0) p.decay[hs] = __expf(Glast);
 
-    // ---- operands, one warp per row at a time (coalesced 512-byte rows, lane = 4 consecutive features):
-    //      K, Q, beta e^G K as bf16 [token x feature] tiles; Q e^G and K e^{G_last - G} to the workspace
+    // ---- operands, one warp per row at a time (lane = 4 consecutive features), from the staged f32 rows:
+    //      Q, K, beta e^G K as bf16 [token x feature] tiles; Q e^G and K e^{G_last - G} to the workspace
     //      (beta V is staged later, by the warps that are idle during the triangular solve)
     if (fh == 0) {
         egs[r] = eG;
         egl[r] = eGl;
     }
+    cp_async_wait_all();
     __syncthreads();
-    const SlotInfo s0 = p.slots[min(2 * static_cast<int>(blockIdx.x), p.num_slots - 1)];
-    const SlotInfo s1 = (2 * blockIdx.x + 1 < p.num_slots) ? p.slots[2 * blockIdx.x + 1] : SlotInfo{0, 0};
     const int tile = lane >> 4, col = (4 * lane) & 63;
-    {
-#pragma unroll 1
-        for (int rr = 0; rr < 16; rr += 4) {
-            float4 kk[4], qq[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int row = warp * 16 + rr + u, ri = row & 63;
-                const SlotInfo sr = (row >> 6) ? s1 : s0;
-                const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-                const long long base_f = (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane;
-                const bool rv = ri < sr.len;
-                kk[u] = rv ? __ldg(reinterpret_cast<const float4*>(p.k + base_f)) : z;
-                qq[u] = rv ? __ldg(reinterpret_cast<const float4*>(p.q + base_f)) : z;
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int row = warp * 16 + rr + u, ri = row & 63;
-                const int rslot = 2 * blockIdx.x + (row >> 6);
-                const float be = bsh[row], eg = egs[row], el = egl[row];
-                const float sk = be * eg;
-                const uint32_t off = tile * kTileBytes + sw128(row, col);
-                st_shared_v2(kop + off, pack2(kk[u].x, kk[u].y), pack2(kk[u].z, kk[u].w));
-                st_shared_v2(qop + off, pack2(qq[u].x, qq[u].y), pack2(qq[u].z, qq[u].w));
-                st_shared_v2(xt + off, pack2(kk[u].x * sk, kk[u].y * sk), pack2(kk[u].z * sk, kk[u].w * sk));
-                if (rslot < p.num_slots) {
-                    const long long hsr = static_cast<long long>(head) * p.num_slots + rslot;
-                    *reinterpret_cast<uint2*>(p.wq + (hsr * 128 + 64 + ri) * kD + 4 * lane) =
-                        make_uint2(pack2(qq[u].x * eg, qq[u].y * eg), pack2(qq[u].z * eg, qq[u].w * eg));
-                    *reinterpret_cast<uint2*>(p.kn + (hsr * 64 + ri) * kD + 4 * lane) =
-                        make_uint2(pack2(kk[u].x * el, kk[u].y * el), pack2(kk[u].z * el, kk[u].w * el));
-                }
-            }
+#pragma unroll 4
+    for (int u = 0; u < 16; ++u) {  // Q first: its staging area is where beta e^G K goes next
+        const int row = warp * 16 + u, ri = row & 63;
+        const int rslot = 2 * blockIdx.x + (row >> 6);
+        const uint4 raw = ld_shared_v4(stage_q + row * 512 + lane * 16);
+        const float4 qq = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
+        const float eg = egs[row];
+        st_shared_v2(qop + tile * kTileBytes + sw128(row, col), pack2(qq.x, qq.y), pack2(qq.z, qq.w));
+        if (rslot < p.num_slots) {
+            const long long hsr = static_cast<long long>(head) * p.num_slots + rslot;
+            *reinterpret_cast<uint2*>(p.wq + (hsr * 128 + 64 + ri) * kD + 4 * lane) =
+                make_uint2(pack2(qq.x * eg, qq.y * eg), pack2(qq.z * eg, qq.w * eg));
+        }
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int u = 0; u < 16; ++u) {
+        const int row = warp * 16 + u, ri = row & 63;
+        const int rslot = 2 * blockIdx.x + (row >> 6);
+        const uint4 raw = ld_shared_v4(stage_k + row * 512 + lane * 16);
+        const float4 kk = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
+        const float el = egl[row], sk = bsh[row] * egs[row];
+        const uint32_t off = tile * kTileBytes + sw128(row, col);
+        st_shared_v2(kop + off, pack2(kk.x, kk.y), pack2(kk.z, kk.w));
+        st_shared_v2(xt + off, pack2(kk.x * sk, kk.y * sk), pack2(kk.z * sk, kk.w * sk));
+        if (rslot < p.num_slots) {
+            const long long hsr = static_cast<long long>(head) * p.num_slots + rslot;
+            *reinterpret_cast<uint2*>(p.kn + (hsr * 64 + ri) * kD + 4 * lane) =
+                make_uint2(pack2(kk.x * el, kk.y * el), pack2(kk.z * el, kk.w * el));
         }
     }
     fence_proxy_async_smem();
@@ -237,6 +257,16 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     bool ok = mbar_wait(smem_u32(bar), 0, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
+    // K and Q tiles are consumed: their 64 KB now stage the raw V rows, in flight while A and P are formed
+#pragma unroll 4
+    for (int u = 0; u < 16; ++u) {
+        const int row = warp * 16 + u, ri = row & 63;
+        const SlotInfo sr = (row >> 6) ? s1 : s0;
+        const bool rv = ok && ri < sr.len;
+        const long long base_f = rv ? (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane : 0;
+        cp_async16_zfill(stage_v + row * 512 + lane * 16, p.v + base_f, rv ? 16u : 0u);
+    }
+    cp_async_commit_group();
     if (ok) {
         tc_fence_after();
         // this thread's 32 of the own chunk's 64 columns of row r
@@ -264,6 +294,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
             }
         }
     }
+    cp_async_wait_all();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -274,24 +305,14 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
         const uint32_t ttile = top + half * kTileBytes;
 #pragma unroll
         for (int ii = 0; ii < 64; ++ii) st_shared_b16(ttile + sw128((1 - half) * 64 + ii, i), __float2bfloat16_rn(0.f));
-        // beta V rows -> tiles 2, 3 of the B operand: 4 warps x 32 rows, one coalesced 512-byte row per warp load
-#pragma unroll 1
-        for (int rr = 0; rr < 32; rr += 8) {
-            float4 vv[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int row = q4 * 32 + rr + u, ri = row & 63;
-                const SlotInfo sr = (row >> 6) ? s1 : s0;
-                const long long base_f = (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane;
-                vv[u] = (ri < sr.len) ? __ldg(reinterpret_cast<const float4*>(p.v + base_f)) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int row = q4 * 32 + rr + u;
-                const float be = bsh[row];
-                st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(vv[u].x * be, vv[u].y * be),
-                             pack2(vv[u].z * be, vv[u].w * be));
-            }
+        // beta V rows (staged f32) -> tiles 2, 3 of the B operand: 4 warps x 32 rows
+#pragma unroll 4
+        for (int u = 0; u < 32; ++u) {
+            const int row = q4 * 32 + u;
+            const uint4 raw = ld_shared_v4(stage_v + row * 512 + lane * 16);
+            const float be = bsh[row];
+            st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(__uint_as_float(raw.x) * be, __uint_as_float(raw.y) * be),
+                         pack2(__uint_as_float(raw.z) * be, __uint_as_float(raw.w) * be));
         }
     } else {
         float t[64];
