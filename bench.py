@@ -150,6 +150,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay each step from a CUDA graph (for small token budgets, where launching from Python is the bottleneck)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -160,6 +162,7 @@ def main():
                           "(lengths U[16,512]), Wqkv / Wo+residual / Wi+GeGLU / MLP-out+residual",
               "tokens": T, "hidden": HIDDEN, "intermediate": INTER, "parallelism": f"replicas x{world}",
               "l2": "4 rotating input sets (400 MB) + 226 MB of outputs per step exceed the 126 MB L2",
+              "launch": "cuda graph replay" if args.graph else "eager",
               "residual": "in place (x += ...); alternate visits of a buffer use -Wo / -Wout to keep the stream bounded"}
 
     if args.impl == "reference":
@@ -239,6 +242,22 @@ def main():
     for i in range(2 * NSETS * ((warmup + 2 * NSETS - 1) // (2 * NSETS))):  # whole +/- cycles
         step(xs[i % NSETS], atts[i % NSETS], negate=bool((i // NSETS) & 1))
     ctx.sync()
+    graphs = None
+    if args.graph:
+        # one graph per (buffer set, sign): the launches of a step with their tensor maps baked in
+        cap = torch.cuda.Stream(dev)
+        with torch.cuda.stream(cap):
+            cap_ctx = device.load(local_rank)  # context of the capture stream, created before any capture
+            step(xs[0], atts[0])
+            cap_ctx.sync()
+        graphs = {}
+        for s_ in range(NSETS):
+            for neg in (False, True):
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, stream=cap):
+                    step(xs[s_], atts[s_], negate=neg)
+                graphs[(s_, neg)] = g_
+        torch.cuda.synchronize()
     launches0 = ctx.launch_count()
     marks = [[ev() for _ in range(5)] for _ in range(args.steps)]
     sampler = ClockSampler(local_rank)
@@ -249,15 +268,23 @@ def main():
     e0, e1 = ev(), ev()
     e0.record()
     for i in range(args.steps):
-        step(xs[i % NSETS], atts[i % NSETS], marks[i], negate=bool((i // NSETS) & 1))
+        if graphs is not None:
+            graphs[(i % NSETS, bool((i // NSETS) & 1))].replay()
+        else:
+            step(xs[i % NSETS], atts[i % NSETS], marks[i], negate=bool((i // NSETS) & 1))
     e1.record()
     barrier()
     t1w = time.time()
     ctx.sync()
     launches = ctx.launch_count() - launches0
     ms_total = e0.elapsed_time(e1)
-    per = {n: sum(marks[i][j].elapsed_time(marks[i][j + 1]) for i in range(args.steps)) / args.steps
-           for j, n in enumerate(names)}
+    if graphs is not None:
+        launches = 4 * args.steps  # replayed from the graphs (4 kernel nodes each), not counted by the context
+        # no per-launch events inside a graph: split the step time by algorithmic flops for the breakdown
+        per = {n: (ms_total / args.steps) * (2 * pj[1] * pj[2]) / FLOPS_PER_TOKEN for n, pj in zip(names, PROJECTIONS)}
+    else:
+        per = {n: sum(marks[i][j].elapsed_time(marks[i][j + 1]) for i in range(args.steps)) / args.steps
+               for j, n in enumerate(names)}
 
     # ---- end-to-end arm: host buffers in, host buffer out, copies inside the timed region ----------------------
     # (copy-in of batch i+1 and copy-out of batch i-1 overlap the compute of batch i: sys1_b200.pipeline)

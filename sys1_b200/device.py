@@ -84,9 +84,12 @@ def load(ordinal: Optional[int] = None) -> Context:
     if ordinal is None:
         ordinal = torch.cuda.current_device()
     stream = torch.cuda.current_stream(ordinal)
-    key = (int(ordinal), int(stream.cuda_stream))
+    key = (ordinal, stream.cuda_stream)
     ctx = _contexts.get(key)
     if ctx is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("no context exists for the capturing stream yet: call device.load() on that stream once "
+                               "before the capture starts (creating a context allocates)")
         ctx = Context(ordinal, stream)
         _contexts[key] = ctx
     return ctx
