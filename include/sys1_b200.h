@@ -153,6 +153,33 @@ int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const flo
                           int key_dim, int value_dim, float* out, void* workspace, size_t workspace_bytes);
 
 /*
+ * The stages around the recurrence in the Qwen3.5 linear-attention layer, on the packed layout (key dim = value
+ * dim = 128; bf16 activations, f32 recurrence inputs):
+ *  s1_conv_silu     y = silu(causal depthwise conv(x)) with weight [channels, taps] (the reference's [C, 1, taps]),
+ *                   the sum and each product rounded to bf16 tap by tap as in src/kernels/qwen35.cu:3-29
+ *                   (CPU form src/archs/qwen35_text.rs:632-650). `positions` (DEVICE int32 [T], index of each token
+ *                   inside its own sequence, from s1_pack_batch) gives the zero left padding per sequence.
+ *  s1_delta_inputs  `delta_inputs` (src/archs/qwen35_text.rs:528-579): split mixed = [q | k | v], repeat the key
+ *                   heads over the value heads, q = l2norm(q) / sqrt(128), k = l2norm(k) (1e-6 inside the root),
+ *                   beta = sigmoid(b), g = softplus(a + dt_bias) * neg_exp_a; outputs f32 [T, Hv, 128] / [T, Hv].
+ *  s1_delta_finish  `finish_delta` up to out_proj (:597-626): o / sqrt(mean(o^2) + eps) * norm_weight * silu(z) -> bf16.
+ *  s1_gated_delta_rule  the three in a row around s1_delta_rule_chunked, from the conv output to the out_proj
+ *                   input; `workspace` (device, 1024-byte aligned) of s1_gated_delta_rule_workspace(...) bytes.
+ */
+int s1_conv_silu(s1_ctx* ctx, const void* x, long long ldx, const void* weight, const int32_t* positions, int total_tokens,
+                 int channels, int taps, void* y, long long ldy);
+int s1_delta_inputs(s1_ctx* ctx, const void* mixed, long long ldm, const void* b_proj, const void* a_proj, long long ldba,
+                    const float* dt_bias, const float* neg_exp_a, int total_tokens, int key_heads, int value_heads, float* q,
+                    float* k, float* v, float* g, float* beta);
+int s1_delta_finish(s1_ctx* ctx, const float* o, const void* z, long long ldz, const void* norm_weight, float eps,
+                    int total_tokens, int value_heads, void* y, long long ldy);
+size_t s1_gated_delta_rule_workspace(int num_seqs, int total_tokens, int value_heads);
+int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const void* b_proj, const void* a_proj, long long ldba,
+                        const float* dt_bias, const float* neg_exp_a, const void* z, long long ldz, const void* norm_weight,
+                        float eps, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens, int key_heads,
+                        int value_heads, void* y, long long ldy, void* workspace, size_t workspace_bytes);
+
+/*
  * Packs the next sequences of a queue into one token-packed batch (host arrays, no GPU work).
  * Takes sequences in order while the running token count stays within `token_budget`; a sequence longer than
  * the budget forms a batch of its own. Writes cu_seqlens[0..num_taken] (cu_seqlens[0] = 0, last = total) and,

@@ -15,4 +15,4 @@ Pinning status
     tree. It is restated from the public contract `Linear::forward(x) = x Wᵀ (+ b)` with f32 accumulation.
 """
 from .projection import (geglu, linear, mlp_modernbert, mlp_qwen35, round_bf16, swiglu)  # noqa: F401
-from .delta_rule import (chunked_delta_rule, delta_inputs, finish_delta, sequential_delta_rule)  # noqa: F401
+from .delta_rule import (causal_conv_silu, chunked_delta_rule, delta_inputs, finish_delta, sequential_delta_rule)  # noqa: F401

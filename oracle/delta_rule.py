@@ -97,6 +97,22 @@ def chunked_delta_rule(q, k, v, g, beta, chunk: int = 32) -> torch.Tensor:
     return torch.cat(outs, 2).transpose(1, 2).contiguous()
 
 
+def causal_conv_silu(x, weight, dtype: str = "bf16") -> torch.Tensor:
+    """`causal_conv_silu` (src/archs/qwen35_text.rs:632-650; CUDA kernel src/kernels/qwen35.cu:3-29): depthwise
+    causal conv over `x [B, L, C]` with `weight [C, 1, taps]` (zero left padding per batch row), then SiLU. In
+    "bf16" the running sum and each product are rounded to bf16 tap by tap, as both reference paths do."""
+    x = x.to(torch.float32)
+    B, L, Cc = x.shape
+    w = weight.to(torch.float32).reshape(Cc, -1)
+    taps = w.shape[1]
+    rnd = (lambda t: t.to(torch.bfloat16).to(torch.float32)) if dtype == "bf16" else (lambda t: t)
+    padded = torch.nn.functional.pad(x, (0, 0, taps - 1, 0))
+    mixed = torch.zeros_like(x)
+    for tap in range(taps):
+        mixed = rnd(mixed + rnd(padded[:, tap:tap + L] * w[:, tap].reshape(1, 1, Cc)))
+    return rnd(mixed / (1.0 + torch.exp(-mixed)))
+
+
 def delta_inputs(mixed, b_proj, a_proj, dt_bias, neg_exp_a, key_heads: int, value_heads: int, key_dim: int,
                  value_dim: int) -> Tuple[torch.Tensor, ...]:
     """`LinearAttention::delta_inputs` (src/archs/qwen35_text.rs:528-579) for `mixed [B, L, 2Kw+Vw]` (already

@@ -54,6 +54,16 @@ SIGNATURES = {
     "s1_delta_rule": (C.c_int, [C.c_void_p] * 7 + [C.c_int] * 5 + [C.c_void_p]),
     "s1_delta_rule_chunked_workspace": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "s1_delta_rule_chunked": (C.c_int, [C.c_void_p] * 6 + [C.POINTER(C.c_int32)] + [C.c_int] * 5 + [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "s1_conv_silu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                               C.c_void_p, C.c_longlong]),
+    "s1_delta_inputs": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p,
+                                  C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 5),
+    "s1_delta_finish": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_float, C.c_int, C.c_int,
+                                  C.c_void_p, C.c_longlong]),
+    "s1_gated_delta_rule_workspace": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "s1_gated_delta_rule": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p,
+                                      C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_float, C.POINTER(C.c_int32),
+                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_size_t]),
     "s1_linear": (C.c_int, [C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                             C.c_void_p, C.c_longlong, C.c_int]),
 }

@@ -1,0 +1,230 @@
+// The elementwise stages around the gated delta rule of the Qwen3.5 linear-attention layer, on the packed
+// layout, and the entry point that chains them with the chunked recurrence:
+//   s1_conv_silu      causal depthwise conv + SiLU   (src/kernels/qwen35.cu:3-29; src/archs/qwen35_text.rs:632-650)
+//   s1_delta_inputs   split / head-repeat / L2-norm / gates  (`delta_inputs`, src/archs/qwen35_text.rs:528-579;
+//                     the Metal build fuses the same steps in src/kernels/qwen35.metal:146-203)
+//   s1_delta_finish   per-head RMS norm x weight x SiLU(z), cast to bf16 (`finish_delta`, :597-626, up to out_proj)
+//   s1_gated_delta_rule = s1_delta_inputs -> s1_delta_rule_chunked -> s1_delta_finish
+// All three are HBM-bound streaming kernels: 16-byte accesses, one warp per (token, head) row where a
+// reduction over the head dimension is needed.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "context.h"
+
+extern "C" size_t s1_delta_rule_chunked_workspace(int num_seqs, int total_tokens, int heads);
+extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const float* v, const float* g,
+                                     const float* beta, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens,
+                                     int heads, int key_dim, int value_dim, float* out, void* workspace,
+                                     size_t workspace_bytes);
+
+namespace {
+
+__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// ------------------------------------------------------------------------------------------------ conv + SiLU
+// y[t, c] = silu( sum_tap x[t + tap - taps + 1, c] * w[c, tap] ), taps that reach before the token's own sequence
+// are skipped (zero left padding per sequence); the running sum and every product are rounded to bf16 tap by
+// tap, as the reference kernel does.
+__global__ void __launch_bounds__(256) s1_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                           const __nv_bfloat16* __restrict__ w, const int32_t* __restrict__ positions,
+                                                           int T, int C, int taps, __nv_bfloat16* __restrict__ y, long long ldy) {
+    const int groups = C / 8;  // 8 channels (16 bytes) per thread
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<long long>(T) * groups) return;
+    const int t = static_cast<int>(idx / groups), c0 = static_cast<int>(idx % groups) * 8;
+    const int pos = positions[t];
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int tap = 0; tap < taps; ++tap) {
+        const int back = taps - 1 - tap;  // how many tokens before t this tap reads
+        if (back > pos) continue;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + static_cast<long long>(t - back) * ldx + c0));
+        const __nv_bfloat16* xv = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float prod = bf16r(__bfloat162float(xv[e]) * __bfloat162float(w[static_cast<long long>(c0 + e) * taps + tap]));
+            acc[e] = bf16r(acc[e] + prod);
+        }
+    }
+    __nv_bfloat16 out[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = __float2bfloat16_rn(acc[e] / (1.f + expf(-acc[e])));
+    *reinterpret_cast<uint4*>(y + static_cast<long long>(t) * ldy + c0) = *reinterpret_cast<const uint4*>(out);
+}
+
+// ------------------------------------------------------------------------------------------------ delta inputs
+// One warp per (token, value head): key head = value head / (Hv / Hk) (src/archs/qwen35_text.rs:552-559).
+__global__ void __launch_bounds__(256) s1_delta_inputs_kernel(const __nv_bfloat16* __restrict__ mixed, long long ldm,
+                                                              const __nv_bfloat16* __restrict__ bproj, const __nv_bfloat16* __restrict__ aproj,
+                                                              long long ldba, const float* __restrict__ dt_bias,
+                                                              const float* __restrict__ neg_exp_a, int T, int Hk, int Hv,
+                                                              float* __restrict__ q, float* __restrict__ k, float* __restrict__ v,
+                                                              float* __restrict__ g, float* __restrict__ beta) {
+    const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= static_cast<long long>(T) * Hv) return;
+    const int t = static_cast<int>(wid / Hv), hv = static_cast<int>(wid % Hv);
+    const int hk = hv / (Hv / Hk);
+    const __nv_bfloat16* row = mixed + static_cast<long long>(t) * ldm;
+    const int kw = Hk * 128;
+    auto load4 = [&](const __nv_bfloat16* p, float (&f)[4]) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p + 4 * lane));
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        f[0] = __low2float(a), f[1] = __high2float(a), f[2] = __low2float(b), f[3] = __high2float(b);
+    };
+    float qf[4], kf[4], vf[4];
+    load4(row + hk * 128, qf);
+    load4(row + kw + hk * 128, kf);
+    load4(row + 2 * kw + hv * 128, vf);
+    float sq = qf[0] * qf[0] + qf[1] * qf[1] + qf[2] * qf[2] + qf[3] * qf[3];
+    float sk = kf[0] * kf[0] + kf[1] * kf[1] + kf[2] * kf[2] + kf[3] * kf[3];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        sk += __shfl_xor_sync(0xffffffffu, sk, o);
+    }
+    const float iq = 0.08838834764831845f / sqrtf(sq + 1e-6f);  // 128^-1/2 / sqrt(sum q^2 + 1e-6)
+    const float ik = 1.f / sqrtf(sk + 1e-6f);
+    const long long o = (static_cast<long long>(t) * Hv + hv) * 128 + 4 * lane;
+    *reinterpret_cast<float4*>(q + o) = make_float4(qf[0] * iq, qf[1] * iq, qf[2] * iq, qf[3] * iq);
+    *reinterpret_cast<float4*>(k + o) = make_float4(kf[0] * ik, kf[1] * ik, kf[2] * ik, kf[3] * ik);
+    *reinterpret_cast<float4*>(v + o) = make_float4(vf[0], vf[1], vf[2], vf[3]);
+    if (lane == 0) {
+        const float bb = __bfloat162float(bproj[static_cast<long long>(t) * ldba + hv]);
+        const float aa = __bfloat162float(aproj[static_cast<long long>(t) * ldba + hv]) + dt_bias[hv];
+        beta[static_cast<long long>(t) * Hv + hv] = 1.f / (1.f + expf(-bb));
+        const float softplus = fmaxf(aa, 0.f) + logf(expf(-fabsf(aa)) + 1.f);
+        g[static_cast<long long>(t) * Hv + hv] = softplus * neg_exp_a[hv];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ finish
+__global__ void __launch_bounds__(256) s1_delta_finish_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ z,
+                                                              long long ldz, const __nv_bfloat16* __restrict__ norm_w, float eps, int T,
+                                                              int Hv, __nv_bfloat16* __restrict__ y, long long ldy) {
+    const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= static_cast<long long>(T) * Hv) return;
+    const int t = static_cast<int>(wid / Hv), hv = static_cast<int>(wid % Hv);
+    const float4 ov = __ldg(reinterpret_cast<const float4*>(o + (static_cast<long long>(t) * Hv + hv) * 128) + lane);
+    float ss = ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+    const float inv = 1.f / sqrtf(ss * (1.f / 128.f) + eps);
+    const uint2 zr = __ldg(reinterpret_cast<const uint2*>(z + static_cast<long long>(t) * ldz + hv * 128 + 4 * lane));
+    const uint2 wr = __ldg(reinterpret_cast<const uint2*>(norm_w + 4 * lane));
+    const __nv_bfloat16* zv = reinterpret_cast<const __nv_bfloat16*>(&zr);
+    const __nv_bfloat16* wv = reinterpret_cast<const __nv_bfloat16*>(&wr);
+    const float of[4] = {ov.x, ov.y, ov.z, ov.w};
+    __nv_bfloat16 out[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float gate = __bfloat162float(zv[e]);
+        out[e] = __float2bfloat16_rn(of[e] * inv * __bfloat162float(wv[e]) * (gate / (1.f + expf(-gate))));
+    }
+    *reinterpret_cast<uint2*>(y + static_cast<long long>(t) * ldy + hv * 128 + 4 * lane) = *reinterpret_cast<const uint2*>(out);
+}
+
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" int s1_conv_silu(s1_ctx* ctx, const void* x, long long ldx, const void* weight, const int32_t* positions,
+                            int total_tokens, int channels, int taps, void* y, long long ldy) {
+    if (!ctx) return S1_EINVAL;
+    if (!x || !weight || !positions || !y) return s1_fail(ctx, S1_EINVAL, "s1_conv_silu: null pointer");
+    if (total_tokens < 0 || channels < 8 || (channels % 8) || taps < 1 || taps > 16)
+        return s1_fail(ctx, S1_EINVAL, "s1_conv_silu: channels must be a multiple of 8, 1 <= taps <= 16");
+    if ((ldx % 8) || (ldy % 8) || ldx < channels || ldy < channels || !al16(x) || !al16(y))
+        return s1_fail(ctx, S1_EINVAL, "s1_conv_silu: rows must be 16-byte aligned");
+    if (total_tokens == 0) return S1_OK;
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    const long long n = static_cast<long long>(total_tokens) * (channels / 8);
+    s1_conv_silu_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
+        static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(weight), positions, total_tokens, channels, taps,
+        static_cast<__nv_bfloat16*>(y), ldy);
+    S1_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return S1_OK;
+}
+
+extern "C" int s1_delta_inputs(s1_ctx* ctx, const void* mixed, long long ldm, const void* b_proj, const void* a_proj,
+                               long long ldba, const float* dt_bias, const float* neg_exp_a, int total_tokens, int key_heads,
+                               int value_heads, float* q, float* k, float* v, float* g, float* beta) {
+    if (!ctx) return S1_EINVAL;
+    if (!mixed || !b_proj || !a_proj || !dt_bias || !neg_exp_a || !q || !k || !v || !g || !beta)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_inputs: null pointer");
+    if (key_heads < 1 || value_heads < key_heads || value_heads % key_heads)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_inputs: value_heads must be a multiple of key_heads");
+    const long long width = 2LL * key_heads * 128 + 1LL * value_heads * 128;
+    if (ldm < width || (ldm % 4) || ldba < value_heads || !al16(mixed) || !al16(q) || !al16(k) || !al16(v))
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_inputs: mixed must have %lld columns per row, 8-byte aligned rows", width);
+    if (total_tokens <= 0) return total_tokens == 0 ? S1_OK : s1_fail(ctx, S1_EINVAL, "s1_delta_inputs: negative token count");
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    const long long warps = static_cast<long long>(total_tokens) * value_heads;
+    s1_delta_inputs_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, ctx->stream>>>(
+        static_cast<const __nv_bfloat16*>(mixed), ldm, static_cast<const __nv_bfloat16*>(b_proj), static_cast<const __nv_bfloat16*>(a_proj),
+        ldba, dt_bias, neg_exp_a, total_tokens, key_heads, value_heads, q, k, v, g, beta);
+    S1_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return S1_OK;
+}
+
+extern "C" int s1_delta_finish(s1_ctx* ctx, const float* o, const void* z, long long ldz, const void* norm_weight, float eps,
+                               int total_tokens, int value_heads, void* y, long long ldy) {
+    if (!ctx) return S1_EINVAL;
+    if (!o || !z || !norm_weight || !y) return s1_fail(ctx, S1_EINVAL, "s1_delta_finish: null pointer");
+    const long long width = 1LL * value_heads * 128;
+    if (value_heads < 1 || ldz < width || ldy < width || (ldz % 4) || (ldy % 4) || !al16(o) || !al16(z) || !al16(y))
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_finish: z and y need %lld columns per row, 8-byte aligned rows", width);
+    if (total_tokens <= 0) return total_tokens == 0 ? S1_OK : s1_fail(ctx, S1_EINVAL, "s1_delta_finish: negative token count");
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    const long long warps = static_cast<long long>(total_tokens) * value_heads;
+    s1_delta_finish_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, ctx->stream>>>(
+        o, static_cast<const __nv_bfloat16*>(z), ldz, static_cast<const __nv_bfloat16*>(norm_weight), eps, total_tokens, value_heads,
+        static_cast<__nv_bfloat16*>(y), ldy);
+    S1_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return S1_OK;
+}
+
+extern "C" size_t s1_gated_delta_rule_workspace(int num_seqs, int total_tokens, int value_heads) {
+    if (num_seqs < 0 || total_tokens < 0 || value_heads < 1) return 0;
+    const size_t th = static_cast<size_t>(total_tokens) * value_heads;
+    // q, k, v, o (f32 [T, Hv, 128]) + g, beta (f32 [T, Hv]) + the recurrence's own workspace
+    return up(th * 128 * 4, 1024) * 4 + up(th * 4, 1024) * 2 + s1_delta_rule_chunked_workspace(num_seqs, total_tokens, value_heads);
+}
+
+extern "C" int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const void* b_proj, const void* a_proj,
+                                   long long ldba, const float* dt_bias, const float* neg_exp_a, const void* z, long long ldz,
+                                   const void* norm_weight, float eps, const int32_t* cu_seqlens_host, int num_seqs,
+                                   int total_tokens, int key_heads, int value_heads, void* y, long long ldy, void* workspace,
+                                   size_t workspace_bytes) {
+    if (!ctx) return S1_EINVAL;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 1023u))
+        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: the workspace must be 1024-byte aligned device memory");
+    if (workspace_bytes < s1_gated_delta_rule_workspace(num_seqs, total_tokens, value_heads))
+        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: workspace of %zu bytes, %zu needed", workspace_bytes,
+                       s1_gated_delta_rule_workspace(num_seqs, total_tokens, value_heads));
+    if (total_tokens == 0) return S1_OK;
+    const size_t th = static_cast<size_t>(total_tokens) * value_heads;
+    const size_t big = up(th * 128 * 4, 1024), small = up(th * 4, 1024);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    float* q = reinterpret_cast<float*>(ws);
+    float* k = reinterpret_cast<float*>(ws + big);
+    float* v = reinterpret_cast<float*>(ws + 2 * big);
+    float* o = reinterpret_cast<float*>(ws + 3 * big);
+    float* g = reinterpret_cast<float*>(ws + 4 * big);
+    float* beta = reinterpret_cast<float*>(ws + 4 * big + small);
+    uint8_t* rest = ws + 4 * big + 2 * small;
+    int rc = s1_delta_inputs(ctx, mixed, ldm, b_proj, a_proj, ldba, dt_bias, neg_exp_a, total_tokens, key_heads, value_heads, q, k, v, g, beta);
+    if (rc) return rc;
+    rc = s1_delta_rule_chunked(ctx, q, k, v, g, beta, cu_seqlens_host, num_seqs, total_tokens, value_heads, 128, 128, o, rest,
+                               workspace_bytes - (4 * big + 2 * small));
+    if (rc) return rc;
+    return s1_delta_finish(ctx, o, z, ldz, norm_weight, eps, total_tokens, value_heads, y, ldy);
+}

@@ -107,3 +107,55 @@ def chunked_delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: tor
     out = delta_rule_packed(tok(q), tok(k), tok(v), g.transpose(1, 2).reshape(B * L, H).contiguous(),
                             beta.transpose(1, 2).reshape(B * L, H).contiguous(), cu)
     return out.reshape(B, L, H, Dv)
+
+
+# ------------------------------------------------------------------------------------------------ linear attention
+def _bf16(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(-1) != 1:
+        raise ValueError(f"{name} must be a bf16 CUDA tensor with contiguous rows (no CPU fallback)")
+
+
+def conv_silu(x: torch.Tensor, weight: torch.Tensor, positions: torch.Tensor, ctx: Optional[device.Context] = None) -> torch.Tensor:
+    """`cuda_conv_silu(projected, conv)` (src/archs/qwen35_text.rs:652-735) on the packed layout: x `[T, C]` bf16,
+    weight `[C, 1, taps]` bf16, positions int32 `[T]` (token index inside its sequence)."""
+    _bf16(x, "x")
+    _bf16(weight, "weight")
+    T, Cc = x.shape
+    w = weight.reshape(Cc, -1).contiguous()
+    y = torch.empty((T, Cc), dtype=torch.bfloat16, device=x.device)
+    if ctx is None:
+        ctx = device.load(x.device.index)
+    ctx.check(ctx._lib.s1_conv_silu(ctx.handle, C.c_void_p(x.data_ptr()), x.stride(0), C.c_void_p(w.data_ptr()),
+                                    C.c_void_p(positions.data_ptr()), T, Cc, w.shape[1], C.c_void_p(y.data_ptr()), y.stride(0)))
+    return y
+
+
+class LinearAttention:
+    """`LinearAttention` (src/archs/qwen35_text.rs:414-630) on a packed batch, same member names: `qkv`, `z`, `b`,
+    `a`, `output` (Linear), `conv` `[C, 1, taps]`, `decay` (= -exp(A_log), f32), `dt_bias` (f32), `norm` `[128]`.
+    Key and value head dim 128. `forward(x, batch)` takes `x [T, hidden]` bf16 and the `PackedBatch` that produced it."""
+
+    def __init__(self, qkv: Linear, z: Linear, b: Linear, a: Linear, conv: torch.Tensor, decay: torch.Tensor,
+                 dt_bias: torch.Tensor, norm: torch.Tensor, output: Linear, key_heads: int, value_heads: int, eps: float):
+        self.qkv, self.z, self.b, self.a, self.output = qkv, z, b, a, output
+        self.conv, self.decay, self.dt_bias, self.norm = conv, decay.float().contiguous(), dt_bias.float().contiguous(), norm
+        self.key_heads, self.value_heads, self.eps = key_heads, value_heads, eps
+
+    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        import numpy as np
+        ctx = device.load(x.device.index)
+        T = x.shape[0]
+        cu = np.ascontiguousarray(cu_seqlens_host, dtype=np.int32)
+        mixed = conv_silu(self.qkv.forward(x), self.conv, positions, ctx)         # project_and_mix (:515-526)
+        zz, bb, aa = self.z.forward(x), self.b.forward(x), self.a.forward(x)
+        y = torch.empty((T, self.value_heads * 128), dtype=torch.bfloat16, device=x.device)
+        need = int(ctx._lib.s1_gated_delta_rule_workspace(len(cu) - 1, T, self.value_heads))
+        ws = _workspace(x.device, need)
+        ptr = (ws.data_ptr() + 1023) // 1024 * 1024
+        rc = ctx._lib.s1_gated_delta_rule(
+            ctx.handle, C.c_void_p(mixed.data_ptr()), mixed.stride(0), C.c_void_p(bb.data_ptr()), C.c_void_p(aa.data_ptr()),
+            bb.stride(0), C.c_void_p(self.dt_bias.data_ptr()), C.c_void_p(self.decay.data_ptr()), C.c_void_p(zz.data_ptr()),
+            zz.stride(0), C.c_void_p(self.norm.data_ptr()), C.c_float(self.eps), cu.ctypes.data_as(C.POINTER(C.c_int32)),
+            len(cu) - 1, T, self.key_heads, self.value_heads, C.c_void_p(y.data_ptr()), y.stride(0), C.c_void_p(ptr), need)
+        ctx.check(rc)
+        return self.output.forward(y, residual=residual)                           # out_proj (+ the layer's residual, :938)

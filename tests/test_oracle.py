@@ -151,3 +151,30 @@ def test_golden_delta_rule_frozen():
         c = oracle.chunked_delta_rule(tr(d["q"]), tr(d["k"]), tr(d["v"]), d["g"][sl].t().unsqueeze(0).contiguous(),
                                       d["beta"][sl].t().unsqueeze(0).contiguous())
         assert (c[0] - d["out"][sl]).abs().max() < 1e-4
+
+
+def test_conv_silu_inputs_of_the_reference_kernel_test():
+    """Inputs of `conv_cuda_matches_candle_across_batches_and_padding` (src/archs/qwen35_text.rs:1264-1318):
+    B2, L7, C31, K4, closed-form values; the vectorised oracle against a tap-by-tap scalar loop, 1e-3 as there."""
+    B, L, Cc, K = 2, 7, 31, 4
+    x = torch.tensor([((i * 17 % 41) - 20.0) * 0.04 for i in range(B * L * Cc)]).reshape(B, L, Cc)
+    w = torch.tensor([((i * 11 % 23) - 11.0) * 0.02 for i in range(Cc * K)]).reshape(Cc, 1, K)
+    for dt in ("f32", "bf16"):
+        got = oracle.causal_conv_silu(x.to(torch.bfloat16) if dt == "bf16" else x, w.to(torch.bfloat16) if dt == "bf16" else w, dtype=dt)
+        xx = x.to(torch.bfloat16).float() if dt == "bf16" else x
+        ww = w.to(torch.bfloat16).float().reshape(Cc, K) if dt == "bf16" else w.reshape(Cc, K)
+        want = torch.zeros(B, L, Cc)
+        for b in range(B):
+            for t in range(L):
+                for c in range(Cc):
+                    acc = 0.0
+                    for tap in range(K):
+                        src = t + tap - K + 1
+                        if src >= 0:
+                            acc += float(xx[b, src, c]) * float(ww[c, tap])
+                    want[b, t, c] = acc / (1.0 + math.exp(-acc))
+        assert (got - want).abs().max() < (1e-3 if dt == "f32" else 0.04)
+    # the first token of every batch row sees only its own tap (zero left padding per row)
+    got = oracle.causal_conv_silu(x, w, dtype="f32")
+    first = x[:, 0] * w.reshape(Cc, K)[:, K - 1]
+    assert torch.allclose(got[:, 0], first / (1 + torch.exp(-first)), atol=1e-6)
