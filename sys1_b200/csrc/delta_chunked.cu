@@ -104,6 +104,15 @@ struct PrepParams {
     __nv_bfloat16* p;    // [H * slots * 64 (i), 64 (j)]
     float* decay;        // [H * slots]  e^{G_last}
     int* status;
+    // fused-input form (s1_gated_delta_rule): q, k, v, g, beta are derived in the kernel from the layer's bf16 tensors
+    const __nv_bfloat16* mixed;  // [T, 2 * Hk * 128 + H * 128] = [q | k | v] after conv + SiLU
+    long long ldm;
+    const __nv_bfloat16* bproj;  // [T, H]
+    const __nv_bfloat16* aproj;  // [T, H]
+    long long ldba;
+    const float* dt_bias;        // [H]
+    const float* neg_exp_a;      // [H]
+    int Hk;                      // key heads (H value heads; key head = value head / (H / Hk))
 };
 
 constexpr int kAStride = 68;  // floats per row of the f32 A matrix in shared memory (16-byte rows, conflict-free)
@@ -112,6 +121,10 @@ constexpr int kPrepSmem = 2 * kTileBytes /*Kop*/ + 2 * kTileBytes /*Qop*/ + 2 * 
 
 constexpr int kPrepThreads = 256;  // two threads per stacked token row: each owns one half of the features / columns
 
+// FUSED = false: q, k (already normalised), v, g, beta given as f32 (the drop-in form of `chunked_delta_rule`).
+// FUSED = true : the steps of `delta_inputs` (src/archs/qwen35_text.rs:528-579) happen here: bf16 rows of the mixed
+//                projection are staged, L2-normalised per row by the warp that converts them, gates from a / b.
+template <bool FUSED>
 __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const PrepParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -158,20 +171,45 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     const SlotInfo s0 = p.slots[min(2 * static_cast<int>(blockIdx.x), p.num_slots - 1)];
     const SlotInfo s1 = (2 * blockIdx.x + 1 < p.num_slots) ? p.slots[2 * blockIdx.x + 1] : SlotInfo{0, 0};
     const uint32_t stage_q = xt, stage_k = top, stage_v = kop;
+    constexpr int kRowBytes = FUSED ? 256 : 512;  // staged row: 128 bf16 or 128 f32
+    const int kw = FUSED ? p.Hk * 128 : 0;
+    const int hk = FUSED ? head / (p.H / p.Hk) : 0;
+    if constexpr (FUSED) {
 #pragma unroll 4
-    for (int u = 0; u < 16; ++u) {
-        const int row = warp * 16 + u, ri = row & 63;
-        const SlotInfo sr = (row >> 6) ? s1 : s0;
-        const bool rv = ri < sr.len;
-        const long long base_f = rv ? (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane : 0;
-        cp_async16_zfill(stage_q + row * 512 + lane * 16, p.q + base_f, rv ? 16u : 0u);
-        cp_async16_zfill(stage_k + row * 512 + lane * 16, p.k + base_f, rv ? 16u : 0u);
+        for (int u = 0; u < 8; ++u) {  // one 16-byte piece per lane: two 256-byte rows per warp instruction
+            const int row = warp * 16 + 2 * u + (lane >> 4), ri = row & 63;
+            const SlotInfo sr = (row >> 6) ? s1 : s0;
+            const bool rv = ri < sr.len;
+            const long long src = rv ? static_cast<long long>(sr.tok_start + ri) * p.ldm + hk * 128 + 8 * (lane & 15) : 0;
+            cp_async16_zfill(stage_q + row * 256 + (lane & 15) * 16, p.mixed + src, rv ? 16u : 0u);
+            cp_async16_zfill(stage_k + row * 256 + (lane & 15) * 16, p.mixed + src + (rv ? kw : 0), rv ? 16u : 0u);
+        }
+    } else {
+#pragma unroll 4
+        for (int u = 0; u < 16; ++u) {
+            const int row = warp * 16 + u, ri = row & 63;
+            const SlotInfo sr = (row >> 6) ? s1 : s0;
+            const bool rv = ri < sr.len;
+            const long long base_f = rv ? (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane : 0;
+            cp_async16_zfill(stage_q + row * 512 + lane * 16, p.q + base_f, rv ? 16u : 0u);
+            cp_async16_zfill(stage_k + row * 512 + lane * 16, p.k + base_f, rv ? 16u : 0u);
+        }
     }
     cp_async_commit_group();
 
     // ---- gates: inclusive cumulative sum inside each chunk (two warps per chunk)
-    const float gi = valid ? p.g[tok * p.H + head] : 0.f;
-    const float bi = valid ? p.beta[tok * p.H + head] : 0.f;
+    float gi = 0.f, bi = 0.f;
+    if (valid) {
+        if constexpr (FUSED) {  // beta = sigmoid(b), g = softplus(a + dt_bias) * (-exp(A_log))  (:567-571)
+            const float bb = __bfloat162float(p.bproj[tok * p.ldba + head]);
+            const float aa = __bfloat162float(p.aproj[tok * p.ldba + head]) + p.dt_bias[head];
+            bi = 1.f / (1.f + expf(-bb));
+            gi = (fmaxf(aa, 0.f) + logf(expf(-fabsf(aa)) + 1.f)) * p.neg_exp_a[head];
+        } else {
+            gi = p.g[tok * p.H + head];
+            bi = p.beta[tok * p.H + head];
+        }
+    }
     float G = gi;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -203,12 +241,32 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     cp_async_wait_all();
     __syncthreads();
     const int tile = lane >> 4, col = (4 * lane) & 63;
+    // this lane's 4 features of a staged row; `norm` > 0: L2-normalise the row (sum over the warp) and scale by it
+    auto fetch4 = [&](uint32_t stage, int row, float norm) -> float4 {
+        float4 f;
+        if constexpr (FUSED) {
+            uint32_t lo, hi;
+            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(stage + row * 256 + lane * 8) : "memory");
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&lo), b = *reinterpret_cast<const __nv_bfloat162*>(&hi);
+            f = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+            if (norm > 0.f) {
+                float ss = f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float sc = norm / sqrtf(ss + 1e-6f);
+                f.x *= sc, f.y *= sc, f.z *= sc, f.w *= sc;
+            }
+        } else {
+            const uint4 raw = ld_shared_v4(stage + row * 512 + lane * 16);
+            f = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
+        }
+        return f;
+    };
 #pragma unroll 4
     for (int u = 0; u < 16; ++u) {  // Q first: its staging area is where beta e^G K goes next
         const int row = warp * 16 + u, ri = row & 63;
         const int rslot = 2 * blockIdx.x + (row >> 6);
-        const uint4 raw = ld_shared_v4(stage_q + row * 512 + lane * 16);
-        const float4 qq = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
+        const float4 qq = fetch4(stage_q, row, 0.08838834764831845f);  // l2norm(q) * 128^-1/2
         const float eg = egs[row];
         st_shared_v2(qop + tile * kTileBytes + sw128(row, col), pack2(qq.x, qq.y), pack2(qq.z, qq.w));
         if (rslot < p.num_slots) {
@@ -222,8 +280,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     for (int u = 0; u < 16; ++u) {
         const int row = warp * 16 + u, ri = row & 63;
         const int rslot = 2 * blockIdx.x + (row >> 6);
-        const uint4 raw = ld_shared_v4(stage_k + row * 512 + lane * 16);
-        const float4 kk = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
+        const float4 kk = fetch4(stage_k, row, 1.f);  // l2norm(k)
         const float el = egl[row], sk = bsh[row] * egs[row];
         const uint32_t off = tile * kTileBytes + sw128(row, col);
         st_shared_v2(kop + off, pack2(kk.x, kk.y), pack2(kk.z, kk.w));
@@ -258,13 +315,24 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     ok = __all_sync(0xffffffffu, ok);
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
     // K and Q tiles are consumed: their 64 KB now stage the raw V rows, in flight while A and P are formed
+    if constexpr (FUSED) {
 #pragma unroll 4
-    for (int u = 0; u < 16; ++u) {
-        const int row = warp * 16 + u, ri = row & 63;
-        const SlotInfo sr = (row >> 6) ? s1 : s0;
-        const bool rv = ok && ri < sr.len;
-        const long long base_f = rv ? (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane : 0;
-        cp_async16_zfill(stage_v + row * 512 + lane * 16, p.v + base_f, rv ? 16u : 0u);
+        for (int u = 0; u < 8; ++u) {
+            const int row = warp * 16 + 2 * u + (lane >> 4), ri = row & 63;
+            const SlotInfo sr = (row >> 6) ? s1 : s0;
+            const bool rv = ok && ri < sr.len;
+            const long long src = rv ? static_cast<long long>(sr.tok_start + ri) * p.ldm + 2 * kw + head * 128 + 8 * (lane & 15) : 0;
+            cp_async16_zfill(stage_v + row * 256 + (lane & 15) * 16, p.mixed + src, rv ? 16u : 0u);
+        }
+    } else {
+#pragma unroll 4
+        for (int u = 0; u < 16; ++u) {
+            const int row = warp * 16 + u, ri = row & 63;
+            const SlotInfo sr = (row >> 6) ? s1 : s0;
+            const bool rv = ok && ri < sr.len;
+            const long long base_f = rv ? (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane : 0;
+            cp_async16_zfill(stage_v + row * 512 + lane * 16, p.v + base_f, rv ? 16u : 0u);
+        }
     }
     cp_async_commit_group();
     if (ok) {
@@ -309,10 +377,9 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
 #pragma unroll 4
         for (int u = 0; u < 32; ++u) {
             const int row = q4 * 32 + u;
-            const uint4 raw = ld_shared_v4(stage_v + row * 512 + lane * 16);
+            const float4 vv = fetch4(stage_v, row, 0.f);
             const float be = bsh[row];
-            st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(__uint_as_float(raw.x) * be, __uint_as_float(raw.y) * be),
-                         pack2(__uint_as_float(raw.z) * be, __uint_as_float(raw.w) * be));
+            st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(vv.x * be, vv.y * be), pack2(vv.z * be, vv.w * be));
         }
     } else {
         float t[64];
@@ -657,28 +724,16 @@ extern "C" size_t s1_delta_rule_chunked_workspace(int num_seqs, int total_tokens
     return layout(num_seqs, max_slots, heads).total;
 }
 
-extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const float* v, const float* g,
-                                     const float* beta, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens,
-                                     int heads, int key_dim, int value_dim, float* out, void* workspace,
-                                     size_t workspace_bytes) {
-    if (!ctx) return S1_EINVAL;
-    if (!q || !k || !v || !g || !beta || !cu_seqlens_host || !out || !workspace)
-        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: null pointer");
-    if (key_dim != kD || value_dim != kD)
-        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: key_dim and value_dim must be 128 (got %d, %d); use s1_delta_rule", key_dim, value_dim);
-    if (num_seqs < 0 || heads < 1 || total_tokens < 0) return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: bad sizes");
-    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
-         reinterpret_cast<uintptr_t>(workspace)) & 15u)
-        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: q, k, v and the workspace must be 16-byte aligned");
+// Shared host path of the two entry points: chunk tables, prep (FUSED or not), scan.
+static int run_chunked(s1_ctx* ctx, const char* who, PrepParams pp, bool fused, const int32_t* cu_seqlens_host, int num_seqs,
+                       int total_tokens, int heads, float* out, void* workspace, size_t workspace_bytes) {
     if (num_seqs == 0 || total_tokens == 0) return S1_OK;
     if (cu_seqlens_host[0] != 0 || cu_seqlens_host[num_seqs] != total_tokens)
-        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: cu_seqlens must run from 0 to total_tokens");
+        return s1_fail(ctx, S1_EINVAL, "%s: cu_seqlens must run from 0 to total_tokens", who);
     const int max_slots = total_tokens / kC + num_seqs + 1;
     const WorkspaceLayout L = layout(num_seqs, max_slots, heads);
-    if (workspace_bytes < L.total)
-        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: workspace of %zu bytes, %zu needed", workspace_bytes, L.total);
-    if ((reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0)
-        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: the workspace must be 1024-byte aligned");
+    if (workspace_bytes < L.total) return s1_fail(ctx, S1_EINVAL, "%s: workspace of %zu bytes, %zu needed", who, workspace_bytes, L.total);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0) return s1_fail(ctx, S1_EINVAL, "%s: the workspace must be 1024-byte aligned", who);
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
 
     // chunk tables, built on the host from the host copy of the offsets
@@ -688,7 +743,7 @@ extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k
     int num_slots = 0;
     for (int s = 0; s < num_seqs; ++s) {
         const int a = cu_seqlens_host[s], b = cu_seqlens_host[s + 1];
-        if (b < a) return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: cu_seqlens must not decrease");
+        if (b < a) return s1_fail(ctx, S1_EINVAL, "%s: cu_seqlens must not decrease", who);
         seqs[s].first_slot = num_slots;
         seqs[s].num_chunks = (b - a + kC - 1) / kC;
         for (int t = a; t < b; t += kC) slots[num_slots++] = SlotInfo{t, (b - t < kC) ? b - t : kC};
@@ -697,13 +752,10 @@ extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k
     // the scan kernel runs one CTA per (sequence, head): start the longest sequences first
     std::stable_sort(seqs, seqs + num_seqs, [](const SeqInfo& a, const SeqInfo& b) { return a.num_chunks > b.num_chunks; });
     uint8_t* ws = static_cast<uint8_t*>(workspace);
+    // (copies from pageable memory are staged before the call returns, so the host buffer can be reused at once)
     S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.slots_off, slots, sizeof(SlotInfo) * num_slots, cudaMemcpyHostToDevice, ctx->stream));
     S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.seqs_off, seqs, sizeof(SeqInfo) * num_seqs, cudaMemcpyHostToDevice, ctx->stream));
-    // the tables are read by the kernels after these copies on the same stream; the host buffer is reused by the
-    // next call only after the copies were issued from pageable memory (which stages them before returning)
 
-    PrepParams pp;
-    pp.q = q, pp.k = k, pp.v = v, pp.g = g, pp.beta = beta;
     pp.slots = reinterpret_cast<const SlotInfo*>(ws + L.slots_off);
     pp.num_slots = num_slots, pp.H = heads;
     pp.wq = reinterpret_cast<__nv_bfloat16*>(ws + L.wq_off);
@@ -714,11 +766,14 @@ extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k
     pp.status = ctx->status_dev;
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
-        S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem));
+        S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_prep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem));
+        S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_prep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem));
         S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmem));
         configured_device = ctx->device;
     }
-    s1_delta_prep_kernel<<<dim3((num_slots + 1) / 2, heads), kPrepThreads, kPrepSmem, ctx->stream>>>(pp);
+    const dim3 pgrid((num_slots + 1) / 2, heads);
+    if (fused) s1_delta_prep_kernel<true><<<pgrid, kPrepThreads, kPrepSmem, ctx->stream>>>(pp);
+    else s1_delta_prep_kernel<false><<<pgrid, kPrepThreads, kPrepSmem, ctx->stream>>>(pp);
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
 
@@ -743,4 +798,62 @@ extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return S1_OK;
+}
+
+extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const float* v, const float* g,
+                                     const float* beta, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens,
+                                     int heads, int key_dim, int value_dim, float* out, void* workspace,
+                                     size_t workspace_bytes) {
+    if (!ctx) return S1_EINVAL;
+    if (!q || !k || !v || !g || !beta || !cu_seqlens_host || !out || !workspace)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: null pointer");
+    if (key_dim != kD || value_dim != kD)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: key_dim and value_dim must be 128 (got %d, %d); use s1_delta_rule", key_dim, value_dim);
+    if (num_seqs < 0 || heads < 1 || total_tokens < 0) return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: bad sizes");
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u)
+        return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: q, k, v must be 16-byte aligned");
+    PrepParams pp = {};
+    pp.q = q, pp.k = k, pp.v = v, pp.g = g, pp.beta = beta;
+    return run_chunked(ctx, "s1_delta_rule_chunked", pp, false, cu_seqlens_host, num_seqs, total_tokens, heads, out, workspace, workspace_bytes);
+}
+
+extern "C" int s1_delta_finish(s1_ctx* ctx, const float* o, const void* z, long long ldz, const void* norm_weight, float eps,
+                               int total_tokens, int value_heads, void* y, long long ldy);
+
+extern "C" size_t s1_gated_delta_rule_workspace(int num_seqs, int total_tokens, int value_heads) {
+    if (num_seqs < 0 || total_tokens < 0 || value_heads < 1) return 0;
+    // the recurrence output o (f32 [T, Hv, 128]) + the chunk workspace
+    return align_up(static_cast<size_t>(total_tokens) * value_heads * 128 * 4, 1024) +
+           s1_delta_rule_chunked_workspace(num_seqs, total_tokens, value_heads);
+}
+
+extern "C" int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const void* b_proj, const void* a_proj,
+                                   long long ldba, const float* dt_bias, const float* neg_exp_a, const void* z, long long ldz,
+                                   const void* norm_weight, float eps, const int32_t* cu_seqlens_host, int num_seqs,
+                                   int total_tokens, int key_heads, int value_heads, void* y, long long ldy, void* workspace,
+                                   size_t workspace_bytes) {
+    if (!ctx) return S1_EINVAL;
+    if (!mixed || !b_proj || !a_proj || !dt_bias || !neg_exp_a || !z || !norm_weight || !cu_seqlens_host || !y || !workspace)
+        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: null pointer");
+    if (key_heads < 1 || value_heads < key_heads || value_heads % key_heads)
+        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: value_heads must be a multiple of key_heads");
+    const long long width = 2LL * key_heads * 128 + 1LL * value_heads * 128;
+    if (ldm < width || (ldm % 8) || ldba < value_heads || (reinterpret_cast<uintptr_t>(mixed) & 15u))
+        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: mixed needs %lld columns per row and 16-byte aligned rows", width);
+    if (reinterpret_cast<uintptr_t>(workspace) & 1023u)
+        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: the workspace must be 1024-byte aligned device memory");
+    if (workspace_bytes < s1_gated_delta_rule_workspace(num_seqs, total_tokens, value_heads))
+        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: workspace of %zu bytes, %zu needed", workspace_bytes,
+                       s1_gated_delta_rule_workspace(num_seqs, total_tokens, value_heads));
+    if (total_tokens == 0) return S1_OK;
+    const size_t obytes = align_up(static_cast<size_t>(total_tokens) * value_heads * 128 * 4, 1024);
+    float* o = static_cast<float*>(workspace);
+    PrepParams pp = {};
+    pp.mixed = static_cast<const __nv_bfloat16*>(mixed), pp.ldm = ldm;
+    pp.bproj = static_cast<const __nv_bfloat16*>(b_proj), pp.aproj = static_cast<const __nv_bfloat16*>(a_proj), pp.ldba = ldba;
+    pp.dt_bias = dt_bias, pp.neg_exp_a = neg_exp_a, pp.Hk = key_heads;
+    int rc = run_chunked(ctx, "s1_gated_delta_rule", pp, true, cu_seqlens_host, num_seqs, total_tokens, value_heads, o,
+                         static_cast<uint8_t*>(workspace) + obytes, workspace_bytes - obytes);
+    if (rc) return rc;
+    return s1_delta_finish(ctx, o, z, ldz, norm_weight, eps, total_tokens, value_heads, y, ldy);
 }

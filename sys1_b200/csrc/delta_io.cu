@@ -4,7 +4,7 @@
 //   s1_delta_inputs   split / head-repeat / L2-norm / gates  (`delta_inputs`, src/archs/qwen35_text.rs:528-579;
 //                     the Metal build fuses the same steps in src/kernels/qwen35.metal:146-203)
 //   s1_delta_finish   per-head RMS norm x weight x SiLU(z), cast to bf16 (`finish_delta`, :597-626, up to out_proj)
-//   s1_gated_delta_rule = s1_delta_inputs -> s1_delta_rule_chunked -> s1_delta_finish
+//   (s1_gated_delta_rule, in delta_chunked.cu, does the first of these inside its own first kernel and calls the last)
 // All three are HBM-bound streaming kernels: 16-byte accesses, one warp per (token, head) row where a
 // reduction over the head dimension is needed.
 #include <cuda_bf16.h>
@@ -12,12 +12,6 @@
 #include <stdint.h>
 
 #include "context.h"
-
-extern "C" size_t s1_delta_rule_chunked_workspace(int num_seqs, int total_tokens, int heads);
-extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const float* v, const float* g,
-                                     const float* beta, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens,
-                                     int heads, int key_dim, int value_dim, float* out, void* workspace,
-                                     size_t workspace_bytes);
 
 namespace {
 
@@ -129,7 +123,6 @@ __global__ void __launch_bounds__(256) s1_delta_finish_kernel(const float* __res
 }
 
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-inline size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
 
@@ -190,41 +183,4 @@ extern "C" int s1_delta_finish(s1_ctx* ctx, const float* o, const void* z, long 
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return S1_OK;
-}
-
-extern "C" size_t s1_gated_delta_rule_workspace(int num_seqs, int total_tokens, int value_heads) {
-    if (num_seqs < 0 || total_tokens < 0 || value_heads < 1) return 0;
-    const size_t th = static_cast<size_t>(total_tokens) * value_heads;
-    // q, k, v, o (f32 [T, Hv, 128]) + g, beta (f32 [T, Hv]) + the recurrence's own workspace
-    return up(th * 128 * 4, 1024) * 4 + up(th * 4, 1024) * 2 + s1_delta_rule_chunked_workspace(num_seqs, total_tokens, value_heads);
-}
-
-extern "C" int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const void* b_proj, const void* a_proj,
-                                   long long ldba, const float* dt_bias, const float* neg_exp_a, const void* z, long long ldz,
-                                   const void* norm_weight, float eps, const int32_t* cu_seqlens_host, int num_seqs,
-                                   int total_tokens, int key_heads, int value_heads, void* y, long long ldy, void* workspace,
-                                   size_t workspace_bytes) {
-    if (!ctx) return S1_EINVAL;
-    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 1023u))
-        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: the workspace must be 1024-byte aligned device memory");
-    if (workspace_bytes < s1_gated_delta_rule_workspace(num_seqs, total_tokens, value_heads))
-        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: workspace of %zu bytes, %zu needed", workspace_bytes,
-                       s1_gated_delta_rule_workspace(num_seqs, total_tokens, value_heads));
-    if (total_tokens == 0) return S1_OK;
-    const size_t th = static_cast<size_t>(total_tokens) * value_heads;
-    const size_t big = up(th * 128 * 4, 1024), small = up(th * 4, 1024);
-    uint8_t* ws = static_cast<uint8_t*>(workspace);
-    float* q = reinterpret_cast<float*>(ws);
-    float* k = reinterpret_cast<float*>(ws + big);
-    float* v = reinterpret_cast<float*>(ws + 2 * big);
-    float* o = reinterpret_cast<float*>(ws + 3 * big);
-    float* g = reinterpret_cast<float*>(ws + 4 * big);
-    float* beta = reinterpret_cast<float*>(ws + 4 * big + small);
-    uint8_t* rest = ws + 4 * big + 2 * small;
-    int rc = s1_delta_inputs(ctx, mixed, ldm, b_proj, a_proj, ldba, dt_bias, neg_exp_a, total_tokens, key_heads, value_heads, q, k, v, g, beta);
-    if (rc) return rc;
-    rc = s1_delta_rule_chunked(ctx, q, k, v, g, beta, cu_seqlens_host, num_seqs, total_tokens, value_heads, 128, 128, o, rest,
-                               workspace_bytes - (4 * big + 2 * small));
-    if (rc) return rc;
-    return s1_delta_finish(ctx, o, z, ldz, norm_weight, eps, total_tokens, value_heads, y, ldy);
 }
