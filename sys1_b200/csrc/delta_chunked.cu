@@ -241,32 +241,48 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     cp_async_wait_all();
     __syncthreads();
     const int tile = lane >> 4, col = (4 * lane) & 63;
-    // this lane's 4 features of a staged row; `norm` > 0: L2-normalise the row (sum over the warp) and scale by it
-    auto fetch4 = [&](uint32_t stage, int row, float norm) -> float4 {
-        float4 f;
+    // this lane's 4 features of a staged row
+    auto fetch4 = [&](uint32_t stage, int row) -> float4 {
         if constexpr (FUSED) {
             uint32_t lo, hi;
             asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(stage + row * 256 + lane * 8) : "memory");
             const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&lo), b = *reinterpret_cast<const __nv_bfloat162*>(&hi);
-            f = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
-            if (norm > 0.f) {
-                float ss = f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                const float sc = norm / sqrtf(ss + 1e-6f);
-                f.x *= sc, f.y *= sc, f.z *= sc, f.w *= sc;
-            }
+            return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
         } else {
             const uint4 raw = ld_shared_v4(stage + row * 512 + lane * 16);
-            f = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
+            return make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
         }
-        return f;
     };
-#pragma unroll 4
+    // fused form: L2 norms of this warp's 16 q rows and 16 k rows, all 32 warp reductions interleaved
+    // (q = l2norm(q) * 128^-1/2, k = l2norm(k), 1e-6 inside the root: src/archs/qwen35_text.rs:560-565)
+    float qsc[16], ksc[16];
+    if constexpr (FUSED) {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const float4 a = fetch4(stage_q, warp * 16 + u), b = fetch4(stage_k, warp * 16 + u);
+            qsc[u] = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            ksc[u] = b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                qsc[u] += __shfl_xor_sync(0xffffffffu, qsc[u], o);
+                ksc[u] += __shfl_xor_sync(0xffffffffu, ksc[u], o);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            qsc[u] = 0.08838834764831845f * rsqrtf(qsc[u] + 1e-6f);
+            ksc[u] = rsqrtf(ksc[u] + 1e-6f);
+        }
+    }
+#pragma unroll
     for (int u = 0; u < 16; ++u) {  // Q first: its staging area is where beta e^G K goes next
         const int row = warp * 16 + u, ri = row & 63;
         const int rslot = 2 * blockIdx.x + (row >> 6);
-        const float4 qq = fetch4(stage_q, row, 0.08838834764831845f);  // l2norm(q) * 128^-1/2
+        float4 qq = fetch4(stage_q, row);
+        if constexpr (FUSED) qq.x *= qsc[u], qq.y *= qsc[u], qq.z *= qsc[u], qq.w *= qsc[u];
         const float eg = egs[row];
         st_shared_v2(qop + tile * kTileBytes + sw128(row, col), pack2(qq.x, qq.y), pack2(qq.z, qq.w));
         if (rslot < p.num_slots) {
@@ -276,11 +292,12 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
         }
     }
     __syncthreads();
-#pragma unroll 4
+#pragma unroll
     for (int u = 0; u < 16; ++u) {
         const int row = warp * 16 + u, ri = row & 63;
         const int rslot = 2 * blockIdx.x + (row >> 6);
-        const float4 kk = fetch4(stage_k, row, 1.f);  // l2norm(k)
+        float4 kk = fetch4(stage_k, row);
+        if constexpr (FUSED) kk.x *= ksc[u], kk.y *= ksc[u], kk.z *= ksc[u], kk.w *= ksc[u];
         const float el = egl[row], sk = bsh[row] * egs[row];
         const uint32_t off = tile * kTileBytes + sw128(row, col);
         st_shared_v2(kop + off, pack2(kk.x, kk.y), pack2(kk.z, kk.w));
@@ -377,7 +394,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
 #pragma unroll 4
         for (int u = 0; u < 32; ++u) {
             const int row = q4 * 32 + u;
-            const float4 vv = fetch4(stage_v, row, 0.f);
+            const float4 vv = fetch4(stage_v, row);
             const float be = bsh[row];
             st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(vv.x * be, vv.y * be), pack2(vv.z * be, vv.w * be));
         }
