@@ -1,0 +1,112 @@
+"""Oracle for the ModernBERT encoder forward (test infrastructure only; see the package docstring).
+
+Restates `Encoder::forward` / `Layer::forward` / `Attention::forward` of src/archs/modernbert.rs (:958-989,
+:857-887, :176-192) for sequences without padding, one sequence at a time (which is what the reference's padded
+batch computes for each row once padded keys are masked out):
+  x = LN(tok_emb[ids]); per layer i: n = x (i == 0, no attn_norm weight: :846-851) or LN(x);
+  qkv = n Wqkv^T -> [L, 3, H, D]; rotate-half RoPE on q, k with f32 tables, theta global / local (:58-110, :908-929);
+  a = softmax(q k^T / sqrt(D) + mask) v, mask = -10000 where |i - j| > local_attention / 2 on local layers
+  (i % global_attn_every_n_layers != 0, :920, :973-977, :1058-1076); x = x + a Wo^T; m = LN(x) Wi^T;
+  x = x + geglu(m) Wout^T; finally LN(x) (:988).
+LayerNorm has a weight and no bias (`LayerNorm::new_no_bias`, :1006-1034).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Sequence
+
+import torch
+
+from .projection import geglu, linear, round_bf16
+
+MASK_VALUE = -10_000.0  # ATTENTION_MASK_VALUE, src/archs/modernbert.rs:23
+
+
+@dataclass(frozen=True)
+class EncoderConfig:
+    vocab_size: int = 50368
+    hidden_size: int = 768
+    num_hidden_layers: int = 22
+    num_attention_heads: int = 12
+    intermediate_size: int = 1152
+    layer_norm_eps: float = 1e-5
+    global_attn_every_n_layers: int = 3
+    local_attention: int = 128
+    global_rope_theta: float = 160000.0
+    local_rope_theta: float = 10000.0
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+
+def init_weights(cfg: EncoderConfig, seed: int) -> Dict[str, torch.Tensor]:
+    """Random-init weights N(0, 0.02) from `seed`, norm weights 1 (float32; cast by the caller)."""
+    g = torch.Generator().manual_seed(seed)
+    w = {"tok_embeddings": torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * 0.02,
+         "embeddings_norm": torch.ones(cfg.hidden_size), "final_norm": torch.ones(cfg.hidden_size)}
+    for i in range(cfg.num_hidden_layers):
+        p = f"layers.{i}."
+        w[p + "Wqkv"] = torch.randn(3 * cfg.hidden_size, cfg.hidden_size, generator=g) * 0.02
+        w[p + "Wo"] = torch.randn(cfg.hidden_size, cfg.hidden_size, generator=g) * 0.02
+        w[p + "Wi"] = torch.randn(2 * cfg.intermediate_size, cfg.hidden_size, generator=g) * 0.02
+        w[p + "mlp_Wo"] = torch.randn(cfg.hidden_size, cfg.intermediate_size, generator=g) * 0.02
+        if i > 0:
+            w[p + "attn_norm"] = torch.ones(cfg.hidden_size)
+        w[p + "mlp_norm"] = torch.ones(cfg.hidden_size)
+    return w
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: str) -> torch.Tensor:
+    x = x.to(torch.float32)
+    mean = x.mean(-1, keepdim=True)
+    var = (x - mean).square().mean(-1, keepdim=True)
+    y = (x - mean) / (var + eps).sqrt() * weight.to(torch.float32)
+    return round_bf16(y) if dtype == "bf16" else y
+
+
+def rope_tables(cfg: EncoderConfig, theta: float, length: int):
+    d = cfg.head_dim
+    inv = torch.tensor([1.0 / (theta ** (j / d)) for j in range(0, d, 2)], dtype=torch.float32)
+    freqs = torch.arange(length, dtype=torch.float32).unsqueeze(1) * inv.unsqueeze(0)
+    return freqs.cos(), freqs.sin()
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotate-half on `[L, H, D]` with tables `[L, D/2]` (candle `rope`; kernel src/kernels/modernbert.cu:31-62)."""
+    h = x.shape[-1] // 2
+    x1, x2 = x[..., :h], x[..., h:]
+    c, s = cos.unsqueeze(1), sin.unsqueeze(1)
+    return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1)
+
+
+def encoder_forward(ids: torch.Tensor, w: Dict[str, torch.Tensor], cfg: EncoderConfig, dtype: str = "f32",
+                    collect: bool = False):
+    """One unpadded sequence `ids [L]` -> final hidden `[L, hidden]` (float32 values of the requested precision);
+    with `collect`, also the list of hidden states after every layer."""
+    r = (lambda t: round_bf16(t)) if dtype == "bf16" else (lambda t: t)
+    L = ids.shape[0]
+    H, D = cfg.num_attention_heads, cfg.head_dim
+    x = layer_norm(w["tok_embeddings"][ids].to(torch.float32), w["embeddings_norm"], cfg.layer_norm_eps, dtype)
+    idx = torch.arange(L)
+    local_mask = torch.where((idx.unsqueeze(0) - idx.unsqueeze(1)).abs() > cfg.local_attention // 2, MASK_VALUE, 0.0)
+    states: List[torch.Tensor] = []
+    for i in range(cfg.num_hidden_layers):
+        p = f"layers.{i}."
+        local = i % cfg.global_attn_every_n_layers != 0
+        n = x if i == 0 else layer_norm(x, w[p + "attn_norm"], cfg.layer_norm_eps, dtype)
+        qkv = linear(n, w[p + "Wqkv"], dtype=dtype).reshape(L, 3, H, D)
+        cos, sin = rope_tables(cfg, cfg.local_rope_theta if local else cfg.global_rope_theta, L)
+        q, k, v = r(rope(qkv[:, 0], cos, sin)), r(rope(qkv[:, 1], cos, sin)), qkv[:, 2]
+        scores = r(torch.einsum("ihd,jhd->hij", r(q * D ** -0.5), k))
+        if local:
+            scores = scores + local_mask
+        probs = r(torch.softmax(scores, dim=-1))
+        attn = r(torch.einsum("hij,jhd->ihd", probs, v)).reshape(L, H * D)
+        x = linear(attn, w[p + "Wo"], residual=x, dtype=dtype)
+        m = geglu(linear(layer_norm(x, w[p + "mlp_norm"], cfg.layer_norm_eps, dtype), w[p + "Wi"], dtype=dtype), dtype)
+        x = linear(m, w[p + "mlp_Wo"], residual=x, dtype=dtype)
+        if collect:
+            states.append(x)
+    y = layer_norm(x, w["final_norm"], cfg.layer_norm_eps, dtype)
+    return (y, states) if collect else y

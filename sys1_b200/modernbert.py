@@ -46,3 +46,85 @@ class AttentionProjections:
     def out(self, attended: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """`attended.apply(&self.wo)` (:191) and, with `residual`, the layer's `x + ·` (:882-883)."""
         return self.wo.forward(attended, residual=residual)
+
+
+class Encoder:
+    """`Encoder::forward` (src/archs/modernbert.rs:958-989) on a token-packed batch. The four projections of every
+    layer run through the C ABI (Wqkv; Wo with the residual stream updated in place; Wi with GeGLU; MLP-out with the
+    residual stream updated in place). Everything else - embedding lookup, LayerNorm (no bias), RoPE, softmax
+    attention - is outside this repository's path and is done here with PyTorch operators, as harness code:
+    attention is `scaled_dot_product_attention` per sequence, with the +-`local_attention/2` band on local layers.
+
+    `weights`: dict with the names of `oracle.modernbert.init_weights` (bf16 CUDA tensors); `cfg`: any object with
+    the fields of `oracle.modernbert.EncoderConfig`."""
+
+    def __init__(self, weights, cfg):
+        self.cfg = cfg
+        self.w = weights
+        self.layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"layers.{i}."
+            self.layers.append((AttentionProjections(Linear(weights[p + "Wqkv"]), Linear(weights[p + "Wo"])),
+                                Mlp(Linear(weights[p + "Wi"]), Linear(weights[p + "mlp_Wo"]))))
+        self._tables = {}
+        self._bands = {}
+
+    def _rope_tables(self, theta: float, length: int, dev):
+        key = (theta, dev)
+        if key not in self._tables or self._tables[key][0].shape[0] < length:
+            d = self.cfg.hidden_size // self.cfg.num_attention_heads
+            inv = torch.tensor([1.0 / (theta ** (j / d)) for j in range(0, d, 2)], dtype=torch.float32, device=dev)
+            fr = torch.arange(max(length, 512), dtype=torch.float32, device=dev).unsqueeze(1) * inv.unsqueeze(0)
+            self._tables[key] = (fr.cos(), fr.sin())
+        return self._tables[key]
+
+    def _band(self, length: int, dev):
+        key = (length, dev)
+        if key not in self._bands:
+            idx = torch.arange(length, device=dev)
+            self._bands[key] = (idx.unsqueeze(0) - idx.unsqueeze(1)).abs() <= self.cfg.local_attention // 2
+        return self._bands[key]
+
+    def forward(self, ids: torch.Tensor, cu_seqlens, positions: torch.Tensor, collect: bool = False):
+        """ids int64 `[T]` (CUDA), cu_seqlens host int offsets `[B+1]`, positions int `[T]` (CUDA). Returns the final
+        hidden states `[T, hidden]` bf16 (and, with `collect`, the residual stream after every layer)."""
+        cfg = self.cfg
+        F = torch.nn.functional
+        H, D = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads
+        T = ids.shape[0]
+        dev = ids.device
+        eps = cfg.layer_norm_eps
+        ln = lambda t, name: F.layer_norm(t, (cfg.hidden_size,), self.w[name], None, eps)
+        x = ln(self.w["tok_embeddings"][ids], "embeddings_norm").contiguous()
+        bounds = [int(v) for v in cu_seqlens]
+        max_len = max((b - a for a, b in zip(bounds[:-1], bounds[1:])), default=0)
+        pos = positions.long()
+        states = []
+        for i, (proj, mlp) in enumerate(self.layers):
+            p = f"layers.{i}."
+            local = i % cfg.global_attn_every_n_layers != 0
+            n = x if i == 0 else ln(x, p + "attn_norm")
+            qkv = proj.qkv(n).view(T, 3, H, D)
+            cos, sin = self._rope_tables(cfg.local_rope_theta if local else cfg.global_rope_theta, max_len, dev)
+            c, s = cos[pos].unsqueeze(1), sin[pos].unsqueeze(1)
+
+            def rot(t):
+                t = t.float()
+                t1, t2 = t[..., : D // 2], t[..., D // 2:]
+                return torch.cat([t1 * c - t2 * s, t1 * s + t2 * c], dim=-1).to(torch.bfloat16)
+
+            q, k, v = rot(qkv[:, 0]), rot(qkv[:, 1]), qkv[:, 2]
+            attn = torch.empty((T, H * D), dtype=torch.bfloat16, device=dev)
+            for a, b in zip(bounds[:-1], bounds[1:]):
+                if a == b:
+                    continue
+                mask = self._band(b - a, dev) if local else None
+                o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1).unsqueeze(0), k[a:b].transpose(0, 1).unsqueeze(0),
+                                                   v[a:b].transpose(0, 1).unsqueeze(0), attn_mask=mask)
+                attn[a:b] = o[0].transpose(0, 1).reshape(b - a, H * D)
+            proj.wo.forward(attn, residual=x, out=x)                       # x += attn Wo^T
+            mlp.output.forward(mlp.gated(ln(x, p + "mlp_norm")), residual=x, out=x)   # x += geglu(LN(x) Wi^T) Wout^T
+            if collect:
+                states.append(x.clone())
+        y = ln(x, "final_norm")
+        return (y, states) if collect else y

@@ -178,3 +178,37 @@ def test_conv_silu_inputs_of_the_reference_kernel_test():
     got = oracle.causal_conv_silu(x, w, dtype="f32")
     first = x[:, 0] * w.reshape(Cc, K)[:, K - 1]
     assert torch.allclose(got[:, 0], first / (1 + torch.exp(-first)), atol=1e-6)
+
+
+def test_encoder_oracle_matches_an_independent_implementation():
+    """The ModernBERT encoder restatement against `transformers`' ModernBertModel (an independent implementation of
+    the same architecture, eager attention, f32) on random weights: agreement to 1e-4. The reference's own encoder
+    snapshot (src/archs/modernbert.rs:1445-1504) needs a Hugging Face checkpoint that is not available offline."""
+    transformers = pytest.importorskip("transformers")
+    cfg = oracle.EncoderConfig(vocab_size=500, hidden_size=128, num_hidden_layers=4, num_attention_heads=2,
+                               intermediate_size=192)
+    w = oracle.init_weights(cfg, 3)
+    g = torch.Generator().manual_seed(4)
+    for k in w:
+        if "norm" in k:
+            w[k] = w[k] + 0.1 * torch.randn(w[k].shape, generator=g)
+    hc = transformers.ModernBertConfig(
+        vocab_size=500, hidden_size=128, num_hidden_layers=4, num_attention_heads=2, intermediate_size=192,
+        max_position_embeddings=512, norm_eps=1e-5, norm_bias=False, global_attn_every_n_layers=3, local_attention=128,
+        global_rope_theta=160000.0, local_rope_theta=10000.0, attention_bias=False, mlp_bias=False,
+        attn_implementation="eager", embedding_dropout=0.0, mlp_dropout=0.0, attention_dropout=0.0, pad_token_id=0)
+    model = transformers.ModernBertModel(hc).eval().float()
+    sd = {"embeddings.tok_embeddings.weight": w["tok_embeddings"], "embeddings.norm.weight": w["embeddings_norm"],
+          "final_norm.weight": w["final_norm"]}
+    for i in range(4):
+        p = f"layers.{i}."
+        sd.update({p + "attn.Wqkv.weight": w[p + "Wqkv"], p + "attn.Wo.weight": w[p + "Wo"], p + "mlp.Wi.weight": w[p + "Wi"],
+                   p + "mlp.Wo.weight": w[p + "mlp_Wo"], p + "mlp_norm.weight": w[p + "mlp_norm"]})
+        if i > 0:
+            sd[p + "attn_norm.weight"] = w[p + "attn_norm"]
+    result = model.load_state_dict(sd, strict=False)
+    assert not result.missing_keys and not result.unexpected_keys
+    ids = torch.randint(1, 500, (180,), generator=g)  # longer than the 129-token band
+    with torch.no_grad():
+        ref = model(input_ids=ids.unsqueeze(0), attention_mask=torch.ones(1, 180, dtype=torch.long)).last_hidden_state[0]
+    assert (oracle.encoder_forward(ids, w, cfg) - ref).abs().max() < 1e-4
