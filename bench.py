@@ -141,6 +141,73 @@ def run_cpu_arm(tokens: int, steps: int, warmup: int, budget_s: float = 20.0):
     return FLOPS_PER_TOKEN * tokens / dt / 1e12, dt, len(times), torch.get_num_threads()
 
 
+def run_encoder(args, rank, world, local_rank):
+    """Secondary workload: ModernBERT-large-shaped encoder forward (28 layers, hidden 1024, 16 heads, GeGLU 2 x 2624,
+    window 128, global every 3rd layer) over packed batches of `--tokens` tokens with log-uniform lengths in
+    [8, 8192], one replica per GPU. The four projections of every layer go through the C ABI; attention, LayerNorm,
+    RoPE and the embedding lookup are PyTorch operators (harness code outside this repository's path), so the
+    tokens/s figure is an upper bound set largely by that harness attention."""
+    from types import SimpleNamespace
+    from sys1_b200 import batching, device, modernbert
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    cfg = SimpleNamespace(vocab_size=50368, hidden_size=1024, num_hidden_layers=28, num_attention_heads=16, intermediate_size=2624,
+                          layer_norm_eps=1e-5, global_attn_every_n_layers=3, local_attention=128, global_rope_theta=160000.0,
+                          local_rope_theta=10000.0)
+    g = torch.Generator(device=dev).manual_seed(1003)
+    mk = lambda *shape: (torch.randn(*shape, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    w = {"tok_embeddings": mk(cfg.vocab_size, cfg.hidden_size), "embeddings_norm": torch.ones(cfg.hidden_size, device=dev, dtype=torch.bfloat16),
+         "final_norm": torch.ones(cfg.hidden_size, device=dev, dtype=torch.bfloat16)}
+    for i in range(cfg.num_hidden_layers):
+        p = f"layers.{i}."
+        w[p + "Wqkv"], w[p + "Wo"] = mk(3 * cfg.hidden_size, cfg.hidden_size), mk(cfg.hidden_size, cfg.hidden_size)
+        w[p + "Wi"], w[p + "mlp_Wo"] = mk(2 * cfg.intermediate_size, cfg.hidden_size), mk(cfg.hidden_size, cfg.intermediate_size)
+        w[p + "attn_norm"] = torch.ones(cfg.hidden_size, device=dev, dtype=torch.bfloat16)
+        w[p + "mlp_norm"] = torch.ones(cfg.hidden_size, device=dev, dtype=torch.bfloat16)
+    enc = modernbert.Encoder(w, cfg)
+    ctx = device.load(local_rank)
+    T = args.tokens
+    lens = batching.synthetic_lengths(1003 + rank, 8, 8192, T, log_uniform=True)
+    batch, _ = batching.pack_next(lens, batching.BatcherConfig(token_budget=T))
+    ids = torch.randint(0, cfg.vocab_size, (T,), device=dev, generator=g)
+    pos = torch.from_numpy(batch.positions).to(dev)
+    warmup, steps = max(args.warmup, 3), min(args.steps, 20)
+    for _ in range(warmup):
+        enc.forward(ids, batch.cu_seqlens, pos)
+    ctx.sync()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        enc.forward(ids, batch.cu_seqlens, pos)
+    e1.record()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t[0])
+    if rank == 0:
+        flops_tok = 28 * 2 * (1024 * 3072 + 1024 * 1024 + 1024 * 5248 + 2624 * 1024)
+        print(json.dumps({"metric": "encoder tokens/s", "value": world * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                          "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": f"ModernBERT-large-shaped encoder forward, packed T={T}, lengths log-uniform [8,8192], "
+                                                 "projections through the C ABI, attention / norms / RoPE as PyTorch operators",
+                                     "sequences": int(len(lens)), "parallelism": f"replicas x{world}"},
+                          "projection_tflops": world * T * flops_tok / (ms * 1e-3) / 1e12,
+                          "gpu_launches": ctx.launch_count() - l0}))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -150,6 +217,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="projections", choices=["projections", "encoder"],
+                    help="projections (default, the headline microbench) or encoder: ModernBERT-large forward, tokens/s")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step from a CUDA graph (for small token budgets, where launching from Python is the bottleneck)")
     args = ap.parse_args()
@@ -181,6 +250,8 @@ def main():
         print(json.dumps(line))
         return
 
+    if args.workload == "encoder" and args.impl != "reference":
+        return run_encoder(args, rank, world, local_rank)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: there is no CPU fallback for the product path (use --impl reference for the CPU arm)")
     from sys1_b200 import batching, device, linear, modernbert

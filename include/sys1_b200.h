@@ -180,6 +180,22 @@ int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const voi
                         int value_heads, void* y, long long ldy, void* workspace, size_t workspace_bytes);
 
 /*
+ * Bidirectional softmax attention over a packed batch in flash form (scores stay on chip), head_dim = 64:
+ *     out_i = sum_j softmax_j(scale * q_i . k_j) v_j   over the keys j of the same sequence with |i - j| <= window
+ * (`window` < 0: all keys of the sequence). This is `scaled_dot_product_attention` of the reference
+ * (src/archs/modernbert.rs:313-351) with its local mask (:1058-1076, window = local_attention / 2); the packed
+ * layout has no padded keys, so the global mask (:1048-1056) has nothing to mask. q, k, v: bf16 [T, heads * 64]
+ * views with row strides ldq / ldk / ldv (they may be the three column blocks of the Wqkv output, after RoPE);
+ * out: bf16 [T, heads * 64] = the merged-heads layout Wo consumes (`merge_heads`, :249-260).
+ * `cu_seqlens_host`: HOST int32 [num_seqs + 1]; `workspace`: device memory of s1_attention_workspace(...) bytes.
+ * Softmax in f32, probabilities rounded to bf16 before they multiply V (as the reference does, :349-350).
+ */
+size_t s1_attention_workspace(int num_seqs, int total_tokens);
+int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
+                 const int32_t* cu_seqlens_host, int num_seqs, int total_tokens, int heads, int head_dim, int window,
+                 float scale, void* out, long long ldo, void* workspace, size_t workspace_bytes);
+
+/*
  * Packs the next sequences of a queue into one token-packed batch (host arrays, no GPU work).
  * Takes sequences in order while the running token count stays within `token_budget`; a sequence longer than
  * the budget forms a batch of its own. Writes cu_seqlens[0..num_taken] (cu_seqlens[0] = 0, last = total) and,

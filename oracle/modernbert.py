@@ -110,3 +110,16 @@ def encoder_forward(ids: torch.Tensor, w: Dict[str, torch.Tensor], cfg: EncoderC
             states.append(x)
     y = layer_norm(x, w["final_norm"], cfg.layer_norm_eps, dtype)
     return (y, states) if collect else y
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int = -1, dtype: str = "f32") -> torch.Tensor:
+    """`eager_attention` with the local mask (src/archs/modernbert.rs:337-351, :1058-1076) for one unpadded sequence:
+    q, k, v `[L, H, D]` -> `[L, H * D]`; keys with |i - j| > window get -10000 added (window < 0: no mask)."""
+    r = (lambda t: round_bf16(t)) if dtype == "bf16" else (lambda t: t)
+    L, H, D = q.shape
+    scores = r(torch.einsum("ihd,jhd->hij", r(q.float() * D ** -0.5), k.float()))
+    if window >= 0:
+        idx = torch.arange(L)
+        scores = scores + torch.where((idx.unsqueeze(0) - idx.unsqueeze(1)).abs() > window, MASK_VALUE, 0.0)
+    probs = r(torch.softmax(scores, dim=-1))
+    return r(torch.einsum("hij,jhd->ihd", probs, v.float())).reshape(L, H * D)

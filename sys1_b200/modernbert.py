@@ -48,6 +48,40 @@ class AttentionProjections:
         return self.wo.forward(attended, residual=residual)
 
 
+_attn_ws = {}
+
+
+def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_host, window: int = -1,
+                     scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`scaled_dot_product_attention` + `merge_heads` (src/archs/modernbert.rs:249-351) on a packed batch through
+    `s1_attention`: q, k, v bf16 `[T, H, 64]` views whose rows are contiguous (token stride free), bidirectional,
+    keys limited to the query's own sequence and, with `window >= 0`, to `|i - j| <= window`. Returns `[T, H * 64]`."""
+    import ctypes as C
+    import numpy as np
+    from . import device
+    T, H, D = q.shape
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(2) != 1 or t.stride(1) != D:
+            raise ValueError(f"{name} must be a bf16 CUDA tensor [T, H, 64] with contiguous heads (no CPU fallback)")
+    cu = np.ascontiguousarray(cu_seqlens_host, dtype=np.int32)
+    if out is None:
+        out = torch.empty((T, H * D), dtype=torch.bfloat16, device=q.device)
+    if T == 0:
+        return out
+    ctx = device.load(q.device.index)
+    need = int(ctx._lib.s1_attention_workspace(len(cu) - 1, T))
+    ws = _attn_ws.get(q.device)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 1 << 16), dtype=torch.uint8, device=q.device)
+        _attn_ws[q.device] = ws
+    rc = ctx._lib.s1_attention(ctx.handle, C.c_void_p(q.data_ptr()), q.stride(0), C.c_void_p(k.data_ptr()), k.stride(0),
+                               C.c_void_p(v.data_ptr()), v.stride(0), cu.ctypes.data_as(C.POINTER(C.c_int32)), len(cu) - 1, T, H, D,
+                               int(window), C.c_float(D ** -0.5 if scale is None else scale), C.c_void_p(out.data_ptr()),
+                               out.stride(0), C.c_void_p(ws.data_ptr()), ws.numel())
+    ctx.check(rc)
+    return out
+
+
 class Encoder:
     """`Encoder::forward` (src/archs/modernbert.rs:958-989) on a token-packed batch. The four projections of every
     layer run through the C ABI (Wqkv; Wo with the residual stream updated in place; Wi with GeGLU; MLP-out with the
@@ -58,7 +92,10 @@ class Encoder:
     `weights`: dict with the names of `oracle.modernbert.init_weights` (bf16 CUDA tensors); `cfg`: any object with
     the fields of `oracle.modernbert.EncoderConfig`."""
 
-    def __init__(self, weights, cfg):
+    def __init__(self, weights, cfg, attention: str = "s1"):
+        """`attention`: "s1" = this library's flash-form kernel (`s1_attention`), "torch" = PyTorch's
+        `scaled_dot_product_attention` per sequence with an explicit band mask (harness fallback for comparison)."""
+        self.attention = attention
         self.cfg = cfg
         self.w = weights
         self.layers = []
@@ -115,7 +152,9 @@ class Encoder:
 
             q, k, v = rot(qkv[:, 0]), rot(qkv[:, 1]), qkv[:, 2]
             attn = torch.empty((T, H * D), dtype=torch.bfloat16, device=dev)
-            for a, b in zip(bounds[:-1], bounds[1:]):
+            if self.attention == "s1" and D == 64:
+                attention_varlen(q, k, v, bounds, window=cfg.local_attention // 2 if local else -1, out=attn)
+            for a, b in (zip(bounds[:-1], bounds[1:]) if not (self.attention == "s1" and D == 64) else ()):
                 if a == b:
                     continue
                 mask = self._band(b - a, dev) if local else None

@@ -1,0 +1,51 @@
+"""`s1_attention` (flash-form bidirectional attention with an optional band, packed batch, head dim 64) against the
+CPU oracle's restatement of the reference's eager attention. bf16 inputs; tolerance 2e-2 of the output scale."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import max_rel
+from sys1_b200 import modernbert
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _case(lens, H, window, seed):
+    cu = np.cumsum([0] + lens).astype(np.int32)
+    T = int(cu[-1])
+    g = torch.Generator().manual_seed(seed)
+    qkv = torch.randn(T, 3, H, 64, generator=g).to(torch.bfloat16)
+    qkv[:, 0] *= 2.0  # sharper softmax than N(0, 1) scores
+    d = qkv.to(DEV)
+    got = modernbert.attention_varlen(d[:, 0], d[:, 1], d[:, 2], cu, window=window).float().cpu()
+    want = torch.empty(T, H * 64)
+    for a, z in zip(cu[:-1], cu[1:]):
+        if z > a:
+            want[a:z] = oracle.attention(qkv[a:z, 0], qkv[a:z, 1], qkv[a:z, 2], window)
+    return got, want
+
+
+@pytest.mark.parametrize("lens,H,window", [
+    ([128], 1, -1), ([5], 2, -1), ([129, 1, 300], 3, -1), ([700, 64], 2, 64), ([130, 0, 257, 1], 4, 64), ([1000], 12, 64),
+    ([1500], 2, -1),
+])
+def test_attention_matches_the_oracle(ctx, lens, H, window):
+    got, want = _case(lens, H, window, 11 * len(lens) + H)
+    ctx.sync()
+    assert torch.isfinite(got).all()
+    assert max_rel(got, want) <= 2e-2
+
+
+def test_sequences_do_not_see_each_other(ctx):
+    """The rows of a sequence are bit-identical whether it is packed with others or run alone."""
+    lens = [200, 333, 90]
+    cu = np.cumsum([0] + lens).astype(np.int32)
+    g = torch.Generator().manual_seed(9)
+    qkv = torch.randn(int(cu[-1]), 3, 4, 64, generator=g).to(torch.bfloat16).to(DEV)
+    for window in (-1, 64):
+        packed = modernbert.attention_varlen(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, window=window)
+        a, z = int(cu[1]), int(cu[2])
+        alone = modernbert.attention_varlen(qkv[a:z, 0], qkv[a:z, 1], qkv[a:z, 2], np.array([0, z - a], dtype=np.int32), window=window)
+        assert torch.equal(packed[a:z], alone)
