@@ -144,9 +144,10 @@ def run_cpu_arm(tokens: int, steps: int, warmup: int, budget_s: float = 20.0):
 def run_encoder(args, rank, world, local_rank):
     """Secondary workload: ModernBERT-large-shaped encoder forward (28 layers, hidden 1024, 16 heads, GeGLU 2 x 2624,
     window 128, global every 3rd layer) over packed batches of `--tokens` tokens with log-uniform lengths in
-    [8, 8192], one replica per GPU. The four projections of every layer go through the C ABI; attention, LayerNorm,
-    RoPE and the embedding lookup are PyTorch operators (harness code outside this repository's path), so the
-    tokens/s figure is an upper bound set largely by that harness attention."""
+    [8, 8192], one replica per GPU. The four projections and the attention of every layer go through the C ABI;
+    LayerNorm, RoPE and the embedding lookup are PyTorch operators (harness code). The line also times one global
+    and one banded attention launch on the same batch (`attention`: microseconds and algorithmic TFLOP/s, counting
+    4 x head_dim flops per query-key pair inside the band)."""
     from types import SimpleNamespace
     from sys1_b200 import batching, device, modernbert
     torch.cuda.set_device(local_rank)
@@ -194,15 +195,36 @@ def run_encoder(args, rank, world, local_rank):
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = float(t[0])
+    H, D = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads
+    qkv = mk(3, T, H * D)
+    attn_stats = {}
+    for name, window in (("global", -1), ("local", cfg.local_attention // 2)):
+        out = torch.empty(T, H * D, device=dev, dtype=torch.bfloat16)
+        for _ in range(3):
+            modernbert.attention_varlen(qkv[0].view(T, H, D), qkv[1].view(T, H, D), qkv[2].view(T, H, D), batch.cu_seqlens,
+                                        window=window, out=out)
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(10):
+            modernbert.attention_varlen(qkv[0].view(T, H, D), qkv[1].view(T, H, D), qkv[2].view(T, H, D), batch.cu_seqlens,
+                                        window=window, out=out)
+        a1.record()
+        torch.cuda.synchronize()
+        us = a0.elapsed_time(a1) * 100.0
+        pairs = 0
+        for n in lens:
+            n = int(n)
+            pairs += n * n if window < 0 or n <= window else n * (2 * window + 1) - window * (window + 1)
+        attn_stats[name] = {"us": us, "tflops": 4.0 * D * H * pairs / (us * 1e-6) / 1e12}
     if rank == 0:
         flops_tok = 28 * 2 * (1024 * 3072 + 1024 * 1024 + 1024 * 5248 + 2624 * 1024)
         print(json.dumps({"metric": "encoder tokens/s", "value": world * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
                           "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                           "config": {"workload": f"ModernBERT-large-shaped encoder forward, packed T={T}, lengths log-uniform [8,8192], "
-                                                 "projections through the C ABI, attention / norms / RoPE as PyTorch operators",
+                                                 "projections and attention through the C ABI, norms / RoPE / embedding as PyTorch operators",
                                      "sequences": int(len(lens)), "parallelism": f"replicas x{world}"},
-                          "projection_tflops": world * T * flops_tok / (ms * 1e-3) / 1e12,
+                          "projection_tflops": world * T * flops_tok / (ms * 1e-3) / 1e12, "attention": attn_stats,
                           "gpu_launches": ctx.launch_count() - l0}))
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -16,4 +16,4 @@ Pinning status
 """
 from .projection import (geglu, linear, mlp_modernbert, mlp_qwen35, round_bf16, swiglu)  # noqa: F401
 from .delta_rule import (causal_conv_silu, chunked_delta_rule, delta_inputs, finish_delta, sequential_delta_rule)  # noqa: F401
-from .modernbert import EncoderConfig, attention, encoder_forward, init_weights  # noqa: F401,E402
+from .modernbert import EncoderConfig, attention, encoder_forward, encoder_layer, init_weights  # noqa: F401,E402

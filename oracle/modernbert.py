@@ -80,32 +80,38 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1)
 
 
+def encoder_layer(i: int, x: torch.Tensor, w: Dict[str, torch.Tensor], cfg: EncoderConfig, dtype: str = "f32") -> torch.Tensor:
+    """`Layer::forward` (src/archs/modernbert.rs:857-887) for layer `i` of one unpadded sequence: residual stream
+    `x [L, hidden]` in, residual stream out."""
+    r = (lambda t: round_bf16(t)) if dtype == "bf16" else (lambda t: t)
+    L = x.shape[0]
+    H, D = cfg.num_attention_heads, cfg.head_dim
+    p = f"layers.{i}."
+    local = i % cfg.global_attn_every_n_layers != 0
+    n = x if i == 0 else layer_norm(x, w[p + "attn_norm"], cfg.layer_norm_eps, dtype)
+    qkv = linear(n, w[p + "Wqkv"], dtype=dtype).reshape(L, 3, H, D)
+    cos, sin = rope_tables(cfg, cfg.local_rope_theta if local else cfg.global_rope_theta, L)
+    q, k, v = r(rope(qkv[:, 0], cos, sin)), r(rope(qkv[:, 1], cos, sin)), qkv[:, 2]
+    scores = r(torch.einsum("ihd,jhd->hij", r(q * D ** -0.5), k))
+    if local:
+        idx = torch.arange(L)
+        scores = scores + torch.where((idx.unsqueeze(0) - idx.unsqueeze(1)).abs() > cfg.local_attention // 2,
+                                      MASK_VALUE, 0.0)
+    probs = r(torch.softmax(scores, dim=-1))
+    attn = r(torch.einsum("hij,jhd->ihd", probs, v)).reshape(L, H * D)
+    x = linear(attn, w[p + "Wo"], residual=x, dtype=dtype)
+    m = geglu(linear(layer_norm(x, w[p + "mlp_norm"], cfg.layer_norm_eps, dtype), w[p + "Wi"], dtype=dtype), dtype)
+    return linear(m, w[p + "mlp_Wo"], residual=x, dtype=dtype)
+
+
 def encoder_forward(ids: torch.Tensor, w: Dict[str, torch.Tensor], cfg: EncoderConfig, dtype: str = "f32",
                     collect: bool = False):
     """One unpadded sequence `ids [L]` -> final hidden `[L, hidden]` (float32 values of the requested precision);
     with `collect`, also the list of hidden states after every layer."""
-    r = (lambda t: round_bf16(t)) if dtype == "bf16" else (lambda t: t)
-    L = ids.shape[0]
-    H, D = cfg.num_attention_heads, cfg.head_dim
     x = layer_norm(w["tok_embeddings"][ids].to(torch.float32), w["embeddings_norm"], cfg.layer_norm_eps, dtype)
-    idx = torch.arange(L)
-    local_mask = torch.where((idx.unsqueeze(0) - idx.unsqueeze(1)).abs() > cfg.local_attention // 2, MASK_VALUE, 0.0)
     states: List[torch.Tensor] = []
     for i in range(cfg.num_hidden_layers):
-        p = f"layers.{i}."
-        local = i % cfg.global_attn_every_n_layers != 0
-        n = x if i == 0 else layer_norm(x, w[p + "attn_norm"], cfg.layer_norm_eps, dtype)
-        qkv = linear(n, w[p + "Wqkv"], dtype=dtype).reshape(L, 3, H, D)
-        cos, sin = rope_tables(cfg, cfg.local_rope_theta if local else cfg.global_rope_theta, L)
-        q, k, v = r(rope(qkv[:, 0], cos, sin)), r(rope(qkv[:, 1], cos, sin)), qkv[:, 2]
-        scores = r(torch.einsum("ihd,jhd->hij", r(q * D ** -0.5), k))
-        if local:
-            scores = scores + local_mask
-        probs = r(torch.softmax(scores, dim=-1))
-        attn = r(torch.einsum("hij,jhd->ihd", probs, v)).reshape(L, H * D)
-        x = linear(attn, w[p + "Wo"], residual=x, dtype=dtype)
-        m = geglu(linear(layer_norm(x, w[p + "mlp_norm"], cfg.layer_norm_eps, dtype), w[p + "Wi"], dtype=dtype), dtype)
-        x = linear(m, w[p + "mlp_Wo"], residual=x, dtype=dtype)
+        x = encoder_layer(i, x, w, cfg, dtype)
         if collect:
             states.append(x)
     y = layer_norm(x, w["final_norm"], cfg.layer_norm_eps, dtype)

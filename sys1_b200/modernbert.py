@@ -122,6 +122,48 @@ class Encoder:
             self._bands[key] = (idx.unsqueeze(0) - idx.unsqueeze(1)).abs() <= self.cfg.local_attention // 2
         return self._bands[key]
 
+    def _layer(self, i: int, x: torch.Tensor, bounds, pos: torch.Tensor, max_len: int) -> torch.Tensor:
+        """`Layer::forward` (src/archs/modernbert.rs:857-887) for layer `i`; updates the residual stream `x` in place."""
+        cfg = self.cfg
+        F = torch.nn.functional
+        H, D = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads
+        T, dev = x.shape[0], x.device
+        ln = lambda t, name: F.layer_norm(t, (cfg.hidden_size,), self.w[name], None, cfg.layer_norm_eps)
+        proj, mlp = self.layers[i]
+        p = f"layers.{i}."
+        local = i % cfg.global_attn_every_n_layers != 0
+        n = x if i == 0 else ln(x, p + "attn_norm")
+        qkv = proj.qkv(n).view(T, 3, H, D)
+        cos, sin = self._rope_tables(cfg.local_rope_theta if local else cfg.global_rope_theta, max_len, dev)
+        c, s = cos[pos].unsqueeze(1), sin[pos].unsqueeze(1)
+
+        def rot(t):
+            t = t.float()
+            t1, t2 = t[..., : D // 2], t[..., D // 2:]
+            return torch.cat([t1 * c - t2 * s, t1 * s + t2 * c], dim=-1).to(torch.bfloat16)
+
+        q, k, v = rot(qkv[:, 0]), rot(qkv[:, 1]), qkv[:, 2]
+        attn = torch.empty((T, H * D), dtype=torch.bfloat16, device=dev)
+        if self.attention == "s1" and D == 64:
+            attention_varlen(q, k, v, bounds, window=cfg.local_attention // 2 if local else -1, out=attn)
+        else:
+            for a, b in zip(bounds[:-1], bounds[1:]):
+                if a == b:
+                    continue
+                mask = self._band(b - a, dev) if local else None
+                o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1).unsqueeze(0), k[a:b].transpose(0, 1).unsqueeze(0),
+                                                   v[a:b].transpose(0, 1).unsqueeze(0), attn_mask=mask)
+                attn[a:b] = o[0].transpose(0, 1).reshape(b - a, H * D)
+        proj.wo.forward(attn, residual=x, out=x)                                  # x += attn Wo^T
+        mlp.output.forward(mlp.gated(ln(x, p + "mlp_norm")), residual=x, out=x)   # x += geglu(LN(x) Wi^T) Wout^T
+        return x
+
+    def layer_forward(self, i: int, x: torch.Tensor, cu_seqlens, positions: torch.Tensor) -> torch.Tensor:
+        """One layer on a given residual stream (a copy is updated and returned): for layer-by-layer checks."""
+        bounds = [int(v) for v in cu_seqlens]
+        max_len = max((b - a for a, b in zip(bounds[:-1], bounds[1:])), default=0)
+        return self._layer(i, x.clone(), bounds, positions.long(), max_len)
+
     def forward(self, ids: torch.Tensor, cu_seqlens, positions: torch.Tensor, collect: bool = False):
         """ids int64 `[T]` (CUDA), cu_seqlens host int offsets `[B+1]`, positions int `[T]` (CUDA). Returns the final
         hidden states `[T, hidden]` bf16 (and, with `collect`, the residual stream after every layer)."""
@@ -137,32 +179,8 @@ class Encoder:
         max_len = max((b - a for a, b in zip(bounds[:-1], bounds[1:])), default=0)
         pos = positions.long()
         states = []
-        for i, (proj, mlp) in enumerate(self.layers):
-            p = f"layers.{i}."
-            local = i % cfg.global_attn_every_n_layers != 0
-            n = x if i == 0 else ln(x, p + "attn_norm")
-            qkv = proj.qkv(n).view(T, 3, H, D)
-            cos, sin = self._rope_tables(cfg.local_rope_theta if local else cfg.global_rope_theta, max_len, dev)
-            c, s = cos[pos].unsqueeze(1), sin[pos].unsqueeze(1)
-
-            def rot(t):
-                t = t.float()
-                t1, t2 = t[..., : D // 2], t[..., D // 2:]
-                return torch.cat([t1 * c - t2 * s, t1 * s + t2 * c], dim=-1).to(torch.bfloat16)
-
-            q, k, v = rot(qkv[:, 0]), rot(qkv[:, 1]), qkv[:, 2]
-            attn = torch.empty((T, H * D), dtype=torch.bfloat16, device=dev)
-            if self.attention == "s1" and D == 64:
-                attention_varlen(q, k, v, bounds, window=cfg.local_attention // 2 if local else -1, out=attn)
-            for a, b in (zip(bounds[:-1], bounds[1:]) if not (self.attention == "s1" and D == 64) else ()):
-                if a == b:
-                    continue
-                mask = self._band(b - a, dev) if local else None
-                o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1).unsqueeze(0), k[a:b].transpose(0, 1).unsqueeze(0),
-                                                   v[a:b].transpose(0, 1).unsqueeze(0), attn_mask=mask)
-                attn[a:b] = o[0].transpose(0, 1).reshape(b - a, H * D)
-            proj.wo.forward(attn, residual=x, out=x)                       # x += attn Wo^T
-            mlp.output.forward(mlp.gated(ln(x, p + "mlp_norm")), residual=x, out=x)   # x += geglu(LN(x) Wi^T) Wout^T
+        for i in range(len(self.layers)):
+            x = self._layer(i, x, bounds, pos, max_len)
             if collect:
                 states.append(x.clone())
         y = ln(x, "final_norm")
