@@ -144,8 +144,8 @@ def run_cpu_arm(tokens: int, steps: int, warmup: int, budget_s: float = 20.0):
 def run_encoder(args, rank, world, local_rank):
     """Secondary workload: ModernBERT-large-shaped encoder forward (28 layers, hidden 1024, 16 heads, GeGLU 2 x 2624,
     window 128, global every 3rd layer) over packed batches of `--tokens` tokens with log-uniform lengths in
-    [8, 8192], one replica per GPU. The four projections and the attention of every layer go through the C ABI;
-    LayerNorm, RoPE and the embedding lookup are PyTorch operators (harness code). The line also times one global
+    [8, 8192], one replica per GPU. Every stage goes through the C ABI: embedding lookup + norm, per layer norm, Wqkv,
+    RoPE in place, attention, Wo + residual, norm, Wi + GeGLU, MLP-out + residual. The line also times one global
     and one banded attention launch on the same batch (`attention`: microseconds and algorithmic TFLOP/s, counting
     4 x head_dim flops per query-key pair inside the band)."""
     from types import SimpleNamespace
@@ -222,7 +222,7 @@ def run_encoder(args, rank, world, local_rank):
                           "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                           "config": {"workload": f"ModernBERT-large-shaped encoder forward, packed T={T}, lengths log-uniform [8,8192], "
-                                                 "projections and attention through the C ABI, norms / RoPE / embedding as PyTorch operators",
+                                                 "every stage through the C ABI (projections, attention, norms, RoPE, embedding lookup)",
                                      "sequences": int(len(lens)), "parallelism": f"replicas x{world}"},
                           "projection_tflops": world * T * flops_tok / (ms * 1e-3) / 1e12, "attention": attn_stats,
                           "gpu_launches": ctx.launch_count() - l0}))

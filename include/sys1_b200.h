@@ -196,6 +196,35 @@ int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const void* k, long 
                  float scale, void* out, long long ldo, void* workspace, size_t workspace_bytes);
 
 /*
+ * Row-wise normalisation of a bf16 matrix, statistics in f32, one rounding at the end:
+ *     kind 0  y = (x - mean(x)) / sqrt(var(x) + eps) * weight        LayerNorm without bias: the reference's `Norm`
+ *                                                                    (src/archs/modernbert.rs:1006-1034)
+ *     kind 1  y = x / sqrt(mean(x^2) + eps) * (1 + weight)           the reference's `RmsNorm`
+ *                                                                    (src/archs/qwen35_text.rs:178-203)
+ * x: [rows, width] with row stride ldx; weight: bf16 [width]; y: [rows, width] with row stride ldy (may be x).
+ * With `gather` (DEVICE int32 [rows]) row r is read from x[gather[r]]: the embedding lookup fused with the
+ * embedding norm (src/archs/modernbert.rs:1084-1092); `gather_rows` is the row count of x, and an index outside
+ * it is reported by s1_sync as S1_EKERNEL (that row is left unwritten). Rows of any width that is a multiple of 8:
+ * hidden states (rows = tokens) and per-head q / k norms (rows = tokens x heads, width = head_dim) alike.
+ */
+int s1_norm(s1_ctx* ctx, const void* x, long long ldx, const int32_t* gather, int gather_rows, const void* weight,
+            float eps, int kind, void* y, long long ldy, long long rows, int width);
+
+/*
+ * Rotate-half rotary embedding, in place, on `heads` consecutive heads of every token row:
+ *     lo' = lo * cos - hi * sin,  hi' = lo * sin + hi * cos     for the column pairs (j, j + rotary_dim / 2)
+ * of the first `rotary_dim` columns of each head; the rest of the head is left as it is. x: bf16 [T, ldx], head h
+ * of token t starts at x + t * ldx + h * head_stride. cos_table / sin_table: DEVICE f32
+ * [max_positions, rotary_dim / 2]; positions: DEVICE int32 [T], a position outside the table is reported by
+ * s1_sync as S1_EKERNEL (that token is left unrotated). Replaces `rope_qkv` (src/kernels/modernbert.cu:31-62,
+ * called from `RotaryEmbedding::apply_qkv`): on the packed Wqkv output [T, 3 * H * D] call it with heads = 2 * H
+ * (q and k lie side by side); v stays where it is and s1_attention reads the three column blocks in place.
+ * Also `Attention::rotary` of src/archs/qwen35_text.rs:296-310 (rotary_dim < head_dim).
+ */
+int s1_rope(s1_ctx* ctx, void* x, long long ldx, const float* cos_table, const float* sin_table, const int32_t* positions,
+            int max_positions, int total_tokens, int heads, long long head_stride, int rotary_dim);
+
+/*
  * Packs the next sequences of a queue into one token-packed batch (host arrays, no GPU work).
  * Takes sequences in order while the running token count stays within `token_budget`; a sequence longer than
  * the budget forms a batch of its own. Writes cu_seqlens[0..num_taken] (cu_seqlens[0] = 0, last = total) and,

@@ -9,6 +9,8 @@ Pinning status
     two independent forms here (token-sequential, 32-token chunked) agree with each other.
   * GeGLU elementwise: PINNED against the 16-value test of src/archs/modernbert.rs:743-766 (expected values
     from the exact-erf GELU definition the test itself uses).
+  * RoPE: checked the way the reference's own test does (fused index arithmetic against the plain rotate-half on
+    the test's formula inputs; that test holds no expected numbers). Norms: restated from the cited formulas.
   * Linear / GEMM arithmetic: PARITY UNPINNED - the only reference tests that pin it are whole-model snapshots
     that need Hugging Face checkpoints which are not available offline, and the arithmetic itself lives in
     third-party crates (candle-core / candle-nn 0.11.0, gemm 0.19.0) whose source is not part of the reference
@@ -16,4 +18,5 @@ Pinning status
 """
 from .projection import (geglu, linear, mlp_modernbert, mlp_qwen35, round_bf16, swiglu)  # noqa: F401
 from .delta_rule import (causal_conv_silu, chunked_delta_rule, delta_inputs, finish_delta, sequential_delta_rule)  # noqa: F401
+from .norm import layer_norm, rms_norm, rope, rope_qkv_indexed, rope_qkv_test_inputs  # noqa: F401,E402
 from .modernbert import EncoderConfig, attention, encoder_forward, encoder_layer, init_weights  # noqa: F401,E402

@@ -17,6 +17,7 @@ from typing import Dict, List, Sequence
 
 import torch
 
+from .norm import layer_norm, rope
 from .projection import geglu, linear, round_bf16
 
 MASK_VALUE = -10_000.0  # ATTENTION_MASK_VALUE, src/archs/modernbert.rs:23
@@ -57,27 +58,11 @@ def init_weights(cfg: EncoderConfig, seed: int) -> Dict[str, torch.Tensor]:
     return w
 
 
-def layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: str) -> torch.Tensor:
-    x = x.to(torch.float32)
-    mean = x.mean(-1, keepdim=True)
-    var = (x - mean).square().mean(-1, keepdim=True)
-    y = (x - mean) / (var + eps).sqrt() * weight.to(torch.float32)
-    return round_bf16(y) if dtype == "bf16" else y
-
-
 def rope_tables(cfg: EncoderConfig, theta: float, length: int):
     d = cfg.head_dim
     inv = torch.tensor([1.0 / (theta ** (j / d)) for j in range(0, d, 2)], dtype=torch.float32)
     freqs = torch.arange(length, dtype=torch.float32).unsqueeze(1) * inv.unsqueeze(0)
     return freqs.cos(), freqs.sin()
-
-
-def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """Rotate-half on `[L, H, D]` with tables `[L, D/2]` (candle `rope`; kernel src/kernels/modernbert.cu:31-62)."""
-    h = x.shape[-1] // 2
-    x1, x2 = x[..., :h], x[..., h:]
-    c, s = cos.unsqueeze(1), sin.unsqueeze(1)
-    return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1)
 
 
 def encoder_layer(i: int, x: torch.Tensor, w: Dict[str, torch.Tensor], cfg: EncoderConfig, dtype: str = "f32") -> torch.Tensor:

@@ -68,6 +68,10 @@ SIGNATURES = {
     "s1_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                                C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p,
                                C.c_longlong, C.c_void_p, C.c_size_t]),
+    "s1_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
+                          C.c_longlong, C.c_longlong, C.c_int]),
+    "s1_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                          C.c_longlong, C.c_int]),
     "s1_linear": (C.c_int, [C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                             C.c_void_p, C.c_longlong, C.c_int]),
 }

@@ -91,6 +91,9 @@ extern "C" int s1_sync(s1_ctx* ctx) {
     S1_CUDA_OK(ctx, cudaMemcpy(st, ctx->status_dev, sizeof(st), cudaMemcpyDeviceToHost));
     if (st[0] != 0) {
         cudaMemset(ctx->status_dev, 0, sizeof(st));
+        if (st[0] == 101 || st[0] == 102)
+            return s1_fail(ctx, S1_EKERNEL, "%s: row %d has index %d outside the table", st[0] == 101 ? "s1_norm gather" : "s1_rope position",
+                           st[2], st[3]);
         return s1_fail(ctx, S1_EKERNEL, "kernel gave up on a bounded wait: code %d block %d role %d tile %d", st[0],
                        st[1], st[2], st[3]);
     }

@@ -1,7 +1,8 @@
 """Projection side of the ModernBERT layer (`src/archs/modernbert.rs`): Wqkv, Wo(+residual), Wi+GeGLU, MLP-out(+residual).
 
 Same member names as the reference structs (`Attention { wqkv, wo }` :137-175, `Mlp { input, output }`
-:494-534). Attention itself, norms and RoPE are outside this path and stay with the caller.
+:494-534, `Norm` :1006-1034, `RotaryEmbedding` :1100-1160), each a thin caller of the C ABI, and `Encoder`, the
+layer stack on a token-packed batch.
 """
 from __future__ import annotations
 
@@ -9,8 +10,38 @@ from typing import Optional
 
 import torch
 
+from . import norm as _norm
 from ._lib import EPI_GEGLU
 from .linear import Linear, fused_linear
+
+
+class Norm:
+    """The bias-free LayerNorm of the reference (`Norm`, src/archs/modernbert.rs:1006-1034) through `s1_norm`."""
+
+    def __init__(self, weight: torch.Tensor, eps: float):
+        self.weight = weight.contiguous()
+        self.eps = float(eps)
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, gather: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return _norm.norm(x, self.weight, self.eps, _norm.LAYER_NORM, gather=gather, out=out)
+
+    __call__ = forward
+
+
+class RotaryEmbedding:
+    """`RotaryEmbedding { sin, cos }` of the reference (tables `[positions, head_dim / 2]`, f32). `apply_qkv` is the
+    reference's fused `rope_qkv` call (src/kernels/modernbert.cu:31-62) on the packed layout: q and k heads of the
+    Wqkv output are rotated where they lie, each token by the table row of its position inside its own sequence."""
+
+    def __init__(self, theta: float, head_dim: int, max_positions: int, dev):
+        inv = torch.tensor([1.0 / (theta ** (j / head_dim)) for j in range(0, head_dim, 2)], dtype=torch.float32, device=dev)
+        fr = torch.arange(max_positions, dtype=torch.float32, device=dev).unsqueeze(1) * inv.unsqueeze(0)
+        self.cos, self.sin = fr.cos().contiguous(), fr.sin().contiguous()
+        self.head_dim = head_dim
+
+    def apply_qkv(self, qkv: torch.Tensor, positions: torch.Tensor, heads: int) -> torch.Tensor:
+        """qkv bf16 `[T, 3 * heads * head_dim]`, positions int32 `[T]`; rotates the 2 * heads q and k heads in place."""
+        return _norm.rope_(qkv, self.cos, self.sin, positions, 2 * heads, self.head_dim, self.head_dim)
 
 
 class Mlp:
@@ -83,37 +114,41 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
 
 
 class Encoder:
-    """`Encoder::forward` (src/archs/modernbert.rs:958-989) on a token-packed batch. The four projections of every
-    layer run through the C ABI (Wqkv; Wo with the residual stream updated in place; Wi with GeGLU; MLP-out with the
-    residual stream updated in place). Everything else - embedding lookup, LayerNorm (no bias), RoPE, softmax
-    attention - is outside this repository's path and is done here with PyTorch operators, as harness code:
-    attention is `scaled_dot_product_attention` per sequence, with the +-`local_attention/2` band on local layers.
+    """`Encoder::forward` (src/archs/modernbert.rs:958-989) on a token-packed batch, every stage through the C ABI:
+    embedding lookup + embedding norm (`s1_norm` with a row index), per layer attn_norm -> Wqkv -> RoPE in place
+    (`s1_rope`) -> flash-form attention (`s1_attention`) -> Wo with the residual stream updated in place ->
+    mlp_norm -> Wi with GeGLU -> MLP-out with the residual stream updated in place, and the final norm.
 
     `weights`: dict with the names of `oracle.modernbert.init_weights` (bf16 CUDA tensors); `cfg`: any object with
     the fields of `oracle.modernbert.EncoderConfig`."""
 
     def __init__(self, weights, cfg, attention: str = "s1"):
-        """`attention`: "s1" = this library's flash-form kernel (`s1_attention`), "torch" = PyTorch's
-        `scaled_dot_product_attention` per sequence with an explicit band mask (harness fallback for comparison)."""
+        """`attention`: "s1" = this library's kernels throughout; "torch" = attention, norms and RoPE as PyTorch
+        operators (`scaled_dot_product_attention` per sequence with an explicit band mask), kept only as a
+        comparison arm for measurements - the projections still go through the C ABI."""
         self.attention = attention
         self.cfg = cfg
         self.w = weights
+        self.head_dim = cfg.hidden_size // cfg.num_attention_heads
+        if attention == "s1" and self.head_dim != 64:
+            raise ValueError("s1_attention is built for head_dim 64")
         self.layers = []
+        self.norms = {}
         for i in range(cfg.num_hidden_layers):
             p = f"layers.{i}."
             self.layers.append((AttentionProjections(Linear(weights[p + "Wqkv"]), Linear(weights[p + "Wo"])),
                                 Mlp(Linear(weights[p + "Wi"]), Linear(weights[p + "mlp_Wo"]))))
-        self._tables = {}
+        for name, t in weights.items():
+            if name.endswith("norm"):
+                self.norms[name] = Norm(t, cfg.layer_norm_eps)
+        self._rotary = {}
         self._bands = {}
 
-    def _rope_tables(self, theta: float, length: int, dev):
+    def _rope(self, theta: float, length: int, dev) -> RotaryEmbedding:
         key = (theta, dev)
-        if key not in self._tables or self._tables[key][0].shape[0] < length:
-            d = self.cfg.hidden_size // self.cfg.num_attention_heads
-            inv = torch.tensor([1.0 / (theta ** (j / d)) for j in range(0, d, 2)], dtype=torch.float32, device=dev)
-            fr = torch.arange(max(length, 512), dtype=torch.float32, device=dev).unsqueeze(1) * inv.unsqueeze(0)
-            self._tables[key] = (fr.cos(), fr.sin())
-        return self._tables[key]
+        if key not in self._rotary or self._rotary[key].cos.shape[0] < length:
+            self._rotary[key] = RotaryEmbedding(theta, self.head_dim, max(length, 8192), dev)
+        return self._rotary[key]
 
     def _band(self, length: int, dev):
         key = (length, dev)
@@ -122,31 +157,40 @@ class Encoder:
             self._bands[key] = (idx.unsqueeze(0) - idx.unsqueeze(1)).abs() <= self.cfg.local_attention // 2
         return self._bands[key]
 
+    def _ln(self, x: torch.Tensor, name: str, gather: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.attention == "s1":
+            return self.norms[name](x, gather=gather)
+        if gather is not None:
+            x = x[gather.long()]
+        return torch.nn.functional.layer_norm(x, (self.cfg.hidden_size,), self.w[name], None, self.cfg.layer_norm_eps)
+
     def _layer(self, i: int, x: torch.Tensor, bounds, pos: torch.Tensor, max_len: int) -> torch.Tensor:
         """`Layer::forward` (src/archs/modernbert.rs:857-887) for layer `i`; updates the residual stream `x` in place."""
         cfg = self.cfg
-        F = torch.nn.functional
-        H, D = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads
+        H, D = cfg.num_attention_heads, self.head_dim
         T, dev = x.shape[0], x.device
-        ln = lambda t, name: F.layer_norm(t, (cfg.hidden_size,), self.w[name], None, cfg.layer_norm_eps)
         proj, mlp = self.layers[i]
         p = f"layers.{i}."
         local = i % cfg.global_attn_every_n_layers != 0
-        n = x if i == 0 else ln(x, p + "attn_norm")
-        qkv = proj.qkv(n).view(T, 3, H, D)
-        cos, sin = self._rope_tables(cfg.local_rope_theta if local else cfg.global_rope_theta, max_len, dev)
-        c, s = cos[pos].unsqueeze(1), sin[pos].unsqueeze(1)
-
-        def rot(t):
-            t = t.float()
-            t1, t2 = t[..., : D // 2], t[..., D // 2:]
-            return torch.cat([t1 * c - t2 * s, t1 * s + t2 * c], dim=-1).to(torch.bfloat16)
-
-        q, k, v = rot(qkv[:, 0]), rot(qkv[:, 1]), qkv[:, 2]
+        n = x if i == 0 else self._ln(x, p + "attn_norm")
+        qkv = proj.qkv(n)
+        rotary = self._rope(cfg.local_rope_theta if local else cfg.global_rope_theta, max_len, dev)
         attn = torch.empty((T, H * D), dtype=torch.bfloat16, device=dev)
-        if self.attention == "s1" and D == 64:
+        if self.attention == "s1":
+            rotary.apply_qkv(qkv, pos, H)
+            q, k, v = qkv.view(T, 3, H, D).unbind(1)
             attention_varlen(q, k, v, bounds, window=cfg.local_attention // 2 if local else -1, out=attn)
         else:
+            F = torch.nn.functional
+            c, s = rotary.cos[pos.long()].unsqueeze(1), rotary.sin[pos.long()].unsqueeze(1)
+
+            def rot(t):
+                t = t.float()
+                t1, t2 = t[..., : D // 2], t[..., D // 2:]
+                return torch.cat([t1 * c - t2 * s, t1 * s + t2 * c], dim=-1).to(torch.bfloat16)
+
+            qkv = qkv.view(T, 3, H, D)
+            q, k, v = rot(qkv[:, 0]), rot(qkv[:, 1]), qkv[:, 2]
             for a, b in zip(bounds[:-1], bounds[1:]):
                 if a == b:
                     continue
@@ -154,34 +198,30 @@ class Encoder:
                 o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1).unsqueeze(0), k[a:b].transpose(0, 1).unsqueeze(0),
                                                    v[a:b].transpose(0, 1).unsqueeze(0), attn_mask=mask)
                 attn[a:b] = o[0].transpose(0, 1).reshape(b - a, H * D)
-        proj.wo.forward(attn, residual=x, out=x)                                  # x += attn Wo^T
-        mlp.output.forward(mlp.gated(ln(x, p + "mlp_norm")), residual=x, out=x)   # x += geglu(LN(x) Wi^T) Wout^T
+        proj.wo.forward(attn, residual=x, out=x)                                        # x += attn Wo^T
+        mlp.output.forward(mlp.gated(self._ln(x, p + "mlp_norm")), residual=x, out=x)   # x += geglu(LN(x) Wi^T) Wout^T
         return x
+
+    @staticmethod
+    def _bounds(cu_seqlens):
+        bounds = [int(v) for v in cu_seqlens]
+        return bounds, max((b - a for a, b in zip(bounds[:-1], bounds[1:])), default=0)
 
     def layer_forward(self, i: int, x: torch.Tensor, cu_seqlens, positions: torch.Tensor) -> torch.Tensor:
         """One layer on a given residual stream (a copy is updated and returned): for layer-by-layer checks."""
-        bounds = [int(v) for v in cu_seqlens]
-        max_len = max((b - a for a, b in zip(bounds[:-1], bounds[1:])), default=0)
-        return self._layer(i, x.clone(), bounds, positions.long(), max_len)
+        bounds, max_len = self._bounds(cu_seqlens)
+        return self._layer(i, x.clone(), bounds, positions.to(torch.int32).contiguous(), max_len)
 
     def forward(self, ids: torch.Tensor, cu_seqlens, positions: torch.Tensor, collect: bool = False):
-        """ids int64 `[T]` (CUDA), cu_seqlens host int offsets `[B+1]`, positions int `[T]` (CUDA). Returns the final
+        """ids int `[T]` (CUDA), cu_seqlens host int offsets `[B+1]`, positions int `[T]` (CUDA). Returns the final
         hidden states `[T, hidden]` bf16 (and, with `collect`, the residual stream after every layer)."""
-        cfg = self.cfg
-        F = torch.nn.functional
-        H, D = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads
-        T = ids.shape[0]
-        dev = ids.device
-        eps = cfg.layer_norm_eps
-        ln = lambda t, name: F.layer_norm(t, (cfg.hidden_size,), self.w[name], None, eps)
-        x = ln(self.w["tok_embeddings"][ids], "embeddings_norm").contiguous()
-        bounds = [int(v) for v in cu_seqlens]
-        max_len = max((b - a for a, b in zip(bounds[:-1], bounds[1:])), default=0)
-        pos = positions.long()
+        x = self._ln(self.w["tok_embeddings"], "embeddings_norm", gather=ids.to(torch.int32).contiguous())
+        bounds, max_len = self._bounds(cu_seqlens)
+        pos = positions.to(torch.int32).contiguous()
         states = []
         for i in range(len(self.layers)):
             x = self._layer(i, x, bounds, pos, max_len)
             if collect:
                 states.append(x.clone())
-        y = ln(x, "final_norm")
+        y = self._ln(x, "final_norm")
         return (y, states) if collect else y

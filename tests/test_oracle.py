@@ -2,6 +2,7 @@
 golden fixtures (which freeze the oracle's own outputs)."""
 import math
 
+import numpy as np
 import pytest
 import torch
 
@@ -212,3 +213,35 @@ def test_encoder_oracle_matches_an_independent_implementation():
     with torch.no_grad():
         ref = model(input_ids=ids.unsqueeze(0), attention_mask=torch.ones(1, 180, dtype=torch.long)).last_hidden_state[0]
     assert (oracle.encoder_forward(ids, w, cfg) - ref).abs().max() < 1e-4
+
+
+def test_rope_index_arithmetic_matches_plain_rope_on_the_reference_test_inputs():
+    """The check of `fused_rope_qkv_matches_candle` (src/archs/modernbert.rs:768-817): fused split kernel, restated
+    index by index, against the plain rotate-half rope on the test's formula inputs; bf16 tolerance 0.03, and here
+    also exact agreement in f32; v passes through unchanged."""
+    cos, sin, values = oracle.rope_qkv_test_inputs()
+    B, L, _, H, D = values.shape
+    for dtype, tol in (("f32", 1e-6), ("bf16", 0.03)):
+        src = oracle.round_bf16(torch.from_numpy(values)).numpy() if dtype == "bf16" else values
+        q, k, v = oracle.rope_qkv_indexed(src, cos, sin, L, H, D, dtype=dtype)
+        for b in range(B):
+            x = torch.from_numpy(src[b])  # [L, 3, H, D]
+            want_q = oracle.rope(x[:, 0], torch.from_numpy(cos), torch.from_numpy(sin))
+            want_k = oracle.rope(x[:, 1], torch.from_numpy(cos), torch.from_numpy(sin))
+            assert np.abs(q[b * L:(b + 1) * L] - want_q.numpy()).max() <= tol
+            assert np.abs(k[b * L:(b + 1) * L] - want_k.numpy()).max() <= tol
+            assert np.array_equal(v[b * L:(b + 1) * L], src[b][:, 2])
+
+
+def test_norms_match_their_definitions():
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(7, 96, generator=g) * 3 + 0.5
+    w = torch.randn(96, generator=g)
+    want = torch.nn.functional.layer_norm(x, (96,), w, None, 1e-5)
+    assert (oracle.layer_norm(x, w, 1e-5) - want).abs().max() < 1e-5
+    rms = oracle.rms_norm(x, w, 1e-6)
+    assert torch.allclose(rms, x / (x.pow(2).mean(-1, keepdim=True) + 1e-6).sqrt() * (1 + w), atol=1e-5)
+    # partial rotation leaves the tail of every head alone
+    cos, sin = torch.rand(7, 8), torch.rand(7, 8)
+    y = oracle.rope(x.view(7, 3, 32), cos, sin, rotary_dim=16)
+    assert torch.equal(y[..., 16:], x.view(7, 3, 32)[..., 16:])
