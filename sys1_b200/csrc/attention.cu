@@ -8,13 +8,18 @@
 // (its flash-attn path is refused for compute capability >= 10, build.rs:53-55) and materialises [L, L] scores.
 //
 // One CTA per (128-query block of one sequence, head); 5 warps:
-//   warp 4      : TMA loads (Q once, K / V tiles of 128 keys through a 2-stage ring) and the MMAs:
-//                 S = Q K^T (M = 128 queries, N = 128 keys, K = 64) and PV (M = 128, N = 64, K = 128 keys,
-//                 V consumed as stored, token rows x dims = MN-major B operand), accumulators in TMEM
-//   warps 0..3  : thread = query row = TMEM lane: online softmax in f32 (running max / sum per thread, no
-//                 shuffles), P rounded to bf16 into a swizzled A-operand tile, O kept in 64 f32 registers
-// Two CTAs fit per SM (112 KB shared memory, 256 TMEM columns each): one computes softmax while the other's MMAs run.
-// Every mbarrier wait is bounded.
+//   warp 4      : TMA loads (Q once; K and V tiles of 128 keys, each through its own 2-stage ring) and the MMAs:
+//                 S = Q K^T (M = 128 queries, N = 128 keys, K = 64) and O += P V (M = 128, N = 64, K = 128 keys,
+//                 V consumed as stored, token rows x dims = MN-major B operand); S and O live in TMEM
+//   warps 0..3  : thread = query row = TMEM lane. Each thread pulls its 128 scores into registers in one go (which
+//                 frees S: the next tile's S = Q K^T runs under this tile's softmax), takes the row maximum,
+//                 exponentiates (f32, ex2 with the scale folded into one fma), adds up the row sum and rounds P to
+//                 bf16 into a swizzled A-operand tile. O stays in TMEM and is accumulated by the MMA itself; it is
+//                 rescaled there only when a row's maximum has grown by more than 2^8 since the last rescale (the
+//                 final division by the row sum makes the reference maximum immaterial), so the common tile costs
+//                 no pass over O at all.
+// Key tiles of banded layers start at the first key of the band (no alignment to 128), so a query block meets two
+// tiles, not three. Two CTAs fit per SM (112 KB shared memory, 256 TMEM columns each). Every mbarrier wait is bounded.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -72,6 +77,13 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+constexpr float kRescaleLog2 = 8.f;  // O is rescaled when a row maximum has grown by more than this many powers of two
 
 __global__ void __launch_bounds__(160, 2)
 s1_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -83,13 +95,13 @@ s1_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         return;
     }
     uint8_t* al = smem_raw;
-    const uint32_t sq = base, skv = base + kTile, sp = base + 5 * kTile;  // stage s: K at skv + s*2*kTile, V right after
+    const uint32_t sq = base, sk = base + kTile, sv = base + 3 * kTile, sp = base + 5 * kTile;
     uint64_t* bars = reinterpret_cast<uint64_t*>(al + 7 * kTile);
-    // bars: 0 Q full; 1,2 KV full; 3,4 KV empty; 5 S ready; 6 P ready; 7 PV ready
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    // bars: 0 Q full; 1,2 K full; 3,4 V full; 5 S ready; 6 S read (4 warps); 7 P ready (4 warps); 8 PV done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t b0 = smem_u32(bars);
-    const uint32_t bar_q = b0, full0 = b0 + 8, empty0 = b0 + 24, bar_s = b0 + 40, bar_p = b0 + 48, bar_o = b0 + 56;
+    const uint32_t bar_q = b0, full_k = b0 + 8, full_v = b0 + 24, bar_s = b0 + 40, bar_sfree = b0 + 48, bar_p = b0 + 56, bar_o = b0 + 64;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const QBlock qb = p.blocks[blockIdx.x];
@@ -98,16 +110,16 @@ s1_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int q_hi = min(q_lo + kQB, qb.seq_len) - 1;              // last valid query
     const int k_first = p.window < 0 ? 0 : max(0, q_lo - p.window);
     const int k_last = p.window < 0 ? qb.seq_len - 1 : min(qb.seq_len - 1, q_hi + p.window);
-    const int kb_lo = k_first / kQB, kb_hi = k_last / kQB;         // key tiles kb_lo .. kb_hi
-    const int nkb = kb_hi - kb_lo + 1;
+    const int nkb = (k_last - k_first) / kQB + 1;                  // key tile i holds keys k_first + 128 i ...
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1);
-        mbar_init(full0, 1);
-        mbar_init(full0 + 8, 1);
-        mbar_init(empty0, 1);
-        mbar_init(empty0 + 8, 1);
+        mbar_init(full_k, 1);
+        mbar_init(full_k + 8, 1);
+        mbar_init(full_v, 1);
+        mbar_init(full_v + 8, 1);
         mbar_init(bar_s, 1);
+        mbar_init(bar_sfree, 4);
         mbar_init(bar_p, 4);
         mbar_init(bar_o, 1);
         *abort_flag = 0;
@@ -123,145 +135,189 @@ s1_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem = *tmem_slot;  // columns 0..127: S, 128..191: O
     int fail = 0;
 
     if (warp == 4) {
         if (lane == 0) {
             const int x = head * kHD;
+            const int y0 = qb.seq_start + k_first;
+            auto load_k = [&](int i) {
+                const uint32_t fb = full_k + 8u * (i & 1);
+                mbar_arrive_expect_tx(fb, kTile);
+                tma_load_2d(sk + (i & 1) * kTile, &tmK, x, y0 + i * kQB, fb);
+            };
+            auto load_v = [&](int i) {
+                const uint32_t fb = full_v + 8u * (i & 1);
+                mbar_arrive_expect_tx(fb, kTile);
+                tma_load_2d(sv + (i & 1) * kTile, &tmV, x, y0 + i * kQB, fb);
+            };
+            auto mma_s = [&](int i) {
+                constexpr uint32_t idesc = make_idesc(1, 128, 128);
+                const uint32_t kt = sk + (i & 1) * kTile;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma_bf16(tmem, make_sw128_kmajor_desc(sq) + 2u * kk, make_sw128_kmajor_desc(kt) + 2u * kk, idesc, kk ? 1u : 0u);
+                umma_commit(bar_s);
+            };
             mbar_arrive_expect_tx(bar_q, kTile);
             tma_load_2d(sq, &tmQ, x, qb.seq_start + q_lo, bar_q);
-            auto load = [&](int i) {
-                const int st = i & 1;
-                const uint32_t fb = full0 + 8u * st, dst = skv + st * 2 * kTile;
-                const int y = qb.seq_start + (kb_lo + i) * kQB;
-                mbar_arrive_expect_tx(fb, 2 * kTile);
-                tma_load_2d(dst, &tmK, x, y, fb);
-                tma_load_2d(dst + kTile, &tmV, x, y, fb);
-            };
-            load(0);
+            load_k(0);
+            load_v(0);
+            if (nkb > 1) {
+                load_k(1);
+                load_v(1);
+            }
             if (!mbar_wait(bar_q, 0, abort_flag)) fail = 1;
-            for (int i = 0; i < nkb && !fail; ++i) {
-                const int st = i & 1;
-                const uint32_t kt = skv + st * 2 * kTile, vt = kt + kTile;
-                if (i + 1 < nkb) {
-                    if (i >= 1 && !mbar_wait(empty0 + 8u * ((i + 1) & 1), ((i - 1) >> 1) & 1, abort_flag)) { fail = 2; break; }
-                    load(i + 1);
-                }
-                if (!mbar_wait(full0 + 8u * st, (i >> 1) & 1, abort_flag)) { fail = 3; break; }
-                // S (TMEM columns 0..127) may be overwritten once the softmax warps have read block i-1: they say so
-                // through bar_p of that block, which this thread has already waited on below
+            if (!fail && !mbar_wait(full_k, 0, abort_flag)) fail = 2;
+            if (!fail) {
                 tc_fence_after();
-                {
-                    constexpr uint32_t idesc = make_idesc(1, 128, 128);
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma_bf16(tmem, make_sw128_kmajor_desc(sq) + 2u * kk, make_sw128_kmajor_desc(kt) + 2u * kk, idesc, kk ? 1u : 0u);
-                    umma_commit(bar_s);
+                mma_s(0);
+            }
+            for (int i = 0; i < nkb && !fail; ++i) {
+                if (i + 1 < nkb) {
+                    // S of tile i+1 as soon as the softmax warps hold tile i in registers: it runs under their softmax
+                    if (!mbar_wait(full_k + 8u * ((i + 1) & 1), ((i + 1) >> 1) & 1, abort_flag)) { fail = 3; break; }
+                    if (!mbar_wait(bar_sfree, i & 1, abort_flag)) { fail = 4; break; }
+                    tc_fence_after();
+                    mma_s(i + 1);
+                    if (i + 2 < nkb) load_k(i + 2);  // its stage held K of tile i, whose S the softmax warps have read
                 }
-                if (!mbar_wait(bar_p, i & 1, abort_flag)) { fail = 4; break; }
+                if (!mbar_wait(bar_p, i & 1, abort_flag)) { fail = 5; break; }
+                if (i >= 1 && i + 1 < nkb) {         // the other V stage held tile i-1: free once that PV has completed
+                    if (!mbar_wait(bar_o, (i - 1) & 1, abort_flag)) { fail = 6; break; }
+                    load_v(i + 1);
+                }
+                if (!mbar_wait(full_v + 8u * (i & 1), (i >> 1) & 1, abort_flag)) { fail = 7; break; }
                 tc_fence_after();
                 {
                     constexpr uint32_t idesc = make_idesc(1, 128, 64) | (1u << 16);  // B (= V) is MN-major
+                    const uint32_t vt = sv + (i & 1) * kTile;
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)  // 16 keys per instruction
                         umma_bf16(tmem + 128, make_sw128_kmajor_desc(sp + (kk >> 2) * kTile) + 2u * (kk & 3), mn_desc(vt) + 128u * kk,
-                                  idesc, kk ? 1u : 0u);
+                                  idesc, (kk || i) ? 1u : 0u);
                     umma_commit(bar_o);
-                    umma_commit(empty0 + 8u * st);
                 }
             }
         }
         __syncwarp();
     } else {
         const int row = threadIdx.x;                       // query row of the block = TMEM lane
-        const int qi = q_lo + row;                         // index inside the sequence
-        const bool q_ok = qi < qb.seq_len;
+        const bool q_ok = q_lo + row < qb.seq_len;
+        const int qi = min(q_lo + row, qb.seq_len - 1);    // rows past the sequence compute like its last row; never stored
         const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-        float O[kHD];
-#pragma unroll
-        for (int d = 0; d < kHD; ++d) O[d] = 0.f;
-        float m = -INFINITY, l = 0.f;
-        const int lo = p.window < 0 ? 0 : qi - p.window, hi = p.window < 0 ? qb.seq_len - 1 : min(qb.seq_len - 1, qi + p.window);
+        const int lo = p.window < 0 ? 0 : max(0, qi - p.window), hi = p.window < 0 ? qb.seq_len - 1 : min(qb.seq_len - 1, qi + p.window);
+        const uint32_t span = static_cast<uint32_t>(hi - lo);
+        const float c = p.scale_log2;
+        const uint32_t prow = sp + static_cast<uint32_t>(row) * 128u, r7 = static_cast<uint32_t>(row) & 7u;
+        float m_used = -INFINITY, l = 0.f;
 
         for (int i = 0; i < nkb; ++i) {
-            const int j0 = (kb_lo + i) * kQB;              // first key of the tile (index inside the sequence)
+            const int j0 = k_first + i * kQB;              // first key of the tile (index inside the sequence)
             bool ok = mbar_wait(bar_s, i & 1, abort_flag);
-            if (!__all_sync(0xffffffffu, ok)) { fail = 5; break; }
+            if (!__all_sync(0xffffffffu, ok)) { fail = 8; break; }
             tc_fence_after();
-            // pass 1: row maximum over the keys this query may see
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t s[32];
-                tmem_ld_32x32b_x32(lane_addr + c * 32, s);
-                tmem_ld_wait();
+            uint32_t s[128];
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int j = j0 + c * 32 + e;
-                    if (j >= lo && j <= hi) mx = fmaxf(mx, __uint_as_float(s[e]));
+            for (int ch = 0; ch < 4; ++ch) tmem_ld_32x32b_x32(lane_addr + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * ch]));
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sfree);
+            if (!(p.window < 0 && j0 + kQB <= qb.seq_len)) {  // a tile that reaches past the band or the sequence
+                const int rel = j0 - lo;
+#pragma unroll
+                for (int e = 0; e < 128; ++e)
+                    if (static_cast<uint32_t>(rel + e) > span) s[e] = 0xff800000u;  // -inf
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 128; e += 8) {
+                mx0 = fmax3(mx0, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
+                mx1 = fmax3(mx1, __uint_as_float(s[e + 2]), __uint_as_float(s[e + 3]));
+                mx2 = fmax3(mx2, __uint_as_float(s[e + 4]), __uint_as_float(s[e + 5]));
+                mx3 = fmax3(mx3, __uint_as_float(s[e + 6]), __uint_as_float(s[e + 7]));
+            }
+            const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+            float alpha = 1.f;
+            bool rescale = false;
+            if (i == 0) {
+                m_used = m_new;
+            } else {
+                // NaN (both -inf) compares false; -inf -> finite gives +inf and rescales by ex2(-inf) = 0
+                rescale = __any_sync(0xffffffffu, (m_new - m_used) * c > kRescaleLog2);
+                if (rescale && m_new != -INFINITY) {
+                    alpha = ex2((m_used - m_new) * c);
+                    m_used = m_new;
                 }
             }
-            const float m_new = fmaxf(m, mx);
-            const float alpha = (m_new == -INFINITY) ? 1.f : ex2((m - m_new) * p.scale_log2);  // m = -inf: ex2(-inf) = 0
-            const float mref = (m_new == -INFINITY) ? 0.f : m_new;
-            // pass 2: p = exp(scale (s - m)), row sum, bf16 P into the A-operand tiles
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t s[32];
-                tmem_ld_32x32b_x32(lane_addr + c * 32, s);
-                tmem_ld_wait();
-                uint32_t pk[16];
+            const float neg_mc = (m_used == -INFINITY) ? 0.f : -m_used * c;
+            uint32_t pk[64];
+            float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int j = j0 + c * 32 + e;
-                    const float p0 = (j >= lo && j <= hi) ? ex2((__uint_as_float(s[e]) - mref) * p.scale_log2) : 0.f;
-                    const float p1 = (j + 1 >= lo && j + 1 <= hi) ? ex2((__uint_as_float(s[e + 1]) - mref) * p.scale_log2) : 0.f;
-                    const __nv_bfloat162 t = __floats2bfloat162_rn(p0, p1);
-                    sum += __low2float(t) + __high2float(t);  // the sum of what is actually multiplied with V
-                    pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
-                }
+            for (int e = 0; e < 128; e += 2) {
+                const float p0 = ex2(fmaf(__uint_as_float(s[e]), c, neg_mc));
+                const float p1 = ex2(fmaf(__uint_as_float(s[e + 1]), c, neg_mc));
+                sum0 += p0;
+                sum1 += p1;
+                pk[e >> 1] = pack_bf16x2_attn(p0, p1);
+            }
+            l = fmaf(l, alpha, sum0 + sum1);
+            if (i >= 1) {  // P and O are the previous PV's operands until it has completed
+                ok = mbar_wait(bar_o, (i - 1) & 1, abort_flag);
+                if (!__all_sync(0xffffffffu, ok)) { fail = 9; break; }
+                tc_fence_after();
+                if (rescale) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int col = (c & 1) * 32 + 8 * e;  // column inside the 64-key tile c / 2
-                    const uint32_t addr = sp + (c >> 1) * kTile + sw128(row, col);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * e]), "r"(pk[4 * e + 1]),
-                                 "r"(pk[4 * e + 2]), "r"(pk[4 * e + 3]) : "memory");
+                    for (int ch = 0; ch < 2; ++ch) {
+                        uint32_t o[32];
+                        tmem_ld_32x32b_x32(lane_addr + 128 + ch * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                        tmem_st_32x32b_x32(lane_addr + 128 + ch * 32, o);
+                    }
+                    tmem_st_wait();
                 }
             }
-            l = l * alpha + sum;
-            m = m_new;
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {  // 8 keys (16 bytes) per store; keys 0..63 in the first P tile, 64..127 in the second
+                const uint32_t addr = prow + (t >> 3) * kTile + (((static_cast<uint32_t>(t) & 7u) ^ r7) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * t]), "r"(pk[4 * t + 1]),
+                             "r"(pk[4 * t + 2]), "r"(pk[4 * t + 3]) : "memory");
+            }
             fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_p);
-
-            ok = mbar_wait(bar_o, i & 1, abort_flag);
-            if (!__all_sync(0xffffffffu, ok)) { fail = 6; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t pv[32];
-                tmem_ld_32x32b_x32(lane_addr + 128 + c * 32, pv);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) O[c * 32 + e] = fmaf(O[c * 32 + e], alpha, __uint_as_float(pv[e]));
-            }
-            tc_fence_before();
         }
-        if (!fail && q_ok) {
+        if (!fail) {
+            const bool ok = mbar_wait(bar_o, (nkb - 1) & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) fail = 10;
+        }
+        if (!fail) {
+            tc_fence_after();
             const float inv = 1.f / l;
             __nv_bfloat16* orow = p.out + static_cast<long long>(qb.seq_start + qi) * p.ldo + head * kHD;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                uint4 v;
-                v.x = pack_bf16x2_attn(O[8 * e] * inv, O[8 * e + 1] * inv);
-                v.y = pack_bf16x2_attn(O[8 * e + 2] * inv, O[8 * e + 3] * inv);
-                v.z = pack_bf16x2_attn(O[8 * e + 4] * inv, O[8 * e + 5] * inv);
-                v.w = pack_bf16x2_attn(O[8 * e + 6] * inv, O[8 * e + 7] * inv);
-                *reinterpret_cast<uint4*>(orow + 8 * e) = v;
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t o[32];
+                tmem_ld_32x32b_x32(lane_addr + 128 + ch * 32, o);
+                tmem_ld_wait();
+                if (q_ok) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        uint4 v;
+                        v.x = pack_bf16x2_attn(__uint_as_float(o[8 * e]) * inv, __uint_as_float(o[8 * e + 1]) * inv);
+                        v.y = pack_bf16x2_attn(__uint_as_float(o[8 * e + 2]) * inv, __uint_as_float(o[8 * e + 3]) * inv);
+                        v.z = pack_bf16x2_attn(__uint_as_float(o[8 * e + 4]) * inv, __uint_as_float(o[8 * e + 5]) * inv);
+                        v.w = pack_bf16x2_attn(__uint_as_float(o[8 * e + 6]) * inv, __uint_as_float(o[8 * e + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + ch * 32 + 8 * e) = v;
+                    }
+                }
             }
+            tc_fence_before();
         }
         __syncwarp();
     }

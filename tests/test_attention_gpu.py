@@ -49,3 +49,28 @@ def test_sequences_do_not_see_each_other(ctx):
         a, z = int(cu[1]), int(cu[2])
         alone = modernbert.attention_varlen(qkv[a:z, 0], qkv[a:z, 1], qkv[a:z, 2], np.array([0, z - a], dtype=np.int32), window=window)
         assert torch.equal(packed[a:z], alone)
+
+
+@pytest.mark.parametrize("window", [-1, 64])
+def test_row_maximum_that_keeps_growing(ctx, window):
+    """Keys whose scores grow along the sequence by far more than 2^8 in total: the running output has to be
+    rescaled again and again (the kernel rescales lazily, only past a growth threshold), and early keys end up with
+    weights that underflow - the result must still match the oracle."""
+    L, H = 1200, 2
+    g = torch.Generator().manual_seed(31)
+    q = torch.randn(L, H, 64, generator=g)
+    k = torch.randn(L, H, 64, generator=g) * 0.3
+    v = torch.randn(L, H, 64, generator=g)
+    ramp = torch.linspace(0.0, 300.0, L).view(L, 1, 1)      # k gains a growing component along q's mean direction
+    k = k + ramp * q.mean(0, keepdim=True) / q.mean(0, keepdim=True).norm(dim=-1, keepdim=True)
+    q = q + 6.0 * q.mean(0, keepdim=True) / q.mean(0, keepdim=True).norm(dim=-1, keepdim=True)
+    q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
+    cu = np.array([0, L], dtype=np.int32)
+    got = modernbert.attention_varlen(q.to(DEV), k.to(DEV), v.to(DEV), cu, window=window).float().cpu()
+    ctx.sync()
+    want = oracle.attention(q, k, v, window)
+    scores = torch.einsum("ihd,jhd->hij", q.float(), k.float()) * 0.125 * 1.4426950408889634
+    # precondition of the case: even inside one 129-key band the maximum grows by more than two rescale thresholds
+    assert float((scores[:, 600, 600:665].max(-1).values - scores[:, 600, 536:600].max(-1).values).min()) > 16.0
+    assert torch.isfinite(got).all()
+    assert max_rel(got, want) <= 2e-2
