@@ -230,6 +230,85 @@ def run_encoder(args, rank, world, local_rank):
         torch.distributed.destroy_process_group()
 
 
+def run_tp(args, rank, world, local_rank):
+    """Secondary workload: the SwiGLU MLP of the 27B-shaped hybrid model (hidden 5120, intermediate 17408) on
+    `--tokens` packed tokens, tensor-parallel over the ranks: gate / up column-parallel with the gating fused,
+    down row-parallel with the residual fused on rank 0, partial sums exchanged by `s1_allreduce_bf16` in `--slabs`
+    row slabs so that the exchange of a slab runs under the projection of the next. Reports whole-job TFLOP/s, the
+    same step without the exchange, and the bus bandwidth of the bare all-reduce of the full [T, 5120] output."""
+    from sys1_b200 import device, tensor_parallel
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    H, I, T = 5120, 17408, args.tokens
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+        tp = tensor_parallel.TensorParallel.from_process_group(local_rank)
+    else:
+        tp = tensor_parallel.TensorParallel(device.load(local_rank), 0, 1)
+    ctx = tp.ctx
+    g = torch.Generator(device=dev).manual_seed(1005)
+    mk = lambda *shape: (torch.randn(*shape, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    # every rank builds only its own shard (same seed on all ranks: the full matrices would be identical)
+    gate, up, down = mk(I // world, H), mk(I // world, H), mk(H, I // world)
+    x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    out = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    from sys1_b200._lib import EPI_SWIGLU
+    from sys1_b200.linear import fused_linear
+    row = tensor_parallel.RowParallelLinear(down, tp, slabs=args.slabs)
+    hbuf = torch.empty(T, I // world, device=dev, dtype=torch.bfloat16)
+
+    def step(exchange=True):
+        fused_linear(x, gate, weight_up=up, epilogue=EPI_SWIGLU, out=hbuf, ctx=ctx)
+        if exchange:
+            row(hbuf, residual=x, out=out)
+        else:
+            fused_linear(hbuf, down, residual=x if rank == 0 else None, out=out, ctx=ctx)
+
+    def timed(fn, n):
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t[0])
+        return ms
+
+    warmup, steps = max(args.warmup, 3), min(args.steps, 20)
+    for _ in range(warmup):
+        step()
+    l0 = ctx.launch_count()
+    ms = timed(step, steps)
+    launches = ctx.launch_count() - l0
+    ms_math = timed(lambda: step(False), steps)
+    ms_ar = timed(lambda: ctx.all_reduce_(out), steps) if world > 1 else 0.0
+    ctx.sync()
+    if rank == 0:
+        flops = 6.0 * T * H * I
+        bytes_ar = T * H * 2
+        print(json.dumps({"metric": "tensor-parallel MLP TFLOP/s", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+                          "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": f"27B-shaped SwiGLU MLP (5120 -> 2 x 17408 -> 5120), T={T}, tensor parallel x{world}, "
+                                                 f"all-reduce in {args.slabs} row slabs", "parallelism": f"tp{world}",
+                                     "l2": "activations (x, h, out) exceed the 126 MB L2"},
+                          "ms_without_exchange": ms_math, "ms_allreduce_alone": ms_ar,
+                          "allreduce_busbw_gbs": (2.0 * (world - 1) / world * bytes_ar / (ms_ar * 1e-3) / 1e9) if world > 1 else None,
+                          "exchange_hidden_frac": (1.0 - (ms - ms_math) / ms_ar) if world > 1 and ms_ar > 0 else None,
+                          "gpu_launches": launches}))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -239,8 +318,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="projections", choices=["projections", "encoder"],
-                    help="projections (default, the headline microbench) or encoder: ModernBERT-large forward, tokens/s")
+    ap.add_argument("--workload", default="projections", choices=["projections", "encoder", "tp"],
+                    help="projections (default, the headline microbench); encoder: ModernBERT-large forward, tokens/s; "
+                         "tp: SwiGLU MLP of the 27B-shaped hybrid model, tensor-parallel over the ranks")
+    ap.add_argument("--slabs", type=int, default=4, help="tp workload: row slabs the all-reduce is pipelined in")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step from a CUDA graph (for small token budgets, where launching from Python is the bottleneck)")
     args = ap.parse_args()
@@ -274,6 +355,8 @@ def main():
 
     if args.workload == "encoder" and args.impl != "reference":
         return run_encoder(args, rank, world, local_rank)
+    if args.workload == "tp" and args.impl != "reference":
+        return run_tp(args, rank, world, local_rank)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: there is no CPU fallback for the product path (use --impl reference for the CPU arm)")
     from sys1_b200 import batching, device, linear, modernbert

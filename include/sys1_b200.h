@@ -225,6 +225,27 @@ int s1_rope(s1_ctx* ctx, void* x, long long ldx, const float* cos_table, const f
             int max_positions, int total_tokens, int heads, long long head_stride, int rotary_dim);
 
 /*
+ * Tensor parallelism: the sum over ranks that follows a row-parallel projection (each rank holds a K range of the
+ * weight and produces a partial [T, N]). The reference has no multi-GPU path (`device::load` opens GPU 0 only,
+ * src/device.rs:43-56); these entry points exist for the sharded projections of the large hybrid model.
+ * NCCL over NVLink underneath, looked up at run time (libnccl.so.2); single-GPU callers never need it.
+ *   s1_comm_unique_id : rank 0 makes the 128-byte id every rank passes to s1_comm_init (carry it over any channel)
+ *   s1_comm_init      : collective over all `size` ranks, one context (= one GPU) per rank
+ *   s1_allreduce_bf16 : in-place sum of `count` bf16 values over the ranks. Runs on a communication stream of the
+ *                       context's own, after everything queued on the context's stream so far; returns at once.
+ *                       Called slab by slab it overlaps the exchange of one slab with the projection of the next.
+ *   s1_allreduce_wait : orders the context's stream after every all-reduce issued so far (no host blocking)
+ *   s1_comm_destroy   : also done by s1_ctx_destroy
+ * Every rank must issue the same sequence of all-reduces with the same counts.
+ */
+#define S1_COMM_ID_BYTES 128
+int s1_comm_unique_id(void* id_out, char* err, size_t err_len);
+int s1_comm_init(s1_ctx* ctx, const void* id, int rank, int size);
+int s1_comm_destroy(s1_ctx* ctx);
+int s1_allreduce_bf16(s1_ctx* ctx, void* buf, size_t count);
+int s1_allreduce_wait(s1_ctx* ctx);
+
+/*
  * Packs the next sequences of a queue into one token-packed batch (host arrays, no GPU work).
  * Takes sequences in order while the running token count stays within `token_budget`; a sequence longer than
  * the budget forms a batch of its own. Writes cu_seqlens[0..num_taken] (cu_seqlens[0] = 0, last = total) and,

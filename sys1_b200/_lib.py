@@ -15,6 +15,7 @@ LIB_PATH = PKG / "libsys1_b200.so"
 S1_OK = 0
 S1_EINVAL, S1_ECUDA, S1_EDEVICE, S1_EKERNEL, S1_ENOMEM, S1_ELIMIT = -1, -2, -3, -4, -5, -6
 STATIC_MAX_TOKENS, STATIC_MAX_FEATURES = 262144, 32768
+COMM_ID_BYTES = 128
 EPI_NONE, EPI_GEGLU, EPI_SWIGLU = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
 
@@ -68,6 +69,11 @@ SIGNATURES = {
     "s1_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                                C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p,
                                C.c_longlong, C.c_void_p, C.c_size_t]),
+    "s1_comm_unique_id": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
+    "s1_comm_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "s1_comm_destroy": (C.c_int, [C.c_void_p]),
+    "s1_allreduce_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "s1_allreduce_wait": (C.c_int, [C.c_void_p]),
     "s1_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
                           C.c_longlong, C.c_longlong, C.c_int]),
     "s1_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,

@@ -21,7 +21,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "libsys1_b200.so"
 STAMP = PKG / "csrc" / ".build_stamp"
 
-SOURCES = ["api.cu", "linear_static.cu", "batching.cu", "delta_rule.cu", "delta_chunked.cu", "delta_io.cu", "attention.cu", "norm_rope.cu"]
+SOURCES = ["api.cu", "linear_static.cu", "batching.cu", "delta_rule.cu", "delta_chunked.cu", "delta_io.cu", "attention.cu", "norm_rope.cu", "comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
@@ -53,7 +53,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     if not force and LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == fp:
         return LIB
     srcs = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(ROOT / "include"), "-o", str(LIB), *srcs, "-lcudart"]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(ROOT / "include"), "-o", str(LIB), *srcs, "-lcudart", "-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

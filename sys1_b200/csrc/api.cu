@@ -59,6 +59,7 @@ extern "C" int s1_ctx_destroy(s1_ctx* ctx) {
     if (!ctx) return S1_EINVAL;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    s1_comm_destroy(ctx);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     delete ctx;
     return S1_OK;

@@ -1,0 +1,148 @@
+// The exchange step of tensor parallelism: an in-place bf16 sum over the ranks after a row-parallel projection
+// (o_proj, out_proj, down_proj of the large hybrid model), on NCCL over NVLink. The reference has no multi-GPU
+// path at all (`device::load` opens GPU 0 only, src/device.rs:43-56); this is the one collective the sharded
+// projection path needs.
+//
+// NCCL is looked up at run time (dlopen of libnccl.so.2: in a PyTorch process that is the copy PyTorch has
+// already loaded), so the library has no link-time dependency on it and single-GPU users never touch it.
+// All-reduces run on a communication stream of the context's own, ordered after the work already queued on the
+// context's stream; s1_allreduce_wait orders the context's stream after them. Issued slab by slab, the sum of one
+// slab of rows travels while the projection of the next slab computes.
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "sys1_b200.h"
+#include "context.h"
+
+namespace {
+
+struct NcclApi {
+    void* handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    const char* why = nullptr;
+};
+
+NcclApi* nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (tried) return &api;
+    tried = true;
+    for (const char* name : {"libnccl.so.2", "libnccl.so"}) {
+        api.handle = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+        if (api.handle) break;
+    }
+    if (!api.handle) {
+        api.why = "libnccl.so.2 not found";
+        return &api;
+    }
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
+    api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
+    if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllReduce || !api.GetErrorString) {
+        api.why = "libnccl.so.2 lacks an expected symbol";
+        api.handle = nullptr;
+    }
+    return &api;
+}
+
+static_assert(sizeof(ncclUniqueId) == S1_COMM_ID_BYTES, "communicator id size");
+
+}  // namespace
+
+extern "C" int s1_comm_unique_id(void* id_out, char* err, size_t err_len) {
+    auto say = [&](const char* msg) {
+        if (err && err_len) snprintf(err, err_len, "%s", msg);
+    };
+    if (!id_out) {
+        say("s1_comm_unique_id: null pointer");
+        return S1_EINVAL;
+    }
+    NcclApi* api = nccl_api();
+    if (!api->handle) {
+        say(api->why);
+        return S1_EDEVICE;
+    }
+    ncclUniqueId id;
+    const ncclResult_t rc = api->GetUniqueId(&id);
+    if (rc != ncclSuccess) {
+        say(api->GetErrorString(rc));
+        return S1_ECUDA;
+    }
+    memcpy(id_out, &id, sizeof(id));
+    return S1_OK;
+}
+
+extern "C" int s1_comm_init(s1_ctx* ctx, const void* id, int rank, int size) {
+    if (!ctx) return S1_EINVAL;
+    if (!id || size < 1 || rank < 0 || rank >= size) return s1_fail(ctx, S1_EINVAL, "s1_comm_init: bad rank %d of %d", rank, size);
+    if (ctx->comm) return s1_fail(ctx, S1_EINVAL, "s1_comm_init: the context already has a communicator");
+    NcclApi* api = nccl_api();
+    if (!api->handle) return s1_fail(ctx, S1_EDEVICE, "s1_comm_init: %s", api->why);
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    ncclUniqueId uid;
+    memcpy(&uid, id, sizeof(uid));
+    ncclComm_t comm = nullptr;
+    const ncclResult_t rc = api->CommInitRank(&comm, size, uid, rank);
+    if (rc != ncclSuccess) return s1_fail(ctx, S1_ECUDA, "ncclCommInitRank failed: %s", api->GetErrorString(rc));
+    cudaError_t e = cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_ready, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+        api->CommDestroy(comm);
+        return s1_fail(ctx, S1_ECUDA, "s1_comm_init: %s", cudaGetErrorString(e));
+    }
+    ctx->comm = comm;
+    ctx->comm_rank = rank;
+    ctx->comm_size = size;
+    ctx->comm_pending = false;
+    return S1_OK;
+}
+
+extern "C" int s1_comm_destroy(s1_ctx* ctx) {
+    if (!ctx) return S1_EINVAL;
+    if (!ctx->comm) return S1_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->comm_stream);
+    nccl_api()->CommDestroy(static_cast<ncclComm_t>(ctx->comm));
+    cudaEventDestroy(ctx->comm_ready);
+    cudaEventDestroy(ctx->comm_done);
+    cudaStreamDestroy(ctx->comm_stream);
+    ctx->comm = nullptr;
+    ctx->comm_stream = nullptr;
+    ctx->comm_size = 0;
+    return S1_OK;
+}
+
+extern "C" int s1_allreduce_bf16(s1_ctx* ctx, void* buf, size_t count) {
+    if (!ctx) return S1_EINVAL;
+    if (!ctx->comm) return s1_fail(ctx, S1_EINVAL, "s1_allreduce_bf16: the context has no communicator (s1_comm_init)");
+    if (!buf && count) return s1_fail(ctx, S1_EINVAL, "s1_allreduce_bf16: null pointer");
+    if (count == 0) return S1_OK;
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    S1_CUDA_OK(ctx, cudaEventRecord(ctx->comm_ready, ctx->stream));
+    S1_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->comm_ready, 0));
+    NcclApi* api = nccl_api();
+    const ncclResult_t rc = api->AllReduce(buf, buf, count, ncclBfloat16, ncclSum, static_cast<ncclComm_t>(ctx->comm), ctx->comm_stream);
+    if (rc != ncclSuccess) return s1_fail(ctx, S1_ECUDA, "ncclAllReduce failed: %s", api->GetErrorString(rc));
+    S1_CUDA_OK(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
+    ctx->comm_pending = true;
+    return S1_OK;
+}
+
+extern "C" int s1_allreduce_wait(s1_ctx* ctx) {
+    if (!ctx) return S1_EINVAL;
+    if (!ctx->comm_pending) return S1_OK;
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    S1_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->comm_done, 0));
+    ctx->comm_pending = false;
+    return S1_OK;
+}

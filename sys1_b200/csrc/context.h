@@ -46,6 +46,11 @@ struct s1_ctx {
     PFN_cuTensorMapEncodeTiled encode = nullptr;
     std::unordered_map<S1TmapKey, CUtensorMap, S1TmapKeyHash> tmaps;
     std::vector<unsigned char> host_scratch;  // host staging for small tables copied to the device
+    void* comm = nullptr;                     // ncclComm_t once s1_comm_init has run
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t comm_ready = nullptr, comm_done = nullptr;
+    int comm_rank = 0, comm_size = 0;
+    bool comm_pending = false;
     char err[512] = {0};
 };
 

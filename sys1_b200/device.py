@@ -64,6 +64,28 @@ class Context:
     def set_option(self, name: str, value: int) -> None:
         self.check(self._lib.s1_set_option(self.handle, name.encode(), int(value)))
 
+    # -- tensor-parallel exchange -----------------------------------------------------------------
+    def comm_init(self, rank: int, size: int, unique_id: bytes) -> None:
+        """Collective: every rank calls it with the id rank 0 got from `comm_unique_id()`."""
+        if len(unique_id) != _lib.COMM_ID_BYTES:
+            raise ValueError("the communicator id has 128 bytes")
+        buf = C.create_string_buffer(unique_id, _lib.COMM_ID_BYTES)
+        self.check(self._lib.s1_comm_init(self.handle, C.cast(buf, C.c_void_p), int(rank), int(size)))
+        self.comm_rank, self.comm_size = int(rank), int(size)
+
+    def all_reduce_(self, t: torch.Tensor, wait: bool = True) -> torch.Tensor:
+        """In-place bf16 sum over the ranks (`s1_allreduce_bf16`), after the work queued on this context's stream.
+        With `wait=False` the context's stream is not held back: call `all_reduce_wait()` before using `t`."""
+        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError("all_reduce_ takes a contiguous bf16 CUDA tensor")
+        self.check(self._lib.s1_allreduce_bf16(self.handle, C.c_void_p(t.data_ptr()), t.numel()))
+        if wait:
+            self.all_reduce_wait()
+        return t
+
+    def all_reduce_wait(self) -> None:
+        self.check(self._lib.s1_allreduce_wait(self.handle))
+
     def close(self) -> None:
         if getattr(self, "_h", None) is not None:
             self._lib.s1_ctx_destroy(self._h)
@@ -77,6 +99,17 @@ class Context:
 
 
 _contexts: Dict[Tuple[int, int], Context] = {}
+
+
+def comm_unique_id() -> bytes:
+    """The id rank 0 creates and hands to every rank's `Context.comm_init` (over any channel)."""
+    lib = _lib.load_library()
+    buf = C.create_string_buffer(_lib.COMM_ID_BYTES)
+    err = C.create_string_buffer(256)
+    rc = lib.s1_comm_unique_id(C.cast(buf, C.c_void_p), err, 256)
+    if rc != _lib.S1_OK:
+        raise S1Error(rc, err.value.decode("utf-8", "replace"))
+    return buf.raw
 
 
 def load(ordinal: Optional[int] = None) -> Context:

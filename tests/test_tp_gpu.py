@@ -1,0 +1,83 @@
+"""Tensor-parallel SwiGLU MLP on two GPUs (one process each): column-parallel gate / up, row-parallel down, the
+partials summed by `s1_allreduce_bf16` slab by slab. Checked against the unsharded product on one GPU and the f32
+CPU oracle (max-relative 2e-2: the partial sums are rounded to bf16 before they are added), and all ranks must end
+up with bit-identical outputs. Needs two GPUs; on a single-GPU box the test is skipped."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from sys1_b200 import qwen35, tensor_parallel
+        from sys1_b200.linear import Linear
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        tp = tensor_parallel.TensorParallel.from_process_group(rank)
+        g = torch.Generator().manual_seed(1005)
+        T, H, I = 1000, 1024, 2048  # 1000 rows: the last slab is ragged
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        wg, wu, wd = ((torch.randn(I, H, generator=g) * 0.02).to(torch.bfloat16), (torch.randn(I, H, generator=g) * 0.02).to(torch.bfloat16),
+                      (torch.randn(H, I, generator=g) * 0.02).to(torch.bfloat16))
+        xd, wgd, wud, wdd = (t.to(dev) for t in (x, wg, wu, wd))
+        mlp = tensor_parallel.Mlp(wgd, wud, wdd, tp, slabs=3)
+        for _ in range(2):  # twice: the second pass reuses streams, events and the communicator
+            y = mlp(xd, residual=xd)
+        tp.ctx.sync()
+        torch.cuda.synchronize()
+        single = qwen35.Mlp(Linear(wgd), Linear(wud), Linear(wdd)).forward(xd, residual=xd)
+        want = oracle.mlp_qwen35(x.float(), wg.float(), wu.float(), wd.float(), residual=x.float(), dtype="f32")
+        scale = float(want.abs().max())
+        err_single = float((y.float() - single.float()).abs().max()) / scale
+        err_oracle = float((y.float().cpu() - want).abs().max()) / scale
+        gathered = [torch.zeros(T, H, dtype=torch.bfloat16) for _ in range(world)]
+        dist.all_gather(gathered, y.cpu())
+        same = all(torch.equal(gathered[0], t) for t in gathered[1:])
+        # a bare all-reduce: sum of rank-dependent values
+        t = torch.full((4096,), float(rank + 1), dtype=torch.bfloat16, device=dev)
+        tp.ctx.all_reduce_(t)
+        torch.cuda.synchronize()
+        ok_sum = bool((t == float(sum(range(1, world + 1)))).all())
+        q.put((rank, err_single, err_oracle, same, ok_sum))
+    except Exception as exc:  # pragma: no cover
+        q.put((rank, repr(exc)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_tensor_parallel_mlp_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=240) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+    for r in results:
+        assert len(r) == 5, r
+        rank, err_single, err_oracle, same, ok_sum = r
+        assert err_single <= 2e-2 and err_oracle <= 2e-2, r
+        assert same and ok_sum, r
