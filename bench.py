@@ -43,8 +43,8 @@ FLOPS_PER_TOKEN = sum(2 * k * n for _, k, n, _, _ in PROJECTIONS)  # 10,027,008
 SEED = 1002
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch at T = 32768, from the ncu capture
 # summarised in profiles/gemm_projections_T32768.md (scaled by T / 32768 for other sizes).
-NCU_TRAFFIC_BYTES = {"wi+geglu": 89_369_088, "wqkv": 153_107_456, "wo+residual": 125_161_216,
-                     "mlp_out+residual": 152_696_576}
+NCU_TRAFFIC_BYTES = {"wi+geglu": 88_296_704, "wqkv": 151_915_520, "wo+residual": 107_385_088,
+                     "mlp_out+residual": 142_664_448}
 FALLBACK_PEAK_TFLOPS = 1590.0
 
 
