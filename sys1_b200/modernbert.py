@@ -1,7 +1,7 @@
 """Projection side of the ModernBERT layer (`src/archs/modernbert.rs`): Wqkv, Wo(+residual), Wi+GeGLU, MLP-out(+residual).
 
 Same member names as the reference structs (`Attention { wqkv, wo }` :137-175, `Mlp { input, output }`
-:494-534, `Norm` :1006-1034, `RotaryEmbedding` :1100-1160), each a thin caller of the C ABI, and `Encoder`, the
+:494-534, `Norm` :1006-1034, `RotaryEmbedding` :58-129), each a thin caller of the C ABI, and `Encoder`, the
 layer stack on a token-packed batch.
 """
 from __future__ import annotations
