@@ -196,6 +196,24 @@ int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const void* k, long 
                  float scale, void* out, long long ldo, void* workspace, size_t workspace_bytes);
 
 /*
+ * Causal grouped-query softmax attention over a packed batch in flash form, head_dim = 256: the attention core of
+ * the reference's `FullAttention::forward` (src/archs/qwen35_text.rs:312-411),
+ *     a_i = sum_{j <= i} softmax_j(scale * q_i . k_j) v_j     over the keys j of the same sequence,
+ * query head h reading KV head h / (heads / kv_heads) (`repeat_kv`, :363-369), with the layer's output gate fused
+ * into the write-out when `gate` is not NULL: out = bf16(a) * bf16(sigmoid(gate)) (:325-329, :408).
+ * q: bf16, head h of token t at q + t * ldq + h * q_head_stride (so the query halves of the interleaved q_proj
+ * output, [T, heads, 2, 256], are read in place with q_head_stride = 512, and gate = q + 256 likewise);
+ * k, v: bf16 [T, kv_heads * 256] views with their own strides; out: bf16 [T, heads * 256] (what o_proj consumes).
+ * `cu_seqlens_host`: HOST int32 [num_seqs + 1]; `workspace`: device memory of s1_attention_gqa_workspace(...) bytes.
+ */
+size_t s1_attention_gqa_workspace(int num_seqs, int total_tokens);
+int s1_attention_gqa(s1_ctx* ctx, const void* q, long long ldq, long long q_head_stride, const void* k, long long ldk,
+                     long long k_head_stride, const void* v, long long ldv, long long v_head_stride, const void* gate,
+                     long long ldg, long long gate_head_stride, const int32_t* cu_seqlens_host, int num_seqs,
+                     int total_tokens, int heads, int kv_heads, int head_dim, float scale, void* out, long long ldo,
+                     void* workspace, size_t workspace_bytes);
+
+/*
  * Row-wise normalisation of a bf16 matrix, statistics in f32, one rounding at the end:
  *     kind 0  y = (x - mean(x)) / sqrt(var(x) + eps) * weight        LayerNorm without bias: the reference's `Norm`
  *                                                                    (src/archs/modernbert.rs:1006-1034)

@@ -11,6 +11,8 @@ Pinning status
     from the exact-erf GELU definition the test itself uses).
   * RoPE: checked the way the reference's own test does (fused index arithmetic against the plain rotate-half on
     the test's formula inputs; that test holds no expected numbers). Norms: restated from the cited formulas.
+  * Qwen3.5 decoder stack (oracle/qwen35.py) and ModernBERT encoder stack (oracle/modernbert.py): cross-checked
+    against the `transformers` implementations of the same architectures on random-init weights (f32, 1e-5).
   * Linear / GEMM arithmetic: PARITY UNPINNED - the only reference tests that pin it are whole-model snapshots
     that need Hugging Face checkpoints which are not available offline, and the arithmetic itself lives in
     third-party crates (candle-core / candle-nn 0.11.0, gemm 0.19.0) whose source is not part of the reference
@@ -20,3 +22,5 @@ from .projection import (geglu, linear, mlp_modernbert, mlp_qwen35, round_bf16, 
 from .delta_rule import (causal_conv_silu, chunked_delta_rule, delta_inputs, finish_delta, sequential_delta_rule)  # noqa: F401
 from .norm import layer_norm, rms_norm, rope, rope_qkv_indexed, rope_qkv_test_inputs  # noqa: F401,E402
 from .modernbert import EncoderConfig, attention, encoder_forward, encoder_layer, init_weights  # noqa: F401,E402
+from .qwen35 import DecoderConfig, causal_attention, decoder_forward, decoder_layer  # noqa: F401,E402
+from . import qwen35  # noqa: F401,E402

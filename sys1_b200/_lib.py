@@ -69,6 +69,11 @@ SIGNATURES = {
     "s1_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                                C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p,
                                C.c_longlong, C.c_void_p, C.c_size_t]),
+    "s1_attention_gqa_workspace": (C.c_size_t, [C.c_int, C.c_int]),
+    "s1_attention_gqa": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_void_p, C.c_longlong, C.c_longlong,
+                                   C.c_void_p, C.c_longlong, C.c_longlong, C.c_void_p, C.c_longlong, C.c_longlong,
+                                   C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p,
+                                   C.c_longlong, C.c_void_p, C.c_size_t]),
     "s1_comm_unique_id": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t]),
     "s1_comm_init": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "s1_comm_destroy": (C.c_int, [C.c_void_p]),

@@ -1,7 +1,8 @@
 """Projection side and linear-attention recurrence of the Qwen3.5 layer (`src/archs/qwen35_text.rs`).
 
 `Mlp` mirrors `Mlp { gate, up, down }` (:205-241); `chunked_delta_rule` mirrors the free function of the same
-name (:789-807). Norms, RoPE, attention and the causal conv stay with the caller.
+name (:789-807); `RmsNorm`, `FullAttention`, `LinearAttention`, `Layer` and `Decoder` mirror the structs of the same
+names on a token-packed batch. Everything runs through the C ABI.
 """
 from __future__ import annotations
 
@@ -11,8 +12,21 @@ from typing import Optional
 import torch
 
 from . import device
+from . import norm as _norm
 from ._lib import EPI_SWIGLU
 from .linear import Linear, fused_linear
+
+
+class RmsNorm:
+    """`RmsNorm` (src/archs/qwen35_text.rs:178-203): x / sqrt(mean(x^2) + eps) * (1 + weight), through `s1_norm`."""
+
+    def __init__(self, weight: torch.Tensor, eps: float):
+        self.weight, self.eps = weight.contiguous(), float(eps)
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return _norm.norm(x, self.weight, self.eps, _norm.RMS_NORM, out=out)
+
+    __call__ = forward
 
 
 class Mlp:
@@ -159,3 +173,133 @@ class LinearAttention:
             len(cu) - 1, T, self.key_heads, self.value_heads, C.c_void_p(y.data_ptr()), y.stride(0), C.c_void_p(ptr), need)
         ctx.check(rc)
         return self.output.forward(y, residual=residual)                           # out_proj (+ the layer's residual, :938)
+
+
+class RopeParams:
+    """`RopeParams` (src/archs/qwen35_text.rs:101-165) for text-only inputs (the three position axes coincide):
+    tables `[positions, rotary_dim / 2]`, phase = position / theta^(2 j / rotary_dim), values rounded to the model
+    dtype (bf16) as the reference casts its tables, kept as f32 for `s1_rope`."""
+
+    def __init__(self, theta: float, rotary_dim: int, max_positions: int, dev):
+        div = torch.tensor([float(theta) ** (2.0 * j / rotary_dim) for j in range(rotary_dim // 2)], dtype=torch.float64).to(torch.float32).to(dev)
+        phase = torch.arange(max_positions, dtype=torch.float32, device=dev).unsqueeze(1) / div.unsqueeze(0)
+        self.cos = phase.cos().to(torch.bfloat16).float().contiguous()
+        self.sin = phase.sin().to(torch.bfloat16).float().contiguous()
+        self.rotary_dim = rotary_dim
+
+
+def attention_causal_gqa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_host, gate: Optional[torch.Tensor] = None,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal grouped-query attention over a packed batch through `s1_attention_gqa` (head dim 256):
+    q `[T, H, 256]` (rows may be strided: the query halves of the interleaved q_proj output), k, v `[T, KV, 256]`,
+    optional `gate [T, H, 256]` (pre-sigmoid; the output is multiplied by sigmoid(gate)). Returns `[T, H * 256]`."""
+    import numpy as np
+    T, H, D = q.shape
+    KV = k.shape[1]
+    cu = np.ascontiguousarray(cu_seqlens_host, dtype=np.int32)
+    if out is None:
+        out = torch.empty((T, H * D), dtype=torch.bfloat16, device=q.device)
+    if T == 0:
+        return out
+    for name, t in (("q", q), ("k", k), ("v", v)) + ((("gate", gate),) if gate is not None else ()):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(2) != 1:
+            raise ValueError(f"{name} must be a bf16 CUDA tensor [T, heads, 256] with contiguous head rows (no CPU fallback)")
+    ctx = device.load(q.device.index)
+    need = int(ctx._lib.s1_attention_gqa_workspace(len(cu) - 1, T))
+    ws = _workspace(q.device, need)
+    rc = ctx._lib.s1_attention_gqa(
+        ctx.handle, C.c_void_p(q.data_ptr()), q.stride(0), q.stride(1), C.c_void_p(k.data_ptr()), k.stride(0), k.stride(1),
+        C.c_void_p(v.data_ptr()), v.stride(0), v.stride(1), C.c_void_p(gate.data_ptr() if gate is not None else 0),
+        gate.stride(0) if gate is not None else 0, gate.stride(1) if gate is not None else 0,
+        cu.ctypes.data_as(C.POINTER(C.c_int32)), len(cu) - 1, T, H, KV, D, C.c_float(D ** -0.5), C.c_void_p(out.data_ptr()),
+        out.stride(0), C.c_void_p(ws.data_ptr()), ws.numel())
+    ctx.check(rc)
+    return out
+
+
+class FullAttention:
+    """`FullAttention` (src/archs/qwen35_text.rs:242-411) on a packed batch, same member names: `q` (query and output
+    gate interleaved per head), `k`, `v`, `output`, `q_norm`, `k_norm`."""
+
+    def __init__(self, q: Linear, k: Linear, v: Linear, output: Linear, q_norm: RmsNorm, k_norm: RmsNorm, heads: int, kv_heads: int,
+                 head_dim: int, rope: RopeParams, core: str = "s1"):
+        self.q, self.k, self.v, self.output, self.q_norm, self.k_norm = q, k, v, output, q_norm, k_norm
+        self.heads, self.kv_heads, self.head_dim, self.rope, self.core = heads, kv_heads, head_dim, rope, core
+
+    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T, H, KV, D = x.shape[0], self.heads, self.kv_heads, self.head_dim
+        qg = self.q.forward(x)                                  # [T, H * 2 * D]: per head [query | gate]
+        k, v = self.k.forward(x), self.v.forward(x)             # [T, KV * D]
+        heads_q = qg.view(T * H, 2 * D)
+        self.q_norm.forward(heads_q[:, :D], out=heads_q[:, :D])  # per-head RMS norm of the query halves, in place
+        self.k_norm.forward(k.view(T * KV, D), out=k.view(T * KV, D))
+        _norm.rope_(qg, self.rope.cos, self.rope.sin, positions, H, 2 * D, self.rope.rotary_dim)
+        _norm.rope_(k, self.rope.cos, self.rope.sin, positions, KV, D, self.rope.rotary_dim)
+        q4 = qg.view(T, H, 2, D)
+        if self.core == "s1":
+            gated = attention_causal_gqa(q4[:, :, 0], k.view(T, KV, D), v.view(T, KV, D), cu_seqlens_host, gate=q4[:, :, 1])
+        else:  # comparison arm: PyTorch attention per sequence
+            F = torch.nn.functional
+            attn = torch.empty((T, H, D), dtype=torch.bfloat16, device=x.device)
+            bounds = [int(b) for b in cu_seqlens_host]
+            for a, b in zip(bounds[:-1], bounds[1:]):
+                if a == b:
+                    continue
+                o = F.scaled_dot_product_attention(q4[a:b, :, 0].transpose(0, 1).unsqueeze(0), k.view(T, KV, D)[a:b].transpose(0, 1).unsqueeze(0),
+                                                   v.view(T, KV, D)[a:b].transpose(0, 1).unsqueeze(0), is_causal=True, enable_gqa=True)
+                attn[a:b] = o[0].transpose(0, 1)
+            gated = (attn * torch.sigmoid(q4[:, :, 1])).reshape(T, H * D)
+        return self.output.forward(gated, residual=residual)
+
+
+class Layer:
+    """`Layer` (src/archs/qwen35_text.rs:890-940): x + mixer(RMS(x)), then x + MLP(RMS(x)); both residual adds are
+    fused into the output projections."""
+
+    def __init__(self, input_norm: RmsNorm, mixer, post_norm: RmsNorm, mlp: Mlp):
+        self.input_norm, self.mixer, self.post_norm, self.mlp = input_norm, mixer, post_norm, mlp
+
+    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor) -> torch.Tensor:
+        x = self.mixer.forward(self.input_norm(x), cu_seqlens_host, positions, residual=x)
+        return self.mlp.forward(self.post_norm(x), residual=x)
+
+
+class Decoder:
+    """`Decoder::forward` (src/archs/qwen35_text.rs:942-1005) on a token-packed batch. `weights`: dict with the names of
+    `oracle.qwen35.init_weights` (bf16 CUDA tensors; A_log / dt_bias f32); `cfg`: the fields of
+    `oracle.qwen35.DecoderConfig`. `core`: "s1" (this library's attention kernel) or "torch" (comparison arm)."""
+
+    def __init__(self, weights, cfg, core: str = "s1", max_positions: int = 8192):
+        self.cfg, self.w = cfg, weights
+        dev = weights["embed_tokens"].device
+        lin = lambda name: Linear(weights[name])
+        rope = RopeParams(cfg.rope_theta, cfg.rotary_dim, max_positions, dev)
+        self.layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"layers.{i}."
+            if cfg.layer_type(i) == "full_attention":
+                a = p + "self_attn."
+                mixer = FullAttention(lin(a + "q_proj"), lin(a + "k_proj"), lin(a + "v_proj"), lin(a + "o_proj"),
+                                      RmsNorm(weights[a + "q_norm"], cfg.rms_norm_eps), RmsNorm(weights[a + "k_norm"], cfg.rms_norm_eps),
+                                      cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, rope, core)
+            else:
+                a = p + "linear_attn."
+                mixer = LinearAttention(lin(a + "in_proj_qkv"), lin(a + "in_proj_z"), lin(a + "in_proj_b"), lin(a + "in_proj_a"),
+                                        weights[a + "conv1d"], -torch.exp(weights[a + "A_log"].float()), weights[a + "dt_bias"].float(),
+                                        weights[a + "norm"], lin(a + "out_proj"), cfg.linear_num_key_heads, cfg.linear_num_value_heads,
+                                        cfg.rms_norm_eps)
+            self.layers.append(Layer(RmsNorm(weights[p + "input_layernorm"], cfg.rms_norm_eps), mixer,
+                                     RmsNorm(weights[p + "post_attention_layernorm"], cfg.rms_norm_eps),
+                                     Mlp(lin(p + "mlp.gate_proj"), lin(p + "mlp.up_proj"), lin(p + "mlp.down_proj"))))
+        self.norm = RmsNorm(weights["norm"], cfg.rms_norm_eps)
+
+    def forward(self, ids: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, collect: bool = False):
+        x = self.w["embed_tokens"][ids.long()]
+        pos = positions.to(torch.int32).contiguous()
+        states = []
+        for layer in self.layers:
+            x = layer.forward(x, cu_seqlens_host, pos)
+            if collect:
+                states.append(x.clone())
+        y = self.norm(x)
+        return (y, states) if collect else y

@@ -245,3 +245,35 @@ def test_norms_match_their_definitions():
     cos, sin = torch.rand(7, 8), torch.rand(7, 8)
     y = oracle.rope(x.view(7, 3, 32), cos, sin, rotary_dim=16)
     assert torch.equal(y[..., 16:], x.view(7, 3, 32)[..., 16:])
+
+
+def test_qwen35_decoder_oracle_matches_transformers():
+    """The decoder restatement (full attention with interleaved gate, per-head q / k norms, partial rope, causal
+    GQA; linear attention; (1 + w) RMSNorm; SwiGLU) against `transformers`' Qwen3.5 text model, an independent
+    implementation of the same architecture, on random-init weights in f32."""
+    cfg_mod = pytest.importorskip("transformers.models.qwen3_5.configuration_qwen3_5")
+    mod = pytest.importorskip("transformers.models.qwen3_5.modeling_qwen3_5")
+    cfg = oracle.DecoderConfig(vocab_size=100, hidden_size=64, intermediate_size=96, num_hidden_layers=4, num_attention_heads=2,
+                               num_key_value_heads=1, head_dim=32, linear_num_key_heads=2, linear_num_value_heads=4,
+                               linear_key_head_dim=16, linear_value_head_dim=16)
+    w = oracle.qwen35.init_weights(cfg, 77)
+    hf_cfg = cfg_mod.Qwen3_5TextConfig(
+        vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+        num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads,
+        num_key_value_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, rms_norm_eps=cfg.rms_norm_eps,
+        linear_num_key_heads=cfg.linear_num_key_heads, linear_num_value_heads=cfg.linear_num_value_heads,
+        linear_key_head_dim=cfg.linear_key_head_dim, linear_value_head_dim=cfg.linear_value_head_dim,
+        layer_types=[cfg.layer_type(i) for i in range(cfg.num_hidden_layers)],
+        rope_parameters={"rope_type": "default", "rope_theta": cfg.rope_theta, "partial_rotary_factor": cfg.partial_rotary_factor,
+                         "mrope_section": [2, 1, 1]})
+    model = mod.Qwen3_5TextModel(hf_cfg).eval()
+    sd = model.state_dict()
+    for name, t in w.items():
+        key = name if name in sd else name + ".weight"
+        assert key in sd and sd[key].shape == t.shape, (name, key)
+        sd[key].copy_(t)
+    ids = torch.randint(0, cfg.vocab_size, (37,), generator=torch.Generator().manual_seed(78))
+    with torch.no_grad():
+        want = model(input_ids=ids.unsqueeze(0)).last_hidden_state[0]
+    got = oracle.decoder_forward(ids, w, cfg, dtype="f32")
+    assert (got - want).abs().max() <= 1e-4 * float(want.abs().max())
