@@ -230,6 +230,86 @@ def run_encoder(args, rank, world, local_rank):
         torch.distributed.destroy_process_group()
 
 
+def run_decoder(args, rank, world, local_rank):
+    """Secondary workload: Qwen3.5-small-shaped hybrid decoder forward (24 layers = (linear, linear, linear, full) x 6,
+    hidden 1024, 16 x 128 delta-rule heads, conv 4, full attention 8 query / 2 KV heads x 256, SwiGLU 3584) over a
+    packed batch of `--tokens` tokens (default here 16384) with lengths uniform in [64, 2048], one replica per GPU.
+    Every stage but the embedding lookup goes through the C ABI."""
+    from types import SimpleNamespace
+    from sys1_b200 import batching, device, qwen35
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    cfg = SimpleNamespace(vocab_size=151936, hidden_size=1024, intermediate_size=3584, num_hidden_layers=24, num_attention_heads=8,
+                          num_key_value_heads=2, head_dim=256, rms_norm_eps=1e-6, rope_theta=1e7, rotary_dim=64,
+                          linear_num_key_heads=16, linear_num_value_heads=16, linear_key_head_dim=128, linear_value_head_dim=128,
+                          linear_conv_kernel_dim=4, layer_type=lambda i: "full_attention" if (i + 1) % 4 == 0 else "linear_attention")
+    g = torch.Generator(device=dev).manual_seed(1004)
+    mk = lambda *shape, s=0.02: (torch.randn(*shape, device=dev, generator=g) * s).to(torch.bfloat16)
+    H, KV, D, Hk, Hv = 8, 2, 256, 16, 16
+    w = {"embed_tokens": mk(cfg.vocab_size, cfg.hidden_size, s=1.0), "norm": mk(cfg.hidden_size, s=0.1)}
+    for i in range(cfg.num_hidden_layers):
+        p = f"layers.{i}."
+        w[p + "input_layernorm"], w[p + "post_attention_layernorm"] = mk(1024, s=0.1), mk(1024, s=0.1)
+        w[p + "mlp.gate_proj"], w[p + "mlp.up_proj"], w[p + "mlp.down_proj"] = mk(3584, 1024), mk(3584, 1024), mk(1024, 3584)
+        if cfg.layer_type(i) == "full_attention":
+            a = p + "self_attn."
+            w[a + "q_proj"], w[a + "k_proj"], w[a + "v_proj"], w[a + "o_proj"] = mk(H * D * 2, 1024), mk(KV * D, 1024), mk(KV * D, 1024), mk(1024, H * D)
+            w[a + "q_norm"], w[a + "k_norm"] = mk(D, s=0.1), mk(D, s=0.1)
+        else:
+            a = p + "linear_attn."
+            width = 2 * Hk * 128 + Hv * 128
+            w[a + "in_proj_qkv"], w[a + "in_proj_z"] = mk(width, 1024), mk(Hv * 128, 1024)
+            w[a + "in_proj_b"], w[a + "in_proj_a"] = mk(Hv, 1024, s=0.1), mk(Hv, 1024, s=0.1)
+            w[a + "conv1d"] = mk(width, 1, 4, s=0.3)
+            w[a + "A_log"] = torch.randn(Hv, device=dev, generator=g) * 0.5
+            w[a + "dt_bias"] = torch.randn(Hv, device=dev, generator=g) * 0.5
+            w[a + "norm"] = (1.0 + torch.randn(128, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+            w[a + "out_proj"] = mk(1024, Hv * 128)
+    dec = qwen35.Decoder(w, cfg)
+    ctx = device.load(local_rank)
+    T = args.tokens if args.tokens != 32768 else 16384
+    lens = batching.synthetic_lengths(1004 + rank, 64, 2048, T)
+    batch, _ = batching.pack_next(lens, batching.BatcherConfig(token_budget=T))
+    ids = torch.randint(0, cfg.vocab_size, (T,), device=dev, generator=g)
+    pos = torch.from_numpy(batch.positions).to(dev)
+    warmup, steps = max(args.warmup, 3), min(args.steps, 20)
+    for _ in range(warmup):
+        dec.forward(ids, batch.cu_seqlens, pos)
+    ctx.sync()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        dec.forward(ids, batch.cu_seqlens, pos)
+    e1.record()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t[0])
+    ctx.sync()
+    if rank == 0:
+        flops_tok = 18 * 43_057_152 + 6 * 36_700_160  # projection flops per token: linear-attention / full-attention layers
+        print(json.dumps({"metric": "decoder tokens/s", "value": world * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                          "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": f"Qwen3.5-small-shaped hybrid decoder forward, packed T={T}, lengths U[64,2048], "
+                                                 "every stage but the embedding lookup through the C ABI",
+                                     "sequences": int(len(lens)), "parallelism": f"replicas x{world}"},
+                          "projection_tflops": world * T * flops_tok / (ms * 1e-3) / 1e12,
+                          "gpu_launches": ctx.launch_count() - l0}))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
 def run_tp(args, rank, world, local_rank):
     """Secondary workload: the SwiGLU MLP of the 27B-shaped hybrid model (hidden 5120, intermediate 17408) on
     `--tokens` packed tokens, tensor-parallel over the ranks: gate / up column-parallel with the gating fused,
@@ -318,7 +398,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="projections", choices=["projections", "encoder", "tp"],
+    ap.add_argument("--workload", default="projections", choices=["projections", "encoder", "decoder", "tp"],
                     help="projections (default, the headline microbench); encoder: ModernBERT-large forward, tokens/s; "
                          "tp: SwiGLU MLP of the 27B-shaped hybrid model, tensor-parallel over the ranks")
     ap.add_argument("--slabs", type=int, default=4, help="tp workload: row slabs the all-reduce is pipelined in")
@@ -355,6 +435,8 @@ def main():
 
     if args.workload == "encoder" and args.impl != "reference":
         return run_encoder(args, rank, world, local_rank)
+    if args.workload == "decoder" and args.impl != "reference":
+        return run_decoder(args, rank, world, local_rank)
     if args.workload == "tp" and args.impl != "reference":
         return run_tp(args, rank, world, local_rank)
     if not torch.cuda.is_available():

@@ -49,6 +49,65 @@ __global__ void __launch_bounds__(256) s1_conv_silu_kernel(const __nv_bfloat16* 
     *reinterpret_cast<uint4*>(y + static_cast<long long>(t) * ldy + c0) = *reinterpret_cast<const uint4*>(out);
 }
 
+// The same arithmetic for the usual 4 taps with each thread walking TT consecutive tokens of its 8 channels: the
+// weights (64 contiguous bytes) and the previous three rows stay in registers, so every input row is read once and the
+// weights once per TT tokens (the per-token kernel above re-reads both for every token, and its 2-byte weight loads
+// spread one warp access over 16 cache lines).
+template <int TAPS, int TT>
+__global__ void __launch_bounds__(256) s1_conv_silu_walk_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                                const __nv_bfloat16* __restrict__ w, const int32_t* __restrict__ positions,
+                                                                int T, int C, __nv_bfloat16* __restrict__ y, long long ldy) {
+    const int groups = C / 8;
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long chunks = (T + TT - 1) / TT;
+    if (idx >= chunks * groups) return;
+    const int c0 = static_cast<int>(idx % groups) * 8;
+    const int t0 = static_cast<int>(idx / groups) * TT;
+    float wv[8 * TAPS];  // wv[e * TAPS + tap]
+#pragma unroll
+    for (int i = 0; i < TAPS; ++i) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(w + static_cast<long long>(c0) * TAPS) + i);
+        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) wv[8 * i + e] = __bfloat162float(h[e]);
+    }
+    float hist[TAPS][8];  // hist[TAPS - 1] = current row, hist[TAPS - 1 - b] = the row b tokens back
+#pragma unroll
+    for (int b = 1; b < TAPS; ++b) {
+        const int t = t0 - b;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (t >= 0) raw = __ldg(reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx + c0));
+        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) hist[TAPS - 1 - b][e] = __bfloat162float(h[e]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+        const int t = t0 + tt;
+        if (t < T) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx + c0));
+            const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) hist[TAPS - 1][e] = __bfloat162float(h[e]);
+            const int pos = positions[t];
+            __nv_bfloat16 out[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float acc = 0.f;
+#pragma unroll
+                for (int tap = 0; tap < TAPS; ++tap)
+                    if (TAPS - 1 - tap <= pos) acc = bf16r(acc + bf16r(hist[tap][e] * wv[e * TAPS + tap]));
+                out[e] = __float2bfloat16_rn(acc / (1.f + expf(-acc)));
+            }
+            *reinterpret_cast<uint4*>(y + static_cast<long long>(t) * ldy + c0) = *reinterpret_cast<const uint4*>(out);
+#pragma unroll
+            for (int b = 0; b + 1 < TAPS; ++b)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) hist[b][e] = hist[b + 1][e];
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ delta inputs
 // One warp per (token, value head): key head = value head / (Hv / Hk) (src/archs/qwen35_text.rs:552-559).
 __global__ void __launch_bounds__(256) s1_delta_inputs_kernel(const __nv_bfloat16* __restrict__ mixed, long long ldm,
@@ -136,10 +195,18 @@ extern "C" int s1_conv_silu(s1_ctx* ctx, const void* x, long long ldx, const voi
         return s1_fail(ctx, S1_EINVAL, "s1_conv_silu: rows must be 16-byte aligned");
     if (total_tokens == 0) return S1_OK;
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
-    const long long n = static_cast<long long>(total_tokens) * (channels / 8);
-    s1_conv_silu_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
-        static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(weight), positions, total_tokens, channels, taps,
-        static_cast<__nv_bfloat16*>(y), ldy);
+    if (taps == 4 && al16(weight) && x != y) {
+        constexpr int TT = 16;
+        const long long n = static_cast<long long>((total_tokens + TT - 1) / TT) * (channels / 8);
+        s1_conv_silu_walk_kernel<4, TT><<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
+            static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(weight), positions, total_tokens, channels,
+            static_cast<__nv_bfloat16*>(y), ldy);
+    } else {
+        const long long n = static_cast<long long>(total_tokens) * (channels / 8);
+        s1_conv_silu_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
+            static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(weight), positions, total_tokens, channels, taps,
+            static_cast<__nv_bfloat16*>(y), ldy);
+    }
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return S1_OK;

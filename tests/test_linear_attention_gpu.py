@@ -28,6 +28,21 @@ def test_conv_silu_packed_matches_the_oracle(ctx):
     assert not torch.allclose(got[7], oracle.causal_conv_silu(x.unsqueeze(0), w)[0][7], atol=1e-3)  # boundary matters
 
 
+@pytest.mark.parametrize("lens,Cc,K", [([40, 3, 70], 64, 4), ([16, 16, 1, 31], 8, 4), ([33, 20], 32, 3)])
+def test_conv_silu_longer_sequences_and_other_tap_counts(ctx, lens, Cc, K):
+    """Sequences that span several of the kernel's 16-token walks, boundaries on and off the walk boundaries, and a
+    tap count served by the per-token kernel; bit-exact against the oracle's per-tap bf16 rounding up to the final SiLU."""
+    T = sum(lens)
+    g = torch.Generator().manual_seed(T + Cc)
+    x = torch.randn(T, Cc, generator=g).to(torch.bfloat16)
+    w = (torch.randn(Cc, 1, K, generator=g) * 0.4).to(torch.bfloat16)
+    b, _ = batching.pack_next(lens, batching.BatcherConfig(token_budget=1024))
+    got = qwen35.conv_silu(x.to(DEV), w.to(DEV), torch.from_numpy(b.positions).to(DEV)).float().cpu()
+    want = torch.cat([oracle.causal_conv_silu(x[a:z].unsqueeze(0), w)[0] for a, z in zip(b.cu_seqlens[:-1], b.cu_seqlens[1:])])
+    assert (got - want).abs().max() <= 2.0 ** -7 * want.abs().max()
+    assert float((got == want).float().mean()) > 0.99
+
+
 def _layer(seed, hidden=256, Hk=4, Hv=8):
     g = torch.Generator().manual_seed(seed)
     width = 2 * Hk * 128 + Hv * 128
