@@ -313,8 +313,8 @@ def run_decoder(args, rank, world, local_rank):
 def run_tp(args, rank, world, local_rank):
     """Secondary workload: the SwiGLU MLP of the 27B-shaped hybrid model (hidden 5120, intermediate 17408) on
     `--tokens` packed tokens, tensor-parallel over the ranks: gate / up column-parallel with the gating fused,
-    down row-parallel with the residual fused on rank 0, partial sums exchanged by `s1_allreduce_bf16` in `--slabs`
-    row slabs so that the exchange of a slab runs under the projection of the next. Reports whole-job TFLOP/s, the
+    down row-parallel with the residual fused on rank 0, the whole MLP in `--slabs` row slabs whose partial sums are
+    exchanged by `s1_allreduce_bf16` under the projections of the next slab. Reports whole-job TFLOP/s, the
     same step without the exchange, and the bus bandwidth of the bare all-reduce of the full [T, 5120] output."""
     from sys1_b200 import device, tensor_parallel
     torch.cuda.set_device(local_rank)
@@ -332,17 +332,10 @@ def run_tp(args, rank, world, local_rank):
     gate, up, down = mk(I // world, H), mk(I // world, H), mk(H, I // world)
     x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
     out = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
-    from sys1_b200._lib import EPI_SWIGLU
-    from sys1_b200.linear import fused_linear
-    row = tensor_parallel.RowParallelLinear(down, tp, slabs=args.slabs)
-    hbuf = torch.empty(T, I // world, device=dev, dtype=torch.bfloat16)
+    mlp = tensor_parallel.Mlp(gate, up, down, tp, slabs=args.slabs, sharded=True, comm_sms=args.comm_sms)
 
     def step(exchange=True):
-        fused_linear(x, gate, weight_up=up, epilogue=EPI_SWIGLU, out=hbuf, ctx=ctx)
-        if exchange:
-            row(hbuf, residual=x, out=out)
-        else:
-            fused_linear(hbuf, down, residual=x if rank == 0 else None, out=out, ctx=ctx)
+        mlp.forward(x, residual=x, out=out, exchange=exchange)
 
     def timed(fn, n):
         if world > 1:
@@ -379,7 +372,7 @@ def run_tp(args, rank, world, local_rank):
                           "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
                           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                           "config": {"workload": f"27B-shaped SwiGLU MLP (5120 -> 2 x 17408 -> 5120), T={T}, tensor parallel x{world}, "
-                                                 f"all-reduce in {args.slabs} row slabs", "parallelism": f"tp{world}",
+                                                 f"gate/up, down and all-reduce in {args.slabs} row slabs, {args.comm_sms} SMs left to the all-reduce", "parallelism": f"tp{world}",
                                      "l2": "activations (x, h, out) exceed the 126 MB L2"},
                           "ms_without_exchange": ms_math, "ms_allreduce_alone": ms_ar,
                           "allreduce_busbw_gbs": (2.0 * (world - 1) / world * bytes_ar / (ms_ar * 1e-3) / 1e9) if world > 1 else None,
@@ -402,6 +395,7 @@ def main():
                     help="projections (default, the headline microbench); encoder: ModernBERT-large forward, tokens/s; "
                          "tp: SwiGLU MLP of the 27B-shaped hybrid model, tensor-parallel over the ranks")
     ap.add_argument("--slabs", type=int, default=4, help="tp workload: row slabs the all-reduce is pipelined in")
+    ap.add_argument("--comm-sms", type=int, default=16, help="tp workload: SMs the projections leave to the all-reduce of the previous slab")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step from a CUDA graph (for small token budgets, where launching from Python is the bottleneck)")
     args = ap.parse_args()

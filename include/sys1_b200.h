@@ -62,7 +62,9 @@ int s1_device_count(int* out);
 /* Number of kernels this context has launched so far. */
 long long s1_launch_count(const s1_ctx* ctx);
 /* Tuning knobs: "gemm_bn" = 0 (auto), 512 / 384 (CTA-pair 256x256 / 256x192 tiles), 256 or 128 (single-CTA 128xBN tiles);
- * "debug" = measurement aids of the GEMM epilogue (0 in production). */
+ * "gemm_sms" = how many SMs the projections' persistent grids may occupy (0 = all; e.g. 132 leaves 16 SMs to the
+ * all-reduce of the previous slab in a tensor-parallel layer); "debug" = measurement aids of the GEMM epilogue
+ * (0 in production). */
 int s1_set_option(s1_ctx* ctx, const char* name, long long value);
 
 /*

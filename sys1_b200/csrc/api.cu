@@ -77,6 +77,12 @@ extern "C" int s1_set_option(s1_ctx* ctx, const char* name, long long value) {
         ctx->opt_gemm_bn = static_cast<int>(value);
         return S1_OK;
     }
+    if (strcmp(name, "gemm_sms") == 0) {  // SMs the projections may occupy (0 = all): leaves room for a concurrent collective
+        if (value < 0 || (value != 0 && value < 2))
+            return s1_fail(ctx, S1_EINVAL, "gemm_sms must be 0 (all) or at least 2 (got %lld)", value);
+        ctx->opt_gemm_sms = static_cast<int>(value);
+        return S1_OK;
+    }
     if (strcmp(name, "debug") == 0) {
         ctx->opt_debug = static_cast<int>(value);
         return S1_OK;
@@ -141,7 +147,8 @@ static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0,
         configured_device = ctx->device;
     }
     const int tiles = p.tiles_m * p.tiles_n;
-    const int units = ctx->sm_count / CTAS;  // CTAs, or CTA pairs
+    const int sms = (ctx->opt_gemm_sms > 0 && ctx->opt_gemm_sms < ctx->sm_count) ? ctx->opt_gemm_sms : ctx->sm_count;
+    const int units = sms / CTAS;  // CTAs, or CTA pairs
     const int grid = (tiles < units ? tiles : units) * CTAS;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);

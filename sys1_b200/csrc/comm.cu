@@ -93,7 +93,9 @@ extern "C" int s1_comm_init(s1_ctx* ctx, const void* id, int rank, int size) {
     ncclComm_t comm = nullptr;
     const ncclResult_t rc = api->CommInitRank(&comm, size, uid, rank);
     if (rc != ncclSuccess) return s1_fail(ctx, S1_ECUDA, "ncclCommInitRank failed: %s", api->GetErrorString(rc));
-    cudaError_t e = cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking);
+    int prio_low = 0, prio_high = 0;  // the collective's blocks go first when SMs free up
+    cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high);
+    cudaError_t e = cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, prio_high);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_ready, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming);
     if (e != cudaSuccess) {

@@ -101,6 +101,11 @@ class Context:
 _contexts: Dict[Tuple[int, int], Context] = {}
 
 
+def sm_count(ctx: "Context") -> int:
+    """Streaming multiprocessors of the context's GPU."""
+    return torch.cuda.get_device_properties(ctx.ordinal).multi_processor_count
+
+
 def comm_unique_id() -> bytes:
     """The id rank 0 creates and hands to every rank's `Context.comm_init` (over any channel)."""
     lib = _lib.load_library()

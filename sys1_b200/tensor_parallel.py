@@ -52,8 +52,10 @@ class RowParallelLinear:
     """`y = x W^T (+ residual)` with K split over the ranks: every rank multiplies its K range, the partials are
     summed in place over NVLink. `slabs` = number of row slabs the exchange is pipelined in."""
 
-    def __init__(self, weight_shard: torch.Tensor, tp: TensorParallel, slabs: int = 4):
-        self.weight, self.tp, self.slabs = weight_shard, tp, max(1, int(slabs))
+    def __init__(self, weight_shard: torch.Tensor, tp: TensorParallel, slabs: int = 4, comm_sms: int = 16):
+        """`comm_sms`: SMs left free by the projections of all but the first slab, so that the all-reduce of the
+        previous slab can run beside them (a persistent grid over every SM would hold it back until it ends)."""
+        self.weight, self.tp, self.slabs, self.comm_sms = weight_shard, tp, max(1, int(slabs)), int(comm_sms)
 
     def forward(self, x_shard: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         T, N = x_shard.shape[0], self.weight.shape[0]
@@ -64,13 +66,21 @@ class RowParallelLinear:
         res = residual if self.tp.rank == 0 else None
         step = -(-T // self.slabs)
         step = max(128, -(-step // 128) * 128)  # whole 128-row tiles per slab
-        for a in range(0, T, step):
-            b = min(T, a + step)
-            fused_linear(x_shard[a:b], self.weight, residual=None if res is None else res[a:b], out=out[a:b], ctx=self.tp.ctx)
-            if self.tp.size > 1:
-                self.tp.ctx.all_reduce_(out[a:b], wait=False)
+        ctx = self.tp.ctx
+        share = self.tp.size > 1 and self.comm_sms > 0 and T > step
+        try:
+            for a in range(0, T, step):
+                b = min(T, a + step)
+                if share and a > 0:
+                    ctx.set_option("gemm_sms", max(2, device.sm_count(ctx) - self.comm_sms))
+                fused_linear(x_shard[a:b], self.weight, residual=None if res is None else res[a:b], out=out[a:b], ctx=ctx)
+                if self.tp.size > 1:
+                    ctx.all_reduce_(out[a:b], wait=False)
+        finally:
+            if share:
+                ctx.set_option("gemm_sms", 0)
         if self.tp.size > 1:
-            self.tp.ctx.all_reduce_wait()
+            ctx.all_reduce_wait()
         return out
 
     __call__ = forward
@@ -78,15 +88,46 @@ class RowParallelLinear:
 
 class Mlp:
     """The SwiGLU MLP (`Mlp::forward`, src/archs/qwen35_text.rs:232-240) under tensor parallelism: gate / up split by
-    output columns (each rank keeps matching gate and up columns), down split along K, one all-reduce."""
+    output columns (each rank keeps matching gate and up columns), down split along K, one sum over ranks. The whole
+    MLP runs slab by slab of token rows - gate/up, down, all-reduce of that slab's partial output - so that the exchange
+    of a slab travels under both projections of the next one; only the last slab's exchange is exposed."""
 
-    def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, tp: TensorParallel, slabs: int = 4):
-        self.tp = tp
-        self.gate, self.up = tp.column_shard(gate), tp.column_shard(up)
-        self.down = RowParallelLinear(tp.row_shard(down), tp, slabs)
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, tp: TensorParallel, slabs: int = 4, sharded: bool = False,
+                 comm_sms: int = 16):
+        """`gate`, `up` `[I, H]`, `down` `[H, I]`: the full matrices (this rank's views are taken here), or with
+        `sharded=True` this rank's shards (`[I / R, H]`, `[I / R, H]`, `[H, I / R]`). `comm_sms`: SMs the projections of
+        all slabs but the first leave free, so that the all-reduce of the previous slab runs beside them (a persistent
+        grid over every SM would hold the collective's blocks back until it ends)."""
+        self.tp, self.slabs, self.comm_sms = tp, max(1, int(slabs)), int(comm_sms)
+        self.gate, self.up = (gate, up) if sharded else (tp.column_shard(gate), tp.column_shard(up))
+        self.down = down if sharded else tp.row_shard(down)
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        h = fused_linear(x, self.gate, weight_up=self.up, epilogue=EPI_SWIGLU, ctx=self.tp.ctx)
-        return self.down(h, residual=residual, out=out)
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                exchange: bool = True) -> torch.Tensor:
+        T, N = x.shape[0], self.down.shape[0]
+        ctx = self.tp.ctx
+        if out is None:
+            out = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+        if not out.is_contiguous():
+            raise ValueError("the summed output must be contiguous")
+        res = residual if self.tp.rank == 0 else None
+        step = max(128, -(-(-(-T // self.slabs)) // 128) * 128)  # whole 128-row tiles per slab
+        h = torch.empty((min(step, T), self.gate.shape[0]), dtype=torch.bfloat16, device=x.device)
+        share = exchange and self.tp.size > 1 and self.comm_sms > 0 and T > step
+        try:
+            for a in range(0, T, step):
+                b = min(T, a + step)
+                if share and a > 0:
+                    ctx.set_option("gemm_sms", max(2, device.sm_count(ctx) - self.comm_sms))
+                fused_linear(x[a:b], self.gate, weight_up=self.up, epilogue=EPI_SWIGLU, out=h[: b - a], ctx=ctx)
+                fused_linear(h[: b - a], self.down, residual=None if res is None else res[a:b], out=out[a:b], ctx=ctx)
+                if exchange and self.tp.size > 1:
+                    ctx.all_reduce_(out[a:b], wait=False)
+        finally:
+            if share:
+                ctx.set_option("gemm_sms", 0)
+        if exchange and self.tp.size > 1:
+            ctx.all_reduce_wait()
+        return out
 
     __call__ = forward
