@@ -55,7 +55,6 @@ struct AttnParams {
     long long ldo;
     int window;       // < 0: none
     float scale_log2; // scale * log2(e)
-    int debug;
     int* status;
 };
 
@@ -86,18 +85,6 @@ __device__ __forceinline__ void pair_barrier(int q4) {
     else if (q4 == 1) named_barrier<2, 64>();
     else if (q4 == 2) named_barrier<3, 64>();
     else named_barrier<4, 64>();
-}
-__device__ __forceinline__ void pair_barrier8(int id) {  // ids 1..8: (query block, row quarter)
-    switch (id) {
-        case 0: named_barrier<1, 64>(); break;
-        case 1: named_barrier<2, 64>(); break;
-        case 2: named_barrier<3, 64>(); break;
-        case 3: named_barrier<4, 64>(); break;
-        case 4: named_barrier<5, 64>(); break;
-        case 5: named_barrier<6, 64>(); break;
-        case 6: named_barrier<7, 64>(); break;
-        default: named_barrier<8, 64>(); break;
-    }
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float r;
@@ -177,7 +164,6 @@ s1_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             auto mma_s = [&](int i) {
                 constexpr uint32_t idesc = make_idesc(1, 128, 128);
                 const uint32_t kt = sk + (i & 1) * kTile;
-                if (!(p.debug & 8))
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     umma_bf16(tmem, make_sw128_kmajor_desc(sq) + 2u * kk, make_sw128_kmajor_desc(kt) + 2u * kk, idesc, kk ? 1u : 0u);
@@ -216,17 +202,10 @@ s1_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 {
                     constexpr uint32_t idesc = make_idesc(1, 128, 64) | (1u << 16);  // B (= V) is MN-major
                     const uint32_t vt = sv + (i & 1) * kTile;
-                    if (!(p.debug & 16))
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)  // 16 keys per instruction
                         umma_bf16(tmem + 128, make_sw128_kmajor_desc(sp + (kk >> 2) * kTile) + 2u * (kk & 3), mn_desc(vt) + 128u * kk,
                                   idesc, (kk || i) ? 1u : 0u);
-                    if (p.debug & 32) {  // K-major B of the same size (wrong result: timing only)
-#pragma unroll
-                        for (int kk = 0; kk < 8; ++kk)
-                            umma_bf16(tmem + 128, make_sw128_kmajor_desc(sp + (kk >> 2) * kTile) + 2u * (kk & 3),
-                                      make_sw128_kmajor_desc(vt) + 2u * (kk & 3), make_idesc(1, 128, 64), (kk || i) ? 1u : 0u);
-                    }
                     umma_commit(bar_o);
                 }
             }
@@ -379,285 +358,6 @@ s1_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
 }
 
-// ---------------------------------------------------------------------------------------------------------------
-// Global attention (no band): two 128-query blocks of one sequence per CTA, sharing every K / V tile.
-// With one query block per CTA the kernel above is bound by the L2 -> shared-memory traffic of K and V (each block
-// streams all keys of its sequence: 128 flop per byte); sharing a tile between two blocks halves that traffic.
-// One CTA per SM, 17 warps: warp 16 loads and issues the MMAs of both blocks; warps 0..7 are the softmax warps of the
-// first block, 8..15 of the second, each group working exactly as in the kernel above (two threads per query row).
-// TMEM (512 columns): block b uses columns 256 b + [0, 128) for S, + [128, 192) for O, + [192, 198) for the exchange.
-constexpr int kPairSmem = 2 * kTile /*Q x 2*/ + 2 * kTile /*K ring*/ + 2 * kTile /*V ring*/ + 4 * kTile /*P: 2 blocks x 2 tiles*/ + 128;
-
-__global__ void __launch_bounds__(544, 1)
-s1_attention_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    const uint32_t base = smem_u32(smem_raw);
-    if (base & 1023u) {
-        if (threadIdx.x == 0 && atomicCAS(p.status, 0, 5) == 0) p.status[1] = blockIdx.x, p.status[2] = 49, p.status[3] = base & 1023u;
-        return;
-    }
-    const uint32_t sq = base, sk = base + 2 * kTile, sv = base + 4 * kTile, sp = base + 6 * kTile;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + 10 * kTile);
-    // bars: 0 Q full; 1,2 K full; 3,4 V full; then per block b (5 + 4 b ...): S ready, S read (8 warps), P ready (8 warps), PV done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const uint32_t b0 = smem_u32(bars);
-    const uint32_t bar_q = b0, full_k = b0 + 8, full_v = b0 + 24;
-    auto bar_s = [&](int b) { return b0 + 40u + 32u * b; };
-    auto bar_sfree = [&](int b) { return b0 + 48u + 32u * b; };
-    auto bar_p = [&](int b) { return b0 + 56u + 32u * b; };
-    auto bar_o = [&](int b) { return b0 + 64u + 32u * b; };
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const QBlock qb = p.blocks[blockIdx.x];     // qb.qb = first of the two query blocks, qb.pad = number of blocks (1 or 2)
-    const int head = blockIdx.y;
-    const int nblk = qb.pad;
-    const int q_first = qb.qb * kQB;
-    const int nkb = (qb.seq_len - 1) / kQB + 1; // every key of the sequence
-
-    if (threadIdx.x == 0) {
-        mbar_init(bar_q, 1);
-        mbar_init(full_k, 1);
-        mbar_init(full_k + 8, 1);
-        mbar_init(full_v, 1);
-        mbar_init(full_v + 8, 1);
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(bar_s(b), 1);
-            mbar_init(bar_sfree(b), 8);
-            mbar_init(bar_p(b), 8);
-            mbar_init(bar_o(b), 1);
-        }
-        *abort_flag = 0;
-        fence_mbar_init();
-        tma_prefetch_desc(&tmQ);
-        tma_prefetch_desc(&tmK);
-        tma_prefetch_desc(&tmV);
-    }
-    if (warp == 16) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-    int fail = 0;
-
-    if (warp == 16) {
-        if (lane == 0) {
-            const int x = head * kHD;
-            auto load_k = [&](int i) {
-                const uint32_t fb = full_k + 8u * (i & 1);
-                mbar_arrive_expect_tx(fb, kTile);
-                tma_load_2d(sk + (i & 1) * kTile, &tmK, x, qb.seq_start + i * kQB, fb);
-            };
-            auto load_v = [&](int i) {
-                const uint32_t fb = full_v + 8u * (i & 1);
-                mbar_arrive_expect_tx(fb, kTile);
-                tma_load_2d(sv + (i & 1) * kTile, &tmV, x, qb.seq_start + i * kQB, fb);
-            };
-            auto mma_s = [&](int b, int i) {
-                constexpr uint32_t idesc = make_idesc(1, 128, 128);
-                const uint32_t kt = sk + (i & 1) * kTile;
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk)
-                    umma_bf16(tmem + 256 * b, make_sw128_kmajor_desc(sq + b * kTile) + 2u * kk, make_sw128_kmajor_desc(kt) + 2u * kk, idesc,
-                              kk ? 1u : 0u);
-                umma_commit(bar_s(b));
-            };
-            mbar_arrive_expect_tx(bar_q, nblk * kTile);
-            for (int b = 0; b < nblk; ++b) tma_load_2d(sq + b * kTile, &tmQ, x, qb.seq_start + q_first + b * kQB, bar_q);
-            load_k(0);
-            load_v(0);
-            if (nkb > 1) {
-                load_k(1);
-                load_v(1);
-            }
-            if (!mbar_wait(bar_q, 0, abort_flag)) fail = 1;
-            if (!fail && !mbar_wait(full_k, 0, abort_flag)) fail = 2;
-            if (!fail) {
-                tc_fence_after();
-                for (int b = 0; b < nblk; ++b) mma_s(b, 0);
-            }
-            for (int i = 0; i < nkb && !fail; ++i) {
-                if (i + 1 < nkb) {
-                    if (!mbar_wait(full_k + 8u * ((i + 1) & 1), ((i + 1) >> 1) & 1, abort_flag)) { fail = 3; break; }
-                    for (int b = 0; b < nblk && !fail; ++b) {
-                        if (!mbar_wait(bar_sfree(b), i & 1, abort_flag)) { fail = 4; break; }
-                        tc_fence_after();
-                        mma_s(b, i + 1);
-                    }
-                    if (fail) break;
-                    if (i + 2 < nkb) load_k(i + 2);  // its stage held K of tile i, whose S both blocks' warps have read
-                }
-                for (int b = 0; b < nblk && !fail; ++b) {
-                    if (!mbar_wait(bar_p(b), i & 1, abort_flag)) { fail = 5; break; }
-                    if (b == 0) {
-                        if (i >= 1 && i + 1 < nkb) {  // the other V stage held tile i-1: free once both blocks' PV have completed
-                            for (int bb = 0; bb < nblk && !fail; ++bb)
-                                if (!mbar_wait(bar_o(bb), (i - 1) & 1, abort_flag)) fail = 6;
-                            if (fail) break;
-                            load_v(i + 1);
-                        }
-                        if (!mbar_wait(full_v + 8u * (i & 1), (i >> 1) & 1, abort_flag)) { fail = 7; break; }
-                    }
-                    tc_fence_after();
-                    constexpr uint32_t idesc = make_idesc(1, 128, 64) | (1u << 16);  // B (= V) is MN-major
-                    const uint32_t vt = sv + (i & 1) * kTile, pt = sp + b * 2 * kTile;
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)
-                        umma_bf16(tmem + 256 * b + 128, make_sw128_kmajor_desc(pt + (kk >> 2) * kTile) + 2u * (kk & 3), mn_desc(vt) + 128u * kk,
-                                  idesc, (kk || i) ? 1u : 0u);
-                    umma_commit(bar_o(b));
-                }
-            }
-        }
-        __syncwarp();
-    } else if ((warp >> 3) < nblk) {
-        const int blk = warp >> 3, q4 = warp & 3, ch = (warp >> 2) & 1;
-        const int row = q4 * 32 + lane;
-        const int q_lo = q_first + blk * kQB;
-        const bool q_ok = q_lo + row < qb.seq_len;
-        const int qi = min(q_lo + row, qb.seq_len - 1);
-        const uint32_t lane_addr = tmem + 256 * blk + (static_cast<uint32_t>(q4 * 32) << 16);
-        const float c = p.scale_log2;
-        const uint32_t prow = sp + (blk * 2 + ch) * kTile + static_cast<uint32_t>(row) * 128u, r7 = static_cast<uint32_t>(row) & 7u;
-        const uint32_t my_s = bar_s(blk), my_sfree = bar_sfree(blk), my_p = bar_p(blk), my_o = bar_o(blk);
-        float m_used = -INFINITY, l = 0.f;
-
-        for (int i = 0; i < nkb; ++i) {
-            const int j0 = i * kQB + ch * 64;
-            bool ok = mbar_wait(my_s, i & 1, abort_flag);
-            if (!__all_sync(0xffffffffu, ok)) { fail = 8; break; }
-            tc_fence_after();
-            uint32_t s[64];
-            tmem_ld_32x32b_x32(lane_addr + ch * 64, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_ld_32x32b_x32(lane_addr + ch * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(my_sfree);
-            if ((i + 1) * kQB > qb.seq_len) {  // the last tile reaches past the sequence
-                const int visible = qb.seq_len - j0;  // keys 0 .. visible-1 of this half tile exist
-#pragma unroll
-                for (int e = 0; e < 64; ++e)
-                    if (e >= visible) s[e] = 0xff800000u;  // -inf
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-            for (int e = 0; e < 64; e += 8) {
-                mx0 = fmax3(mx0, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
-                mx1 = fmax3(mx1, __uint_as_float(s[e + 2]), __uint_as_float(s[e + 3]));
-                mx2 = fmax3(mx2, __uint_as_float(s[e + 4]), __uint_as_float(s[e + 5]));
-                mx3 = fmax3(mx3, __uint_as_float(s[e + 6]), __uint_as_float(s[e + 7]));
-            }
-            const float mx_own = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            const uint32_t xcol = lane_addr + 192 + 2 * (i & 1);
-            tmem_st_32x32b_x1(xcol + ch, __float_as_uint(mx_own));
-            tmem_st_wait();
-            tc_fence_before();
-            pair_barrier8(blk * 4 + q4);
-            tc_fence_after();
-            const float mx_other = __uint_as_float(tmem_ld_32x32b_x1(xcol + (ch ^ 1)));
-            tmem_ld_wait();
-            const float m_new = fmaxf(m_used, fmaxf(mx_own, mx_other));
-            float alpha = 1.f;
-            bool rescale = false;
-            if (i == 0) {
-                m_used = m_new;
-            } else {
-                rescale = __any_sync(0xffffffffu, (m_new - m_used) * c > kRescaleLog2);
-                if (rescale && m_new != -INFINITY) {
-                    alpha = ex2((m_used - m_new) * c);
-                    m_used = m_new;
-                }
-            }
-            const float neg_mc = (m_used == -INFINITY) ? 0.f : -m_used * c;
-            uint32_t pk[32];
-            float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-            for (int e = 0; e < 64; e += 2) {
-                const float p0 = ex2(fmaf(__uint_as_float(s[e]), c, neg_mc));
-                const float p1 = ex2(fmaf(__uint_as_float(s[e + 1]), c, neg_mc));
-                sum0 += p0;
-                sum1 += p1;
-                pk[e >> 1] = pack_bf16x2_attn(p0, p1);
-            }
-            l = fmaf(l, alpha, sum0 + sum1);
-            if (i >= 1) {
-                ok = mbar_wait(my_o, (i - 1) & 1, abort_flag);
-                if (!__all_sync(0xffffffffu, ok)) { fail = 9; break; }
-                tc_fence_after();
-                if (rescale) {
-                    uint32_t o[32];
-                    tmem_ld_32x32b_x32(lane_addr + 128 + ch * 32, o);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-                    tmem_st_32x32b_x32(lane_addr + 128 + ch * 32, o);
-                    tmem_st_wait();
-                }
-            }
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const uint32_t addr = prow + ((static_cast<uint32_t>(t) ^ r7) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * t]), "r"(pk[4 * t + 1]),
-                             "r"(pk[4 * t + 2]), "r"(pk[4 * t + 3]) : "memory");
-            }
-            fence_proxy_async_smem();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(my_p);
-        }
-        if (!fail) {
-            const bool ok = mbar_wait(my_o, (nkb - 1) & 1, abort_flag);
-            if (!__all_sync(0xffffffffu, ok)) fail = 10;
-        }
-        if (!fail) {
-            tc_fence_after();
-            tmem_st_32x32b_x1(lane_addr + 196 + ch, __float_as_uint(l));
-            tmem_st_wait();
-            tc_fence_before();
-            pair_barrier8(blk * 4 + q4);
-            tc_fence_after();
-            const float l0 = ch == 0 ? l : __uint_as_float(tmem_ld_32x32b_x1(lane_addr + 196));
-            const float l1 = ch == 1 ? l : __uint_as_float(tmem_ld_32x32b_x1(lane_addr + 197));
-            tmem_ld_wait();
-            const float inv = 1.f / (l0 + l1);
-            __nv_bfloat16* orow = p.out + static_cast<long long>(qb.seq_start + qi) * p.ldo + head * kHD + ch * 32;
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(lane_addr + 128 + ch * 32, o);
-            tmem_ld_wait();
-            if (q_ok) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    uint4 v;
-                    v.x = pack_bf16x2_attn(__uint_as_float(o[8 * e]) * inv, __uint_as_float(o[8 * e + 1]) * inv);
-                    v.y = pack_bf16x2_attn(__uint_as_float(o[8 * e + 2]) * inv, __uint_as_float(o[8 * e + 3]) * inv);
-                    v.z = pack_bf16x2_attn(__uint_as_float(o[8 * e + 4]) * inv, __uint_as_float(o[8 * e + 5]) * inv);
-                    v.w = pack_bf16x2_attn(__uint_as_float(o[8 * e + 6]) * inv, __uint_as_float(o[8 * e + 7]) * inv);
-                    *reinterpret_cast<uint4*>(orow + 8 * e) = v;
-                }
-            }
-            tc_fence_before();
-        }
-        __syncwarp();
-    }
-    if (fail && atomicCAS(p.status, 0, 4) == 0) {
-        p.status[1] = blockIdx.x;
-        p.status[2] = 40 + fail;
-        p.status[3] = blockIdx.y;
-    }
-    if (*abort_flag) __nanosleep(200000);
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 16) {
-        tc_fence_after();
-        tmem_dealloc(tmem, 512);
-    }
-}
-
 }  // namespace
 
 extern "C" size_t s1_attention_workspace(int num_seqs, int total_tokens) {
@@ -689,15 +389,10 @@ extern "C" int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const voi
     ctx->host_scratch.resize(sizeof(QBlock) * max_blocks);
     QBlock* blocks = reinterpret_cast<QBlock*>(ctx->host_scratch.data());
     int nb = 0;
-    const bool pairs = window < 0 && !(ctx->opt_debug & 0x80);  // global attention: two query blocks of a sequence per CTA share the K / V tiles
     for (int s = 0; s < num_seqs; ++s) {
         const int a = cu_seqlens_host[s], len = cu_seqlens_host[s + 1] - a;
         if (len < 0) return s1_fail(ctx, S1_EINVAL, "s1_attention: cu_seqlens must not decrease");
-        if (pairs) {
-            for (int b = 0; b * kQB < len; b += 2) blocks[nb++] = QBlock{a, len, b, (b + 1) * kQB < len ? 2 : 1};
-        } else {
-            for (int b = 0; b * kQB < len; ++b) blocks[nb++] = QBlock{a, len, b, 0};
-        }
+        for (int b = 0; b * kQB < len; ++b) blocks[nb++] = QBlock{a, len, b, 0};
     }
     if (nb == 0) return S1_OK;
     // without a window the work of a block grows with its sequence: longest sequences first
@@ -718,15 +413,12 @@ extern "C" int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const voi
     ap.window = window;
     ap.scale_log2 = scale * 1.4426950408889634f;
     ap.status = ctx->status_dev;
-    ap.debug = ctx->opt_debug >> 8;
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
         S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_attention_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
         configured_device = ctx->device;
     }
-    if (pairs) s1_attention_pair_kernel<<<dim3(nb, heads), 544, kPairSmem, ctx->stream>>>(tq, tk, tv, ap);
-    else s1_attention_kernel<<<dim3(nb, heads), 288, kAttnSmem, ctx->stream>>>(tq, tk, tv, ap);
+    s1_attention_kernel<<<dim3(nb, heads), 288, kAttnSmem, ctx->stream>>>(tq, tk, tv, ap);
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return S1_OK;
