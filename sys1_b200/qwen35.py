@@ -150,18 +150,39 @@ class LinearAttention:
     Key and value head dim 128. `forward(x, batch)` takes `x [T, hidden]` bf16 and the `PackedBatch` that produced it."""
 
     def __init__(self, qkv: Linear, z: Linear, b: Linear, a: Linear, conv: torch.Tensor, decay: torch.Tensor,
-                 dt_bias: torch.Tensor, norm: torch.Tensor, output: Linear, key_heads: int, value_heads: int, eps: float):
+                 dt_bias: torch.Tensor, norm: torch.Tensor, output: Linear, key_heads: int, value_heads: int, eps: float,
+                 merge_inputs: bool = True):
+        """`merge_inputs`: stack the four input projections, which share their input, into one weight `[N_qkv + N_z + 2 Hv,
+        K]` at load time, so that they run as one contraction (two of them are only `Hv` = 16 or 48 columns wide, a
+        launch each for next to no work); the outputs are column views of one buffer."""
         self.qkv, self.z, self.b, self.a, self.output = qkv, z, b, a, output
         self.conv, self.decay, self.dt_bias, self.norm = conv, decay.float().contiguous(), dt_bias.float().contiguous(), norm
         self.key_heads, self.value_heads, self.eps = key_heads, value_heads, eps
+        self.merged = None
+        if merge_inputs and all(l.bias is None for l in (qkv, z, b, a)):
+            parts = [qkv.weight, z.weight, b.weight, a.weight]
+            if all(w.shape[0] % 8 == 0 for w in parts):
+                self.merged = Linear(torch.cat(parts, dim=0).contiguous())
+                self._splits = [w.shape[0] for w in parts]
+
+    def _inputs(self, x: torch.Tensor):
+        """mixed-pre-conv, z, b, a: the four input projections of `x` (`project_and_mix` up to the conv, :515-526, :567-568)."""
+        if self.merged is None:
+            return self.qkv.forward(x), self.z.forward(x), self.b.forward(x), self.a.forward(x)
+        y = self.merged.forward(x)
+        outs, at = [], 0
+        for n in self._splits:
+            outs.append(y[:, at:at + n])
+            at += n
+        return tuple(outs)
 
     def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         import numpy as np
         ctx = device.load(x.device.index)
         T = x.shape[0]
         cu = np.ascontiguousarray(cu_seqlens_host, dtype=np.int32)
-        mixed = conv_silu(self.qkv.forward(x), self.conv, positions, ctx)         # project_and_mix (:515-526)
-        zz, bb, aa = self.z.forward(x), self.b.forward(x), self.a.forward(x)
+        pre, zz, bb, aa = self._inputs(x)
+        mixed = conv_silu(pre, self.conv, positions, ctx)                         # project_and_mix (:515-526)
         y = torch.empty((T, self.value_heads * 128), dtype=torch.bfloat16, device=x.device)
         need = int(ctx._lib.s1_gated_delta_rule_workspace(len(cu) - 1, T, self.value_heads))
         ws = _workspace(x.device, need)
