@@ -120,6 +120,44 @@ __device__ __forceinline__ float gelu_erf_ref(float v) {
     const float half_erfc = 0.5f * t * ex2_approx(1.4426950408889634f * u);  // Phi(-|v|)
     return v * (v >= 0.f ? 1.f - half_erfc : half_erfc);
 }
+// Packed pairs of f32 on the FMA pipe (one instruction for two lanes of work).
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void fmul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// gelu_erf_ref for two values at once: the same erfc fit, its polynomial and products as packed instructions, the
+// factor log2(e) folded into the coefficients so that the exponent is one fma away from ex2.
+__device__ __forceinline__ void gelu_erf_pair(float v0, float v1, float& g0, float& g1) {
+    constexpr float L2E = 1.4426950408889634f;
+    const float z0 = fabsf(v0) * 0.70710678118654752f, z1 = fabsf(v1) * 0.70710678118654752f;
+    const float s0 = fabsf(v0) * (-0.70710678118654752f * L2E), s1 = fabsf(v1) * (-0.70710678118654752f * L2E);
+    float d0, d1;
+    ffma2(d0, d1, z0, z1, 0.5f, 0.5f, 1.f, 1.f);
+    const float t0 = rcp_approx(d0), t1 = rcp_approx(d1);
+    float u0, u1;
+    ffma2(u0, u1, t0, t1, 0.17087277f * L2E, 0.17087277f * L2E, -0.82215223f * L2E, -0.82215223f * L2E);
+    ffma2(u0, u1, t0, t1, u0, u1, 1.48851587f * L2E, 1.48851587f * L2E);
+    ffma2(u0, u1, t0, t1, u0, u1, -1.13520398f * L2E, -1.13520398f * L2E);
+    ffma2(u0, u1, t0, t1, u0, u1, 0.27886807f * L2E, 0.27886807f * L2E);
+    ffma2(u0, u1, t0, t1, u0, u1, -0.18628806f * L2E, -0.18628806f * L2E);
+    ffma2(u0, u1, t0, t1, u0, u1, 0.09678418f * L2E, 0.09678418f * L2E);
+    ffma2(u0, u1, t0, t1, u0, u1, 0.37409196f * L2E, 0.37409196f * L2E);
+    ffma2(u0, u1, t0, t1, u0, u1, 1.00002368f * L2E, 1.00002368f * L2E);
+    ffma2(u0, u1, t0, t1, u0, u1, -1.26551223f * L2E, -1.26551223f * L2E);
+    ffma2(u0, u1, s0, s1, z0, z1, u0, u1);  // log2(e) * (poly - z^2)
+    const float e0 = ex2_approx(u0), e1 = ex2_approx(u1);
+    float h0, h1, w0, w1;
+    fmul2(h0, h1, t0, t1, e0, e1);                      // 2 Phi(-|v|)
+    fmul2(w0, w1, h0, h1, 0.5f * v0, 0.5f * v1);        // v Phi(-|v|)
+    g0 = v0 >= 0.f ? v0 - w0 : w0;
+    g1 = v1 >= 0.f ? v1 - w1 : w1;
+}
 __device__ __forceinline__ float silu_ref(float v) { return v * rcp_approx(1.f + ex2_approx(-1.4426950408889634f * v)); }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -232,7 +270,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                 const float a0 = __low2float(a2), a1 = __high2float(a2);
                 __nv_bfloat162 act2;
                 if (p.debug & 8) act2 = a2;  // measurement aid: no activation
-                else if constexpr (EPI == EPI_GEGLU) act2 = __floats2bfloat162_rn(gelu_erf_ref(a0), gelu_erf_ref(a1));
+                else if constexpr (EPI == EPI_GEGLU) {
+                    float g0, g1;
+                    gelu_erf_pair(a0, a1, g0, g1);
+                    act2 = __floats2bfloat162_rn(g0, g1);
+                }
                 else act2 = __floats2bfloat162_rn(silu_ref(a0), silu_ref(a1));
                 __nv_bfloat162 o2 = __hmul2(act2, g2);
                 out[j] = *reinterpret_cast<uint32_t*>(&o2);
