@@ -83,6 +83,10 @@ extern "C" int s1_set_option(s1_ctx* ctx, const char* name, long long value) {
         ctx->opt_gemm_sms = static_cast<int>(value);
         return S1_OK;
     }
+    if (strcmp(name, "pdl") == 0) {  // programmatic dependent launch of the projections (default on)
+        ctx->opt_pdl = value != 0;
+        return S1_OK;
+    }
     if (strcmp(name, "debug") == 0) {
         ctx->opt_debug = static_cast<int>(value);
         return S1_OK;
@@ -155,13 +159,16 @@ static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0,
     cfg.blockDim = dim3(gemm_threads<BN, EPI>(), 1, 1);
     cfg.dynamicSmemBytes = Cfg::smem_bytes(StoreCfg<BN, EPI, CTAS>::kStagingBytes);
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: the set-up of this kernel overlaps the tail of the previous one in the stream
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = ctx->opt_pdl ? 1 : 0;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     S1_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, kern, a, b0, b1, ty, p));
     ctx->launches += 1;
     return S1_OK;

@@ -383,6 +383,10 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers exist before anything remote touches them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up done (barriers, TMEM, descriptor prefetch): it may have overlapped the tail of the previous kernel in the
+    // stream; from here on this kernel touches memory that kernel may still be writing
+    griddep_launch_dependents();
+    griddep_wait();
 
     int fail_role = 0, fail_tile = -1;
 

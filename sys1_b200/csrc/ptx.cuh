@@ -244,6 +244,12 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
           "r"(taddr)
         : "memory");
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may become
+// resident while its predecessor in the stream is still draining; `griddep_wait` blocks until that predecessor has
+// completed and its writes are visible (a no-op without the attribute), `griddep_launch_dependents` lets the
+// successor's blocks be scheduled from here on.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // One 32-bit column of this thread's lane.
 __device__ __forceinline__ uint32_t tmem_ld_32x32b_x1(uint32_t taddr) {
     uint32_t r;
