@@ -191,10 +191,35 @@ def run_encoder(args, rank, world, local_rank):
         torch.distributed.barrier()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
+    launches = ctx.launch_count() - l0
     if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = float(t[0])
+    # end to end through the public call: token ids and positions from pinned host memory every step, final hidden states
+    # back to pinned host memory every step (copies on side streams, overlapped with the previous / next step)
+    from sys1_b200 import pipeline
+    host_ids = ids.to(torch.int32).cpu().pin_memory()
+    host_pos = pos.to(torch.int32).cpu().pin_memory()
+    host_out = torch.empty(T, cfg.hidden_size, dtype=torch.bfloat16).pin_memory()
+    pipe = pipeline.HostPipeline(dev, [(T,), (T,)], torch.int32, depth=2)
+    fwd = lambda bufs: enc.forward(bufs[0], batch.cu_seqlens, bufs[1])
+    for _ in range(2):
+        pipe.submit([host_ids, host_pos], host_out, fwd)
+    pipe.drain()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    import time as _time
+    t0 = _time.perf_counter()
+    for _ in range(steps):
+        pipe.submit([host_ids, host_pos], host_out, fwd)
+    pipe.drain()
+    ms_e2e = (_time.perf_counter() - t0) * 1e3 / steps
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_e2e = float(t[0])
     H, D = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads
     qkv = mk(3, T, H * D)
     attn_stats = {}
@@ -225,7 +250,9 @@ def run_encoder(args, rank, world, local_rank):
                                                  "every stage through the C ABI (projections, attention, norms, RoPE, embedding lookup)",
                                      "sequences": int(len(lens)), "parallelism": f"replicas x{world}"},
                           "projection_tflops": world * T * flops_tok / (ms * 1e-3) / 1e12, "attention": attn_stats,
-                          "gpu_launches": ctx.launch_count() - l0}))
+                          "e2e": {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                                  "h2d_bytes_per_step": 8 * T, "d2h_bytes_per_step": 2 * T * cfg.hidden_size},
+                          "gpu_launches": launches}))
     if world > 1:
         torch.distributed.destroy_process_group()
 

@@ -268,6 +268,18 @@ int s1_allreduce_bf16(s1_ctx* ctx, void* buf, size_t count);
 int s1_allreduce_wait(s1_ctx* ctx);
 
 /*
+ * s1_linear followed by s1_rope on the first `rotated_heads` heads (64 columns each) of the output, the rotation done
+ * in the projection's epilogue while the tile is still on chip: the reference's Wqkv projection and its `rope_qkv`
+ * kernel (src/archs/modernbert.rs:184-205, src/kernels/modernbert.cu:31-62) as one launch. Plain projections only
+ * (no bias, activation, gating or residual); head_dim = rotary_dim = 64. The result is bit-identical to the two calls
+ * made one after the other, which is also what happens for shapes the fused tile does not cover (fewer than a wave of
+ * 256 x 256 tiles, or a rotated width that is not a multiple of 128 columns).
+ */
+int s1_linear_rope(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, void* y, long long ldy, int T,
+                   const float* cos_table, const float* sin_table, const int32_t* positions, int max_positions,
+                   int rotated_heads);
+
+/*
  * Packs the next sequences of a queue into one token-packed batch (host arrays, no GPU work).
  * Takes sequences in order while the running token count stays within `token_budget`; a sequence longer than
  * the budget forms a batch of its own. Writes cu_seqlens[0..num_taken] (cu_seqlens[0] = 0, last = total) and,

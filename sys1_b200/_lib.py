@@ -83,6 +83,8 @@ SIGNATURES = {
                           C.c_longlong, C.c_longlong, C.c_int]),
     "s1_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                           C.c_longlong, C.c_int]),
+    "s1_linear_rope": (C.c_int, [C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_int,
+                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "s1_linear": (C.c_int, [C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                             C.c_void_p, C.c_longlong, C.c_int]),
 }

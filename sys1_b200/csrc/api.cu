@@ -176,8 +176,19 @@ static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0,
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, const void* residual,
-                         long long ldr, void* y, long long ldy, int T) {
+namespace {
+struct RopeArgs {  // rotary embedding fused into the epilogue of a plain projection (s1_linear_rope)
+    const float* cos_table;
+    const float* sin_table;
+    const int32_t* positions;
+    int max_positions;
+    int rope_cols;  // output columns [0, rope_cols) are 64-column heads to rotate
+    bool* fused;    // out: whether the fused kernel ran (otherwise the caller rotates afterwards)
+};
+}  // namespace
+
+static int linear_impl(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, const void* residual, long long ldr,
+                       void* y, long long ldy, int T, const RopeArgs* rope) {
     if (!ctx) return S1_EINVAL;
     if (!lin || !x || !y || !lin->w) return s1_fail(ctx, S1_EINVAL, "s1_linear: null pointer");
     const int epi = lin->epilogue;
@@ -253,6 +264,9 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
     p.residual = static_cast<const __nv_bfloat16*>(residual);
     p.bias = static_cast<const __nv_bfloat16*>(lin->bias);
     p.status = ctx->status_dev;
+    p.rope_cos = p.rope_sin = nullptr;
+    p.rope_pos = nullptr;
+    p.rope_max = p.rope_cols = 0;
 
     CUtensorMap ta, tb0, tb1, ty;
     int rc = s1_get_tmap(ctx, x, T, lin->K, ldx, kBM, kBK, 2, 128, &ta);
@@ -280,6 +294,18 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
     int mode = (residual ? 1 : 0) | ((lin->bias || lin->act != S1_ACT_NONE) ? 2 : 0);
     // residual stream updated in place (y is the residual buffer): no residual reads, the add happens in memory
     if (mode == 1 && residual == y && ldr == ldy) mode = 4;
+    if (rope) {
+        // the fused form exists for the CTA-pair tile (256 columns = 4 heads per tile, 128 per epilogue warp)
+        *rope->fused = (epi == S1_EPI_NONE && mode == 0 && ctas == 2 && bn == 256 && (rope->rope_cols % 128) == 0);
+        if (*rope->fused) {
+            p.rope_cos = rope->cos_table;
+            p.rope_sin = rope->sin_table;
+            p.rope_pos = rope->positions;
+            p.rope_max = rope->max_positions;
+            p.rope_cols = rope->rope_cols;
+            return launch_gemm<256, EPI_NONE, 8, 2>(ctx, ta, tb0, tb1, ty, p);
+        }
+    }
 #define S1_LAUNCH(BN_, CTAS_)                                                                            \
     do {                                                                                                 \
         if (epi == S1_EPI_GEGLU) return launch_gemm<BN_, EPI_GEGLU, 0, CTAS_>(ctx, ta, tb0, tb1, ty, p);   \
@@ -305,4 +331,28 @@ extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, 
     if (bn == 256) S1_LAUNCH(256, 1);
     S1_LAUNCH(128, 1);
 #undef S1_LAUNCH
+}
+
+extern "C" int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, const void* residual,
+                         long long ldr, void* y, long long ldy, int T) {
+    return linear_impl(ctx, lin, x, ldx, residual, ldr, y, ldy, T, nullptr);
+}
+
+extern "C" int s1_linear_rope(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long ldx, void* y, long long ldy, int T,
+                              const float* cos_table, const float* sin_table, const int32_t* positions, int max_positions,
+                              int rotated_heads) {
+    if (!ctx) return S1_EINVAL;
+    if (!lin || !cos_table || !sin_table || !positions) return s1_fail(ctx, S1_EINVAL, "s1_linear_rope: null pointer");
+    if (lin->epilogue != S1_EPI_NONE || lin->bias || lin->act != S1_ACT_NONE)
+        return s1_fail(ctx, S1_EINVAL, "s1_linear_rope: a plain projection only (no bias, activation or gating)");
+    if (rotated_heads < 1 || max_positions < 1 || 64LL * rotated_heads > lin->N)
+        return s1_fail(ctx, S1_EINVAL, "s1_linear_rope: %d heads of 64 columns do not fit N=%d", rotated_heads, lin->N);
+    if ((reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table)) & 15u)
+        return s1_fail(ctx, S1_EINVAL, "s1_linear_rope: tables must be 16-byte aligned");
+    bool fused = false;
+    RopeArgs args{cos_table, sin_table, positions, max_positions, 64 * rotated_heads, &fused};
+    const int rc = linear_impl(ctx, lin, x, ldx, nullptr, 0, y, ldy, T, &args);
+    if (rc != S1_OK || fused) return rc;
+    // small token counts and odd head counts run the projection's other tile shapes: rotate in a second pass
+    return s1_rope(ctx, y, ldy, cos_table, sin_table, positions, max_positions, T, rotated_heads, 64, 64);
 }

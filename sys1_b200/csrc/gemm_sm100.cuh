@@ -48,6 +48,12 @@ struct GemmParams {
     const __nv_bfloat16* residual;  // [M, n_out] or null
     const __nv_bfloat16* bias;      // [n_out] or null
     int* status;                    // device int[4]: {code, block, role, tile}; 0 = ok
+    // MODE 8 (rotary embedding in the epilogue): output columns [0, rope_cols) are heads of 64 columns whose halves are
+    // rotated by the f32 table row of the token's position; columns past rope_cols are written as they are
+    const float* rope_cos;          // [rope_max, 32]
+    const float* rope_sin;
+    const int* rope_pos;            // [M]
+    int rope_max, rope_cols;
 };
 
 constexpr int kBM = 128;  // rows per CTA
@@ -200,6 +206,71 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     static_assert(CH >= 1, "tile too narrow for this many epilogue warps");
     uint32_t va[2][32];
     uint32_t vg[PAIRED ? 2 : 1][PAIRED ? 32 : 1];
+    // staging + TMA store of one 32-column chunk of the warp's rows
+    auto emit = [&](int cix, const uint32_t (&o)[16]) {
+        const int ucol = col0 + (cix / UNIT) * SW;  // first column of the store this chunk belongs to
+        if (row0 < p.M && ucol < p.n_out && !(p.debug & 1)) {
+            const uint32_t buf = stage_buf + (nstore % NBUF) * TILE_BYTES;
+            if (cix % UNIT == 0) {
+                // the staging tile about to be overwritten must have been read out by its TMA store
+                if (lane == 0) tma_store_wait_read<NBUF - 1>();
+                __syncwarp();
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t addr;
+                if constexpr (SW == 64) {
+                    // 128-byte rows, 128B swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+                    addr = buf + lane * 128 + ((((cix % UNIT) * 4 + j) ^ (lane & 7)) << 4);
+                } else {
+                    // 64-byte rows, 64B swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
+                    addr = buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+                }
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[4 * j]), "r"(o[4 * j + 1]),
+                             "r"(o[4 * j + 2]), "r"(o[4 * j + 3])
+                             : "memory");
+            }
+            if (cix % UNIT == UNIT - 1) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (MODE == 4) tma_reduce_add_2d(tmY, buf, ucol, row0);  // y already holds the residual
+                    else tma_store_2d(tmY, buf, ucol, row0);
+                    tma_store_commit();
+                }
+                ++nstore;
+            }
+        }
+    };
+    // MODE 8: cos / sin of this lane's token (its row), fetched once per tile and used by every head of the tile
+    float cs[MODE == 8 ? 32 : 1], sn[MODE == 8 ? 32 : 1], lo[MODE == 8 ? 32 : 1];
+    bool rotate = false;
+    if constexpr (MODE == 8) {
+        static_assert(MODE != 8 || (UNIT == 2 && CH % 2 == 0), "a head's two chunks must form one store");
+        rotate = col0 < p.rope_cols;  // the same for the whole warp
+        if (rotate) {
+            const int row = row0 + lane;
+            int pos = row < p.M ? p.rope_pos[row] : 0;
+            if (pos < 0 || pos >= p.rope_max) {
+                if (atomicCAS(p.status, 0, 102) == 0) {
+                    p.status[1] = static_cast<int>(blockIdx.x);
+                    p.status[2] = row;
+                    p.status[3] = pos;
+                }
+                pos = -1;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float4 c4 = make_float4(1.f, 1.f, 1.f, 1.f), s4 = make_float4(0.f, 0.f, 0.f, 0.f);  // a bad position leaves the token unrotated
+                if (pos >= 0) {
+                    c4 = __ldg(reinterpret_cast<const float4*>(p.rope_cos + static_cast<long long>(pos) * 32) + e);
+                    s4 = __ldg(reinterpret_cast<const float4*>(p.rope_sin + static_cast<long long>(pos) * 32) + e);
+                }
+                cs[4 * e] = c4.x, cs[4 * e + 1] = c4.y, cs[4 * e + 2] = c4.z, cs[4 * e + 3] = c4.w;
+                sn[4 * e] = s4.x, sn[4 * e + 1] = s4.y, sn[4 * e + 2] = s4.z, sn[4 * e + 3] = s4.w;
+            }
+        }
+    }
     tmem_ld_32x32b_x32(taddr, va[0]);
     if constexpr (PAIRED) tmem_ld_32x32b_x32(taddr + BN / 2, vg[0]);
 #pragma unroll
@@ -217,7 +288,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
             if (lane == 0) mbar_arrive_cluster(tempty_bar);
         }
         uint32_t out[16];
-        if constexpr (!PAIRED) {
+        if constexpr (MODE == 8) {
+            // handled below, a head (two chunks) at a time
+        } else if constexpr (!PAIRED) {
             const uint32_t* v = va[ci & 1];
             if constexpr ((MODE & 2) == 0) {
                 // y = bf16(acc) [+ residual, added in bf16 with one rounding like the reference's bf16 add]
@@ -280,38 +353,37 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                 out[j] = *reinterpret_cast<uint32_t*>(&o2);
             }
         }
-        const int ucol = col0 + (ci / UNIT) * SW;  // first column of the store this chunk belongs to
-        if (row0 < p.M && ucol < p.n_out && !(p.debug & 1)) {
-            const uint32_t buf = stage_buf + (nstore % NBUF) * TILE_BYTES;
-            if (ci % UNIT == 0) {
-                // the staging tile about to be overwritten must have been read out by its TMA store
-                if (lane == 0) tma_store_wait_read<NBUF - 1>();
-                __syncwarp();
-            }
+        if constexpr (MODE == 8) {
+            // the two chunks of a head leave together: at the odd chunk, the even one (kept in `lo`) is rotated with it
+            if ((ci & 1) == 0) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t addr;
-                if constexpr (SW == 64) {
-                    // 128-byte rows, 128B swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
-                    addr = buf + lane * 128 + ((((ci % UNIT) * 4 + j) ^ (lane & 7)) << 4);
+                for (int e = 0; e < 32; ++e) lo[e] = bf16_round(__uint_as_float(va[0][e]));
+            } else {
+                uint32_t out_lo[16];
+                const uint32_t* v = va[1];
+                if (rotate) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float h0 = bf16_round(__uint_as_float(v[2 * j])), h1 = bf16_round(__uint_as_float(v[2 * j + 1]));
+                        const float l0 = lo[2 * j], l1 = lo[2 * j + 1];
+                        // products rounded one by one (no fused multiply-add), as the unfused kernel and the reference do
+                        out_lo[j] = pack_bf16x2(__fsub_rn(__fmul_rn(l0, cs[2 * j]), __fmul_rn(h0, sn[2 * j])),
+                                                __fsub_rn(__fmul_rn(l1, cs[2 * j + 1]), __fmul_rn(h1, sn[2 * j + 1])));
+                        out[j] = pack_bf16x2(__fadd_rn(__fmul_rn(l0, sn[2 * j]), __fmul_rn(h0, cs[2 * j])),
+                                             __fadd_rn(__fmul_rn(l1, sn[2 * j + 1]), __fmul_rn(h1, cs[2 * j + 1])));
+                    }
                 } else {
-                    // 64-byte rows, 64B swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
-                    addr = buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        out_lo[j] = pack_bf16x2(lo[2 * j], lo[2 * j + 1]);
+                        out[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                    }
                 }
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(out[4 * j]),
-                             "r"(out[4 * j + 1]), "r"(out[4 * j + 2]), "r"(out[4 * j + 3])
-                             : "memory");
+                emit(ci - 1, out_lo);
+                emit(ci, out);
             }
-            if (ci % UNIT == UNIT - 1) {
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    if constexpr (MODE == 4) tma_reduce_add_2d(tmY, buf, ucol, row0);  // y already holds the residual
-                    else tma_store_2d(tmY, buf, ucol, row0);
-                    tma_store_commit();
-                }
-                ++nstore;
-            }
+        } else {
+            emit(ci, out);
         }
     }
 }

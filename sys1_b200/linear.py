@@ -76,6 +76,37 @@ def fused_linear(x: torch.Tensor, weight: torch.Tensor, *, weight_up: Optional[t
     return out
 
 
+def linear_rope(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
+                rotated_heads: int, out: Optional[torch.Tensor] = None, ctx: Optional[device.Context] = None) -> torch.Tensor:
+    """`x W^T` with the rotate-half rotary embedding applied to the first `rotated_heads` 64-column heads of the
+    output in the projection's epilogue (`s1_linear_rope`): Wqkv and `RotaryEmbedding::apply_qkv` of the reference
+    (src/archs/modernbert.rs:184-205) as one launch. Tables f32 `[positions, 32]`, positions int32 `[T]`."""
+    _check(x, "x")
+    _check(weight, "weight")
+    T, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise ValueError(f"weight is {tuple(weight.shape)}, x has K={K}")
+    for name, t in (("cos", cos), ("sin", sin)):
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] != 32 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous f32 CUDA table [positions, 32]")
+    if not positions.is_cuda or positions.dtype != torch.int32 or not positions.is_contiguous() or positions.numel() != T:
+        raise ValueError("positions must be a contiguous int32 CUDA vector with one entry per row")
+    if out is None:
+        out = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+    else:
+        _check(out, "out")
+    if T == 0:
+        return out
+    if ctx is None:
+        ctx = device.load(x.device.index)
+    desc = LinearDesc(w=weight.data_ptr(), ldw=weight.stride(0), w_up=0, ldw_up=0, bias=0, N=N, K=K, epilogue=EPI_NONE, act=_ACTS[None])
+    rc = ctx._lib.s1_linear_rope(ctx.handle, C.byref(desc), _ptr(x), x.stride(0), _ptr(out), out.stride(0), T, _ptr(cos), _ptr(sin),
+                                 _ptr(positions), min(cos.shape[0], sin.shape[0]), int(rotated_heads))
+    ctx.check(rc)
+    return out
+
+
 class Linear:
     """`candle_nn::Linear` as the reference builds it: `weight [out, in]`, optional `bias [out]`."""
 

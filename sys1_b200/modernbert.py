@@ -12,7 +12,7 @@ import torch
 
 from . import norm as _norm
 from ._lib import EPI_GEGLU
-from .linear import Linear, fused_linear
+from .linear import Linear, fused_linear, linear_rope
 
 
 class Norm:
@@ -38,6 +38,11 @@ class RotaryEmbedding:
         fr = torch.arange(max_positions, dtype=torch.float32, device=dev).unsqueeze(1) * inv.unsqueeze(0)
         self.cos, self.sin = fr.cos().contiguous(), fr.sin().contiguous()
         self.head_dim = head_dim
+
+    def project_qkv(self, x: torch.Tensor, wqkv: Linear, positions: torch.Tensor, heads: int) -> torch.Tensor:
+        """`x.apply(&self.wqkv)` followed by `apply_qkv` (src/archs/modernbert.rs:184-205) as one launch: the rotation
+        happens in the projection's epilogue (`s1_linear_rope`)."""
+        return linear_rope(x, wqkv.weight, self.cos, self.sin, positions, 2 * heads)
 
     def apply_qkv(self, qkv: torch.Tensor, positions: torch.Tensor, heads: int) -> torch.Tensor:
         """qkv bf16 `[T, 3 * heads * head_dim]`, positions int32 `[T]`; rotates the 2 * heads q and k heads in place."""
@@ -173,15 +178,15 @@ class Encoder:
         p = f"layers.{i}."
         local = i % cfg.global_attn_every_n_layers != 0
         n = x if i == 0 else self._ln(x, p + "attn_norm")
-        qkv = proj.qkv(n)
         rotary = self._rope(cfg.local_rope_theta if local else cfg.global_rope_theta, max_len, dev)
         attn = torch.empty((T, H * D), dtype=torch.bfloat16, device=dev)
         if self.attention == "s1":
-            rotary.apply_qkv(qkv, pos, H)
+            qkv = rotary.project_qkv(n, proj.wqkv, pos, H)   # Wqkv with RoPE in its epilogue
             q, k, v = qkv.view(T, 3, H, D).unbind(1)
             attention_varlen(q, k, v, bounds, window=cfg.local_attention // 2 if local else -1, out=attn)
         else:
             F = torch.nn.functional
+            qkv = proj.qkv(n)
             c, s = rotary.cos[pos.long()].unsqueeze(1), rotary.sin[pos.long()].unsqueeze(1)
 
             def rot(t):

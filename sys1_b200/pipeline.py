@@ -45,6 +45,7 @@ class HostPipeline:
         result = step(self.inputs[slot])
         self.done[slot].record(comp)
         self.s_out.wait_event(self.done[slot])
+        result.record_stream(self.s_out)  # the caching allocator must not hand the result's memory out before the copy ran
         with torch.cuda.stream(self.s_out):
             host_out.copy_(result, non_blocking=True)
             self.slot_free[slot].record(self.s_out)

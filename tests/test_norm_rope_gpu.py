@@ -127,3 +127,28 @@ def test_rope_position_outside_the_table_is_reported(ctx):
         ctx.sync()
     ctx.sync()
     assert torch.equal(x[3].cpu(), torch.ones(3 * 64, dtype=torch.bfloat16))  # that token left as it was
+
+
+@pytest.mark.parametrize("T,H,hidden", [(4100, 16, 1024), (4096, 12, 768), (300, 4, 256), (5000, 3, 512)])
+def test_projection_with_rope_in_its_epilogue_equals_the_two_calls(ctx, T, H, hidden):
+    """`s1_linear_rope` against `s1_linear` followed by `s1_rope`: bit-identical, both where the fused tile runs (a wave
+    or more of 256 x 256 tiles, rotated width a multiple of 128 columns) and where the library falls back to two passes
+    (few tokens; 3 heads = 384 rotated columns)."""
+    from sys1_b200.linear import fused_linear, linear_rope
+    g = torch.Generator().manual_seed(T + H)
+    x = torch.randn(T, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(3 * H * 64, hidden, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    P = 700
+    pos = torch.randint(0, P, (T,), generator=g, dtype=torch.int32).to(DEV)
+    rot = RotaryEmbedding(10000.0, 64, P, DEV)
+    got = linear_rope(x, w, rot.cos, rot.sin, pos, 2 * H)
+    want = fused_linear(x, w)
+    norm.rope_(want, rot.cos, rot.sin, pos, 2 * H, 64, 64)
+    ctx.sync()
+    assert torch.equal(got, want)
+    # and against the oracle on a sample of rows
+    rows = torch.randint(0, T, (40,), generator=g)
+    y = oracle.linear(x[rows].float().cpu(), w.float().cpu(), dtype="bf16").view(40, 3, H, 64)
+    c, s = rot.cos[pos[rows].long()].cpu(), rot.sin[pos[rows].long()].cpu()
+    ref_q = oracle.round_bf16(oracle.rope(y[:, 0], c, s))
+    assert (got[rows].float().cpu().view(40, 3, H, 64)[:, 0] - ref_q).abs().max() <= 2e-2 * float(ref_q.abs().max())
