@@ -349,7 +349,7 @@ def run_tp(args, rank, world, local_rank):
     H, I, T = 5120, 17408, args.tokens
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=dev)
-        tp = tensor_parallel.TensorParallel.from_process_group(local_rank)
+        tp = tensor_parallel.TensorParallel.from_process_group(local_rank, comm_ctas=args.comm_ctas)
     else:
         tp = tensor_parallel.TensorParallel(device.load(local_rank), 0, 1)
     ctx = tp.ctx
@@ -399,7 +399,7 @@ def run_tp(args, rank, world, local_rank):
                           "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
                           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                           "config": {"workload": f"27B-shaped SwiGLU MLP (5120 -> 2 x 17408 -> 5120), T={T}, tensor parallel x{world}, "
-                                                 f"gate/up, down and all-reduce in {args.slabs} row slabs, {args.comm_sms} SMs left to the all-reduce", "parallelism": f"tp{world}",
+                                                 f"gate/up, down and all-reduce in {args.slabs} row slabs, {args.comm_sms} SMs left to the all-reduce ({args.comm_ctas or 'default'} blocks)", "parallelism": f"tp{world}",
                                      "l2": "activations (x, h, out) exceed the 126 MB L2"},
                           "ms_without_exchange": ms_math, "ms_allreduce_alone": ms_ar,
                           "allreduce_busbw_gbs": (2.0 * (world - 1) / world * bytes_ar / (ms_ar * 1e-3) / 1e9) if world > 1 else None,
@@ -422,6 +422,7 @@ def main():
                     help="projections (default, the headline microbench); encoder: ModernBERT-large forward, tokens/s; "
                          "tp: SwiGLU MLP of the 27B-shaped hybrid model, tensor-parallel over the ranks")
     ap.add_argument("--slabs", type=int, default=4, help="tp workload: row slabs the all-reduce is pipelined in")
+    ap.add_argument("--comm-ctas", type=int, default=0, help="tp workload: blocks the all-reduce may use (0 = NCCL's default)")
     ap.add_argument("--comm-sms", type=int, default=16, help="tp workload: SMs the projections leave to the all-reduce of the previous slab")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step from a CUDA graph (for small token budgets, where launching from Python is the bottleneck)")

@@ -63,7 +63,8 @@ int s1_device_count(int* out);
 long long s1_launch_count(const s1_ctx* ctx);
 /* Tuning knobs: "gemm_bn" = 0 (auto), 512 / 384 (CTA-pair 256x256 / 256x192 tiles), 256 or 128 (single-CTA 128xBN tiles);
  * "gemm_sms" = how many SMs the projections' persistent grids may occupy (0 = all; e.g. 132 leaves 16 SMs to the
- * all-reduce of the previous slab in a tensor-parallel layer); "pdl" = 1 (default) launches the projections with
+ * all-reduce of the previous slab in a tensor-parallel layer); "comm_ctas" = how many blocks the collective may use
+ * (0 = NCCL's default; takes effect at s1_comm_init); "pdl" = 1 (default) launches the projections with
  * programmatic stream serialization, so that a projection's set-up overlaps the tail of the kernel before it, 0 turns
  * that off; "debug" = measurement aids of the GEMM epilogue
  * (0 in production). */

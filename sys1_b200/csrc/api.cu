@@ -83,6 +83,11 @@ extern "C" int s1_set_option(s1_ctx* ctx, const char* name, long long value) {
         ctx->opt_gemm_sms = static_cast<int>(value);
         return S1_OK;
     }
+    if (strcmp(name, "comm_ctas") == 0) {  // set before s1_comm_init
+        if (value < 0 || value > 64) return s1_fail(ctx, S1_EINVAL, "comm_ctas must be between 0 (default) and 64 (got %lld)", value);
+        ctx->opt_comm_ctas = static_cast<int>(value);
+        return S1_OK;
+    }
     if (strcmp(name, "pdl") == 0) {  // programmatic dependent launch of the projections (default on)
         ctx->opt_pdl = value != 0;
         return S1_OK;

@@ -23,6 +23,7 @@ struct NcclApi {
     void* handle = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;  // optional
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -44,6 +45,7 @@ NcclApi* nccl_api() {
     }
     api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
     api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
+    api.CommInitRankConfig = reinterpret_cast<decltype(api.CommInitRankConfig)>(dlsym(api.handle, "ncclCommInitRankConfig"));
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
     api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
@@ -91,7 +93,15 @@ extern "C" int s1_comm_init(s1_ctx* ctx, const void* id, int rank, int size) {
     ncclUniqueId uid;
     memcpy(&uid, id, sizeof(uid));
     ncclComm_t comm = nullptr;
-    const ncclResult_t rc = api->CommInitRank(&comm, size, uid, rank);
+    ncclResult_t rc;
+    if (ctx->opt_comm_ctas > 0 && api->CommInitRankConfig) {
+        // a bounded number of blocks for the collective, so that it fits on the SMs the projections leave free ("gemm_sms")
+        ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+        config.maxCTAs = ctx->opt_comm_ctas;
+        rc = api->CommInitRankConfig(&comm, size, uid, rank, &config);
+    } else {
+        rc = api->CommInitRank(&comm, size, uid, rank);
+    }
     if (rc != ncclSuccess) return s1_fail(ctx, S1_ECUDA, "ncclCommInitRank failed: %s", api->GetErrorString(rc));
     int prio_low = 0, prio_high = 0;  // the collective's blocks go first when SMs free up
     cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high);

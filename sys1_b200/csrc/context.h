@@ -44,6 +44,7 @@ struct s1_ctx {
     int opt_gemm_bn = 0;
     int opt_debug = 0;
     int opt_gemm_sms = 0;  // 0 = all SMs
+    int opt_comm_ctas = 0;  // blocks the collective may use (0 = the library's default); read by s1_comm_init
     bool opt_pdl = true;   // launch the projections with programmatic stream serialization
     PFN_cuTensorMapEncodeTiled encode = nullptr;
     std::unordered_map<S1TmapKey, CUtensorMap, S1TmapKeyHash> tmaps;

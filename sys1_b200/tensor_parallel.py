@@ -30,14 +30,16 @@ class TensorParallel:
         self.ctx, self.rank, self.size = ctx, int(rank), int(size)
 
     @classmethod
-    def from_process_group(cls, ordinal: int) -> "TensorParallel":
-        """Builds the communicator over the ranks of `torch.distributed`'s default group (used only to carry the id)."""
+    def from_process_group(cls, ordinal: int, comm_ctas: int = 0) -> "TensorParallel":
+        """Builds the communicator over the ranks of `torch.distributed`'s default group (used only to carry the id).
+        `comm_ctas` bounds the blocks the collective runs on (0 = NCCL's default)."""
         import torch.distributed as dist
         rank, size = dist.get_rank(), dist.get_world_size()
         box = [device.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         ctx = device.load(ordinal)
         if getattr(ctx, "comm_size", 0) != size:
+            ctx.set_option("comm_ctas", comm_ctas)
             ctx.comm_init(rank, size, box[0])
         return cls(ctx, rank, size)
 
