@@ -74,3 +74,26 @@ def test_row_maximum_that_keeps_growing(ctx, window):
     assert float((scores[:, 600, 600:665].max(-1).values - scores[:, 600, 536:600].max(-1).values).min()) > 16.0
     assert torch.isfinite(got).all()
     assert max_rel(got, want) <= 2e-2
+
+
+def test_edge_cases_empty_batch_window_wider_than_sequences_and_strided_views(ctx):
+    # nothing to do
+    q = torch.zeros(0, 2, 64, dtype=torch.bfloat16, device=DEV)
+    assert modernbert.attention_varlen(q, q, q, np.array([0], dtype=np.int32)).shape == (0, 128)
+    # a window wider than every sequence is global attention
+    lens = [50, 7, 120]
+    cu = np.cumsum([0] + lens).astype(np.int32)
+    g = torch.Generator().manual_seed(77)
+    qkv = torch.randn(int(cu[-1]), 3 * 2 * 64 + 16, generator=g).to(torch.bfloat16).to(DEV)  # padded rows: ld = 400
+    v4 = qkv[:, : 3 * 128].view(-1, 3, 2, 64)
+    wide = modernbert.attention_varlen(v4[:, 0], v4[:, 1], v4[:, 2], cu, window=500)
+    glob = modernbert.attention_varlen(v4[:, 0], v4[:, 1], v4[:, 2], cu, window=-1)
+    ctx.sync()
+    assert torch.equal(wide, glob)
+    # window 0: every token attends to itself only, so the output is v
+    self_only = modernbert.attention_varlen(v4[:, 0], v4[:, 1], v4[:, 2], cu, window=0)
+    ctx.sync()
+    assert torch.equal(self_only.view(-1, 2, 64), v4[:, 2])
+    # bad arguments are refused before anything is launched
+    with pytest.raises(RuntimeError):
+        modernbert.attention_varlen(v4[:, 0], v4[:, 1], v4[:, 2], np.array([0, 10], dtype=np.int32))  # does not end at T
