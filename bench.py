@@ -437,6 +437,8 @@ def main():
               "tokens": T, "hidden": HIDDEN, "intermediate": INTER, "parallelism": f"replicas x{world}",
               "l2": "4 rotating input sets (400 MB) + 226 MB of outputs per step exceed the 126 MB L2",
               "launch": "cuda graph replay" if args.graph else "eager",
+              "timing": "K steps back to back between two events; per-kernel durations from 40 back-to-back launches of each "
+                        "projection on the same rotating buffers between two events of their own",
               "residual": "in place (x += ...); alternate visits of a buffer use -Wo / -Wout to keep the stream bounded"}
 
     if args.impl == "reference":
@@ -499,18 +501,12 @@ def main():
     neg_proj = modernbert.AttentionProjections(proj.wqkv, linear.linear_no_bias(-W["wo"]))
     neg_mlp = modernbert.Mlp(mlp.input, linear.linear_no_bias(-W["wout"]))
 
-    def step(x, a, marks=None, negate=False):
-        """marks: list of 5 events recorded between the launches (on the launching stream)."""
+    def step(x, a, negate=False):
         proj, mlp = (neg_proj, neg_mlp) if negate else (pos_proj, pos_mlp)
-        if marks: marks[0].record()
         proj.wqkv.forward(x, out=qkv)
-        if marks: marks[1].record()
         proj.wo.forward(a, residual=x, out=x)
-        if marks: marks[2].record()
         linear.fused_linear(x, mlp.input.weight, epilogue=linear.EPI_GEGLU, out=m)
-        if marks: marks[3].record()
         mlp.output.forward(m, residual=x, out=x)
-        if marks: marks[4].record()
         return x
 
     def barrier():
@@ -539,7 +535,6 @@ def main():
                 graphs[(s_, neg)] = g_
         torch.cuda.synchronize()
     launches0 = ctx.launch_count()
-    marks = [[ev() for _ in range(5)] for _ in range(args.steps)]
     sampler = ClockSampler(local_rank)
     sampler.start()
     time.sleep(0.15)
@@ -551,7 +546,7 @@ def main():
         if graphs is not None:
             graphs[(i % NSETS, bool((i // NSETS) & 1))].replay()
         else:
-            step(xs[i % NSETS], atts[i % NSETS], marks[i], negate=bool((i // NSETS) & 1))
+            step(xs[i % NSETS], atts[i % NSETS], negate=bool((i // NSETS) & 1))
     e1.record()
     barrier()
     t1w = time.time()
@@ -560,11 +555,32 @@ def main():
     ms_total = e0.elapsed_time(e1)
     if graphs is not None:
         launches = 4 * args.steps  # replayed from the graphs (4 kernel nodes each), not counted by the context
-        # no per-launch events inside a graph: split the step time by algorithmic flops for the breakdown
-        per = {n: (ms_total / args.steps) * (2 * pj[1] * pj[2]) / FLOPS_PER_TOKEN for n, pj in zip(names, PROJECTIONS)}
-    else:
-        per = {n: sum(marks[i][j].elapsed_time(marks[i][j + 1]) for i in range(args.steps)) / args.steps
-               for j, n in enumerate(names)}
+    # per-kernel durations: each projection launched back to back on the rotating buffer sets between two events of its
+    # own (an event between every two launches of a step would itself cost several microseconds per launch and keep
+    # a projection's set-up from overlapping its predecessor's tail, which is what the timed loop above benefits from)
+    def one(name, i):
+        x, a, neg = xs[i % NSETS], atts[i % NSETS], bool((i // NSETS) & 1)
+        pj, ml = (neg_proj, neg_mlp) if neg else (pos_proj, pos_mlp)
+        if name == "wqkv":
+            pj.wqkv.forward(x, out=qkv)
+        elif name == "wo+residual":
+            pj.wo.forward(a, residual=x, out=x)
+        elif name == "wi+geglu":
+            linear.fused_linear(x, ml.input.weight, epilogue=linear.EPI_GEGLU, out=m)
+        else:
+            ml.output.forward(m, residual=x, out=x)
+
+    per, reps = {}, 2 * NSETS * 5
+    for n in names:
+        for i in range(2 * NSETS):
+            one(n, i)
+        k0, k1 = ev(), ev()
+        k0.record()
+        for i in range(reps):
+            one(n, i)
+        k1.record()
+        torch.cuda.synchronize()
+        per[n] = k0.elapsed_time(k1) / reps
 
     # ---- end-to-end arm: host buffers in, host buffer out, copies inside the timed region ----------------------
     # (copy-in of batch i+1 and copy-out of batch i-1 overlap the compute of batch i: sys1_b200.pipeline)
