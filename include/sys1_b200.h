@@ -220,18 +220,21 @@ int s1_attention_gqa(s1_ctx* ctx, const void* q, long long ldq, long long q_head
 
 /*
  * Row-wise normalisation of a bf16 matrix, statistics in f32, one rounding at the end:
- *     kind 0  y = (x - mean(x)) / sqrt(var(x) + eps) * weight        LayerNorm without bias: the reference's `Norm`
- *                                                                    (src/archs/modernbert.rs:1006-1034)
+ *     kind 0  y = (x - mean(x)) / sqrt(var(x) + eps) * weight (+ bias)   LayerNorm: without bias the reference's `Norm`
+ *                                                                    (src/archs/modernbert.rs:1006-1034), with `bias`
+ *                                                                    (bf16 [width], else NULL) the `layer_norm` of the
+ *                                                                    decision heads (src/models/laya.rs:85-86,258)
  *     kind 1  y = x / sqrt(mean(x^2) + eps) * (1 + weight)           the reference's `RmsNorm`
  *                                                                    (src/archs/qwen35_text.rs:178-203)
  * x: [rows, width] with row stride ldx; weight: bf16 [width]; y: [rows, width] with row stride ldy (may be x).
  * With `gather` (DEVICE int32 [rows]) row r is read from x[gather[r]]: the embedding lookup fused with the
  * embedding norm (src/archs/modernbert.rs:1084-1092); `gather_rows` is the row count of x, and an index outside
- * it is reported by s1_sync as S1_EKERNEL (that row is left unwritten). Rows of any width that is a multiple of 8:
+ * it is reported by s1_sync as S1_EKERNEL (that row is left unwritten); the same index is the marker-row selection
+ * ahead of the scorer (`index_select` + `scorer_norm`, src/models/laya.rs:476-513). Rows of any width that is a multiple of 8:
  * hidden states (rows = tokens) and per-head q / k norms (rows = tokens x heads, width = head_dim) alike.
  */
 int s1_norm(s1_ctx* ctx, const void* x, long long ldx, const int32_t* gather, int gather_rows, const void* weight,
-            float eps, int kind, void* y, long long ldy, long long rows, int width);
+            const void* bias, float eps, int kind, void* y, long long ldy, long long rows, int width);
 
 /*
  * Rotate-half rotary embedding, in place, on `heads` consecutive heads of every token row:

@@ -19,11 +19,14 @@ import torch
 from .projection import round_bf16
 
 
-def layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: str = "f32") -> torch.Tensor:
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: str = "f32", bias=None) -> torch.Tensor:
+    """Without `bias` the encoder's `Norm`; with it the `layer_norm` of the decision heads (src/models/laya.rs:85-86,258)."""
     x = x.to(torch.float32)
     mean = x.mean(-1, keepdim=True)
     var = (x - mean).square().mean(-1, keepdim=True)
     y = (x - mean) / (var + eps).sqrt() * weight.to(torch.float32)
+    if bias is not None:
+        y = y + bias.to(torch.float32)
     return round_bf16(y) if dtype == "bf16" else y
 
 

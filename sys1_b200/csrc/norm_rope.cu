@@ -24,6 +24,7 @@ struct NormParams {
     const int32_t* gather;  // optional row index into x
     int gather_rows;
     const __nv_bfloat16* w;
+    const __nv_bfloat16* b;  // optional bias (LayerNorm with bias: the heads' `layer_norm`, src/models/laya.rs:85-86,258)
     float eps;
     int kind;  // 0 LayerNorm (mean removed), 1 RMSNorm with (1 + w)
     __nv_bfloat16* y;
@@ -120,11 +121,12 @@ __global__ void __launch_bounds__(256) s1_norm_kernel(const NormParams p) {
     for (int i = 0; i < MAXCH; ++i) {
         const int c = sub + i * LPR;
         if (c < nchunks) {
-            float f[8], g[8];
+            float f[8], g[8], bb[8];
             unpack8(v[i], f);
             unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + c * 8)), g);
+            unpack8(p.b ? __ldg(reinterpret_cast<const uint4*>(p.b + c * 8)) : make_uint4(0, 0, 0, 0), bb);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd * (g[e] + one);
+            for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd * (g[e] + one) + bb[e];
             *reinterpret_cast<uint4*>(dst + c * 8) = pack8(f);
         }
     }
@@ -159,11 +161,12 @@ __global__ void __launch_bounds__(256) s1_norm_wide_kernel(const NormParams p) {
     const float one = p.kind == 1 ? 1.f : 0.f;
     __nv_bfloat16* dst = p.y + row * p.ldy;
     for (int c = lane; c < nchunks; c += 32) {
-        float f[8], g[8];
+        float f[8], g[8], bb[8];
         unpack8(*reinterpret_cast<const uint4*>(src + c * 8), f);
         unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + c * 8)), g);
+        unpack8(p.b ? __ldg(reinterpret_cast<const uint4*>(p.b + c * 8)) : make_uint4(0, 0, 0, 0), bb);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd * (g[e] + one);
+        for (int e = 0; e < 8; ++e) f[e] = (f[e] - mean) * rstd * (g[e] + one) + bb[e];
         *reinterpret_cast<uint4*>(dst + c * 8) = pack8(f);
     }
 }
@@ -224,18 +227,18 @@ inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) =
 }  // namespace
 
 extern "C" int s1_norm(s1_ctx* ctx, const void* x, long long ldx, const int32_t* gather, int gather_rows, const void* weight,
-                       float eps, int kind, void* y, long long ldy, long long rows, int width) {
+                       const void* bias, float eps, int kind, void* y, long long ldy, long long rows, int width) {
     if (!ctx) return S1_EINVAL;
     if (!x || !weight || !y) return s1_fail(ctx, S1_EINVAL, "s1_norm: null pointer");
     if (kind != 0 && kind != 1) return s1_fail(ctx, S1_EINVAL, "s1_norm: kind must be 0 (LayerNorm) or 1 (RMSNorm)");
     if (rows < 0 || width < 8 || (width % 8)) return s1_fail(ctx, S1_EINVAL, "s1_norm: width must be a multiple of 8");
-    if ((ldx % 8) || (ldy % 8) || ldx < width || ldy < width || !al16(x) || !al16(y) || !al16(weight))
+    if ((ldx % 8) || (ldy % 8) || ldx < width || ldy < width || !al16(x) || !al16(y) || !al16(weight) || !al16(bias))
         return s1_fail(ctx, S1_EINVAL, "s1_norm: rows and weight must be 16-byte aligned, ld >= width");
     if (gather && gather_rows <= 0) return s1_fail(ctx, S1_EINVAL, "s1_norm: gather needs the row count of x");
     if (rows == 0) return S1_OK;
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     NormParams p{static_cast<const __nv_bfloat16*>(x), ldx, gather, gather_rows, static_cast<const __nv_bfloat16*>(weight),
-                 eps, kind, static_cast<__nv_bfloat16*>(y), ldy, rows, width, ctx->status_dev};
+                 static_cast<const __nv_bfloat16*>(bias), eps, kind, static_cast<__nv_bfloat16*>(y), ldy, rows, width, ctx->status_dev};
     const int chunks = width / 8;
     if (chunks <= 8) launch_norm<1, 8>(p, ctx->stream);
     else if (chunks <= 16) launch_norm<1, 16>(p, ctx->stream);

@@ -19,7 +19,7 @@ def _rows(t: torch.Tensor, name: str) -> torch.Tensor:
 
 
 def norm(x: torch.Tensor, weight: torch.Tensor, eps: float, kind: int = LAYER_NORM, gather: Optional[torch.Tensor] = None,
-         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+         out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`Norm::forward` (src/archs/modernbert.rs:1024-1034; kind 0) or `RmsNorm::forward`
     (src/archs/qwen35_text.rs:191-203; kind 1) on `x [rows, width]`. With `gather` (int32 CUDA `[rows]`) the rows are
     `x[gather]`: embedding lookup and embedding norm in one pass. `out` may be `x`."""
@@ -30,6 +30,8 @@ def norm(x: torch.Tensor, weight: torch.Tensor, eps: float, kind: int = LAYER_NO
         raise ValueError("gather must be a contiguous int32 CUDA vector")
     if weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.numel() != width or not weight.is_contiguous():
         raise ValueError("weight must be a contiguous bf16 CUDA vector of the row width")
+    if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_cuda or bias.numel() != width or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous bf16 CUDA vector of the row width")
     if out is None:
         out = torch.empty((rows, width), dtype=torch.bfloat16, device=x.device)
     _rows(out, "out")
@@ -37,7 +39,8 @@ def norm(x: torch.Tensor, weight: torch.Tensor, eps: float, kind: int = LAYER_NO
         return out
     ctx = device.load(x.device.index)
     rc = ctx._lib.s1_norm(ctx.handle, C.c_void_p(x.data_ptr()), x.stride(0), C.c_void_p(gather.data_ptr() if gather is not None else 0),
-                          x.shape[0] if gather is not None else 0, C.c_void_p(weight.data_ptr()), C.c_float(eps), int(kind),
+                          x.shape[0] if gather is not None else 0, C.c_void_p(weight.data_ptr()),
+                          C.c_void_p(bias.data_ptr() if bias is not None else 0), C.c_float(eps), int(kind),
                           C.c_void_p(out.data_ptr()), out.stride(0), rows, width)
     ctx.check(rc)
     return out

@@ -41,3 +41,23 @@ def test_shard_views():
         device.column_parallel_shard(w, 0, 3)
     with pytest.raises(ValueError):
         device.row_parallel_shard(w, 0, 3)
+
+
+def test_deduplicate_keeps_first_occurrences_in_order():
+    """`deduplicate` of src/models/laya.rs:689-707: representatives in order of first appearance, one index per input."""
+    from sys1_b200 import laya
+    a, b, c = ("kind0", (1, 2, 3), (0, 2)), ("kind0", (1, 2, 3), (0, 1)), ("kind1", (1, 2, 3), (0, 2))
+    unique, indices = laya.deduplicate([a, b, a, c, b, a])
+    assert unique == [a, b, c]
+    assert indices == [0, 1, 0, 2, 1, 0]
+    assert laya.deduplicate([]) == ([], [])
+
+
+def test_marker_rows_on_the_packed_layout():
+    from sys1_b200 import laya
+    rows, counts = laya.marker_rows([0, 5, 5, 12], [[0, 4], [], [6, 1, 1]])
+    assert rows.tolist() == [0, 4, 11, 6, 6] and counts == [2, 0, 3]
+    with pytest.raises(ValueError):
+        laya.marker_rows([0, 5], [[5]])          # position past the end of its sequence
+    with pytest.raises(ValueError):
+        laya.marker_rows([0, 5, 9], [[0]])       # one marker list per sequence

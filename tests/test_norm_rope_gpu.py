@@ -152,3 +152,31 @@ def test_projection_with_rope_in_its_epilogue_equals_the_two_calls(ctx, T, H, hi
     c, s = rot.cos[pos[rows].long()].cpu(), rot.sin[pos[rows].long()].cpu()
     ref_q = oracle.round_bf16(oracle.rope(y[:, 0], c, s))
     assert (got[rows].float().cpu().view(40, 3, H, 64)[:, 0] - ref_q).abs().max() <= 2e-2 * float(ref_q.abs().max())
+
+
+def test_layer_norm_with_bias_and_the_scorer_on_marker_rows(ctx):
+    """`s1_norm` with a bias (the heads' `layer_norm`) and the scorer chain of src/models/laya.rs:476-518 on the packed
+    layout: marker rows selected and normalised in one call, Linear + bias + GELU(erf), Linear to one logit."""
+    from sys1_b200 import laya
+    from sys1_b200.linear import Linear
+    g = torch.Generator().manual_seed(21)
+    hidden, lens = 256, [40, 3, 77]
+    cu = np.cumsum([0] + lens).astype(np.int32)
+    T = int(cu[-1])
+    h = torch.randn(T, hidden, generator=g).to(torch.bfloat16)
+    nw, nb = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16), (0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
+    w1, b1 = (torch.randn(hidden, hidden, generator=g) * 0.05).to(torch.bfloat16), (0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
+    w2, b2 = (torch.randn(1, hidden, generator=g) * 0.05).to(torch.bfloat16), (0.1 * torch.randn(1, generator=g)).to(torch.bfloat16)
+    got_n = norm.norm(h.to(DEV), nw.to(DEV), 1e-5, bias=nb.to(DEV))
+    _close_one_step(got_n, oracle.layer_norm(h.float(), nw.float(), 1e-5, dtype="bf16", bias=nb.float()))
+    markers = [[0, 39, 7], [], [76, 76, 1, 30]]
+    scorer = laya.Scorer(nw.to(DEV), nb.to(DEV), Linear(w1.to(DEV), b1.to(DEV)), Linear(w2.to(DEV), b2.to(DEV)))
+    got = scorer.score_packed(h.to(DEV), cu, markers)
+    ctx.sync()
+    assert [len(v) for v in got] == [3, 0, 4]
+    rows, _ = laya.marker_rows(cu, markers)
+    sel = oracle.layer_norm(h[torch.from_numpy(rows).long()].float(), nw.float(), 1e-5, dtype="f32", bias=nb.float())
+    want = oracle.linear(oracle.linear(sel, w1, b1, act="gelu", dtype="f32"), w2, b2, dtype="f32")[:, 0]
+    flat = torch.tensor([v for seq in got for v in seq])
+    assert (flat - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max()))
+    assert got[2][0] == got[2][1]  # the same marker twice gives the same logit
