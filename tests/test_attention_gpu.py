@@ -97,3 +97,30 @@ def test_edge_cases_empty_batch_window_wider_than_sequences_and_strided_views(ct
     # bad arguments are refused before anything is launched
     with pytest.raises(RuntimeError):
         modernbert.attention_varlen(v4[:, 0], v4[:, 1], v4[:, 2], np.array([0, 10], dtype=np.int32))  # does not end at T
+
+
+def test_full_size_batch_properties(ctx):
+    """The encoder benchmark's batch (T = 32768, 16 heads, log-uniform lengths up to 8192): a sequence's rows are
+    bit-identical whether it runs inside the packed batch or alone, global and banded, and sampled rows match the
+    oracle (which could not finish the whole batch in reasonable time)."""
+    from sys1_b200 import batching
+    T, H = 32768, 16
+    lens = batching.synthetic_lengths(1003, 8, 8192, T, log_uniform=True)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    g = torch.Generator(device=DEV).manual_seed(5)
+    qkv = torch.randn(T, 3, H, 64, device=DEV, generator=g).to(torch.bfloat16)
+    order = np.argsort(lens)
+    picks = [int(order[len(order) // 2]), int(order[-1])]  # a median-length sequence and the longest one
+    for window in (-1, 64):
+        packed = modernbert.attention_varlen(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, window=window)
+        for s in picks:
+            a, z = int(cu[s]), int(cu[s + 1])
+            alone = modernbert.attention_varlen(qkv[a:z, 0], qkv[a:z, 1], qkv[a:z, 2], np.array([0, z - a], dtype=np.int32), window=window)
+            assert torch.equal(packed[a:z], alone)
+        s = picks[0]
+        a, z = int(cu[s]), int(cu[s + 1])
+        if z - a <= 1500:
+            sub = qkv[a:z].cpu()
+            want = oracle.attention(sub[:, 0], sub[:, 1], sub[:, 2], window)
+            assert max_rel(packed[a:z].float().cpu(), want) <= 2e-2
+    ctx.sync()

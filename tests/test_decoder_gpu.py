@@ -97,3 +97,24 @@ def test_small_hybrid_stack(ctx):
         got = y[z - 1].float().cpu() @ probe.t()
         want = out["f32"][0][z - 1] @ probe.t()
         assert torch.equal(got.argsort(), want.argsort())
+
+
+def test_causal_gqa_full_size_batch_properties(ctx):
+    """The decoder benchmark's batch (T = 16384, 8 query / 2 KV heads, lengths 64-2048): packed versus alone bit-identical
+    for a short and the longest sequence, and the first token of every sequence attends to itself only (output = v * gate)."""
+    T, H, KV = 16384, 8, 2
+    lens = batching.synthetic_lengths(1004, 64, 2048, T)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    g = torch.Generator(device=DEV).manual_seed(6)
+    q = torch.randn(T, H, 256, device=DEV, generator=g).to(torch.bfloat16)
+    k = torch.randn(T, KV, 256, device=DEV, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, KV, 256, device=DEV, generator=g).to(torch.bfloat16)
+    packed = qwen35.attention_causal_gqa(q, k, v, cu)
+    for s in (int(np.argmin(lens)), int(np.argmax(lens))):
+        a, z = int(cu[s]), int(cu[s + 1])
+        alone = qwen35.attention_causal_gqa(q[a:z], k[a:z], v[a:z], np.array([0, z - a], dtype=np.int32))
+        assert torch.equal(packed[a:z], alone)
+    ctx.sync()
+    first = torch.from_numpy(cu[:-1].astype(np.int64)).to(DEV)
+    want = v[first].repeat_interleave(H // KV, dim=1).reshape(len(first), H * 256)
+    assert torch.equal(packed[first], want)
