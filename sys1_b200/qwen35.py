@@ -39,8 +39,10 @@ class Mlp:
     def gated(self, x: torch.Tensor) -> torch.Tensor:
         return fused_linear(x, self.gate.weight, weight_up=self.up.weight, epilogue=EPI_SWIGLU)
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return self.down.forward(self.gated(x), residual=residual)
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, inplace: bool = False) -> torch.Tensor:
+        """`inplace`: write `residual + mlp(x)` into `residual` itself (the residual stream updated in memory by the
+        projection's store, no read of it by the SMs)."""
+        return self.down.forward(self.gated(x), residual=residual, out=residual if inplace else None)
 
     __call__ = forward
 
@@ -176,7 +178,8 @@ class LinearAttention:
             at += n
         return tuple(outs)
 
-    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                inplace: bool = False) -> torch.Tensor:
         import numpy as np
         ctx = device.load(x.device.index)
         T = x.shape[0]
@@ -193,7 +196,7 @@ class LinearAttention:
             zz.stride(0), C.c_void_p(self.norm.data_ptr()), C.c_float(self.eps), cu.ctypes.data_as(C.POINTER(C.c_int32)),
             len(cu) - 1, T, self.key_heads, self.value_heads, C.c_void_p(y.data_ptr()), y.stride(0), C.c_void_p(ptr), need)
         ctx.check(rc)
-        return self.output.forward(y, residual=residual)                           # out_proj (+ the layer's residual, :938)
+        return self.output.forward(y, residual=residual, out=residual if inplace else None)  # out_proj (+ the layer's residual, :938)
 
 
 class RopeParams:
@@ -247,7 +250,8 @@ class FullAttention:
         self.q, self.k, self.v, self.output, self.q_norm, self.k_norm = q, k, v, output, q_norm, k_norm
         self.heads, self.kv_heads, self.head_dim, self.rope, self.core = heads, kv_heads, head_dim, rope, core
 
-    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                inplace: bool = False) -> torch.Tensor:
         T, H, KV, D = x.shape[0], self.heads, self.kv_heads, self.head_dim
         qg = self.q.forward(x)                                  # [T, H * 2 * D]: per head [query | gate]
         k, v = self.k.forward(x), self.v.forward(x)             # [T, KV * D]
@@ -270,7 +274,7 @@ class FullAttention:
                                                    v.view(T, KV, D)[a:b].transpose(0, 1).unsqueeze(0), is_causal=True, enable_gqa=True)
                 attn[a:b] = o[0].transpose(0, 1)
             gated = (attn * torch.sigmoid(q4[:, :, 1])).reshape(T, H * D)
-        return self.output.forward(gated, residual=residual)
+        return self.output.forward(gated, residual=residual, out=residual if inplace else None)
 
 
 class Layer:
@@ -280,9 +284,10 @@ class Layer:
     def __init__(self, input_norm: RmsNorm, mixer, post_norm: RmsNorm, mlp: Mlp):
         self.input_norm, self.mixer, self.post_norm, self.mlp = input_norm, mixer, post_norm, mlp
 
-    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor) -> torch.Tensor:
-        x = self.mixer.forward(self.input_norm(x), cu_seqlens_host, positions, residual=x)
-        return self.mlp.forward(self.post_norm(x), residual=x)
+    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, inplace: bool = False) -> torch.Tensor:
+        """`inplace`: update the residual stream `x` in memory (both adds become part of the projections' stores)."""
+        x = self.mixer.forward(self.input_norm(x), cu_seqlens_host, positions, residual=x, inplace=inplace)
+        return self.mlp.forward(self.post_norm(x), residual=x, inplace=inplace)
 
 
 class Decoder:
@@ -319,7 +324,7 @@ class Decoder:
         pos = positions.to(torch.int32).contiguous()
         states = []
         for layer in self.layers:
-            x = layer.forward(x, cu_seqlens_host, pos)
+            x = layer.forward(x, cu_seqlens_host, pos, inplace=True)  # x is this call's own buffer (the embedding rows)
             if collect:
                 states.append(x.clone())
         y = self.norm(x)
