@@ -80,7 +80,47 @@ def delta_rule():
                         cu_seqlens=np.cumsum([0] + lens).astype(np.int32), out=out.numpy())
 
 
+def layers():
+    """Attention (global and banded), norms, RoPE, causal GQA attention and one whole layer of each architecture:
+    small seeded inputs and the oracle's f32 outputs (all stored as float32; bf16-valued inputs are exact in it)."""
+    g = torch.Generator().manual_seed(1003)
+    out = {}
+    # ModernBERT attention, head dim 64, two sequences packed
+    lens = [150, 37]
+    T, H = sum(lens), 2
+    qkv = bf(torch.randn(T, 3, H, 64, generator=g))
+    qkv[:, 0] *= 2.0
+    out["attn/cu_seqlens"] = np.cumsum([0] + lens).astype(np.int32)
+    out["attn/qkv"] = qkv.numpy()
+    for name, window in (("global", -1), ("band", 64)):
+        o = torch.cat([oracle.attention(qkv[a:z, 0], qkv[a:z, 1], qkv[a:z, 2], window) for a, z in ((0, 150), (150, 187))])
+        out[f"attn/{name}"] = o.numpy()
+    # causal grouped-query attention with gate, head dim 256
+    Hq, KV, glens = 2, 1, [70, 20]
+    Tg = sum(glens)
+    qg = bf(torch.randn(Tg, Hq, 2, 256, generator=g))
+    kk, vv = bf(torch.randn(Tg, KV, 256, generator=g)), bf(torch.randn(Tg, KV, 256, generator=g))
+    o = torch.cat([oracle.causal_attention(qg[a:z, :, 0], kk[a:z], vv[a:z]).reshape(z - a, Hq * 256) *
+                   torch.sigmoid(qg[a:z, :, 1]).reshape(z - a, Hq * 256) for a, z in ((0, 70), (70, 90))])
+    out.update({"gqa/cu_seqlens": np.cumsum([0] + glens).astype(np.int32), "gqa/qg": qg.numpy(), "gqa/k": kk.numpy(),
+                "gqa/v": vv.numpy(), "gqa/out": o.numpy()})
+    # norms and rope
+    x = bf(torch.randn(33, 256, generator=g) * 2 + 0.3)
+    w, b = bf(1 + 0.2 * torch.randn(256, generator=g)), bf(0.1 * torch.randn(256, generator=g))
+    out.update({"norm/x": x.numpy(), "norm/w": w.numpy(), "norm/b": b.numpy(),
+                "norm/layer": oracle.layer_norm(x, w, 1e-5, dtype="bf16").numpy(),
+                "norm/layer_bias": oracle.layer_norm(x, w, 1e-5, dtype="bf16", bias=b).numpy(),
+                "norm/rms": oracle.rms_norm(x, w - 1, 1e-6, dtype="bf16").numpy()})
+    pos = torch.randint(0, 200, (33,), generator=g)
+    fr = torch.arange(200, dtype=torch.float32).unsqueeze(1) * torch.rand(32, generator=g).unsqueeze(0)
+    r = oracle.round_bf16(oracle.rope(x.view(33, 4, 64), fr.cos()[pos], fr.sin()[pos]))
+    out.update({"rope/pos": pos.numpy().astype(np.int32), "rope/cos": fr.cos().numpy(), "rope/sin": fr.sin().numpy(),
+                "rope/out": r.reshape(33, 256).numpy()})
+    np.savez_compressed(OUT / "layers.npz", **out)
+
+
 if __name__ == "__main__":
     projections()
     delta_rule()
+    layers()
     print("wrote", sorted(p.name for p in OUT.glob("*.npz")))

@@ -26,3 +26,9 @@ def load_projections():
 def load_delta_rule():
     raw = np.load(GOLDEN / "delta_rule.npz")
     return {k: torch.from_numpy(raw[k].copy()) for k in raw.files}
+
+
+def load_layers():
+    """{"group/name": tensor}: attention, causal GQA attention, norm and rope cases (float32; int32 index arrays)."""
+    raw = np.load(GOLDEN / "layers.npz")
+    return {k: torch.from_numpy(raw[k].copy()) for k in raw.files}

@@ -277,3 +277,16 @@ def test_qwen35_decoder_oracle_matches_transformers():
         want = model(input_ids=ids.unsqueeze(0)).last_hidden_state[0]
     got = oracle.decoder_forward(ids, w, cfg, dtype="f32")
     assert (got - want).abs().max() <= 1e-4 * float(want.abs().max())
+
+
+def test_layers_fixture_is_what_the_oracle_computes():
+    """tests/golden/layers.npz freezes oracle outputs for attention, causal GQA attention, norms and RoPE."""
+    from golden_io import load_layers
+    L = load_layers()
+    qkv, cu = L["attn/qkv"], L["attn/cu_seqlens"].tolist()
+    for name, window in (("global", -1), ("band", 64)):
+        got = torch.cat([oracle.attention(qkv[a:z, 0], qkv[a:z, 1], qkv[a:z, 2], window) for a, z in zip(cu[:-1], cu[1:])])
+        assert torch.allclose(got, L[f"attn/{name}"], atol=1e-6)
+    x, w, b = L["norm/x"], L["norm/w"], L["norm/b"]
+    assert torch.equal(oracle.layer_norm(x, w, 1e-5, dtype="bf16", bias=b), L["norm/layer_bias"])
+    assert torch.equal(oracle.rms_norm(x, w - 1, 1e-6, dtype="bf16"), L["norm/rms"])
