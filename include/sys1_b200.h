@@ -226,6 +226,9 @@ int s1_attention_gqa(s1_ctx* ctx, const void* q, long long ldq, long long q_head
  *                                                                    decision heads (src/models/laya.rs:85-86,258)
  *     kind 1  y = x / sqrt(mean(x^2) + eps) * (1 + weight)           the reference's `RmsNorm`
  *                                                                    (src/archs/qwen35_text.rs:178-203)
+ *     kind 2  y = x                                                  no normalisation (weight, bias, eps unused): with
+ *                                                                    `gather` the plain embedding lookup of the decoder
+ *                                                                    (`Decoder::embed`, src/archs/qwen35_text.rs:978-980)
  * x: [rows, width] with row stride ldx; weight: bf16 [width]; y: [rows, width] with row stride ldy (may be x).
  * With `gather` (DEVICE int32 [rows]) row r is read from x[gather[r]]: the embedding lookup fused with the
  * embedding norm (src/archs/modernbert.rs:1084-1092); `gather_rows` is the row count of x, and an index outside

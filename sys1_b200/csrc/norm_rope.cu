@@ -26,7 +26,7 @@ struct NormParams {
     const __nv_bfloat16* w;
     const __nv_bfloat16* b;  // optional bias (LayerNorm with bias: the heads' `layer_norm`, src/models/laya.rs:85-86,258)
     float eps;
-    int kind;  // 0 LayerNorm (mean removed), 1 RMSNorm with (1 + w)
+    int kind;  // 0 LayerNorm (mean removed), 1 RMSNorm with (1 + w), 2 no normalisation: rows copied (through the index)
     __nv_bfloat16* y;
     long long ldy;
     long long rows;
@@ -121,6 +121,10 @@ __global__ void __launch_bounds__(256) s1_norm_kernel(const NormParams p) {
     for (int i = 0; i < MAXCH; ++i) {
         const int c = sub + i * LPR;
         if (c < nchunks) {
+            if (p.kind == 2) {
+                *reinterpret_cast<uint4*>(dst + c * 8) = v[i];
+                continue;
+            }
             float f[8], g[8], bb[8];
             unpack8(v[i], f);
             unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + c * 8)), g);
@@ -161,6 +165,10 @@ __global__ void __launch_bounds__(256) s1_norm_wide_kernel(const NormParams p) {
     const float one = p.kind == 1 ? 1.f : 0.f;
     __nv_bfloat16* dst = p.y + row * p.ldy;
     for (int c = lane; c < nchunks; c += 32) {
+        if (p.kind == 2) {
+            *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(src + c * 8);
+            continue;
+        }
         float f[8], g[8], bb[8];
         unpack8(*reinterpret_cast<const uint4*>(src + c * 8), f);
         unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + c * 8)), g);
@@ -229,8 +237,8 @@ inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) =
 extern "C" int s1_norm(s1_ctx* ctx, const void* x, long long ldx, const int32_t* gather, int gather_rows, const void* weight,
                        const void* bias, float eps, int kind, void* y, long long ldy, long long rows, int width) {
     if (!ctx) return S1_EINVAL;
-    if (!x || !weight || !y) return s1_fail(ctx, S1_EINVAL, "s1_norm: null pointer");
-    if (kind != 0 && kind != 1) return s1_fail(ctx, S1_EINVAL, "s1_norm: kind must be 0 (LayerNorm) or 1 (RMSNorm)");
+    if (!x || !y || (!weight && kind != 2)) return s1_fail(ctx, S1_EINVAL, "s1_norm: null pointer");
+    if (kind < 0 || kind > 2) return s1_fail(ctx, S1_EINVAL, "s1_norm: kind must be 0 (LayerNorm), 1 (RMSNorm) or 2 (copy)");
     if (rows < 0 || width < 8 || (width % 8)) return s1_fail(ctx, S1_EINVAL, "s1_norm: width must be a multiple of 8");
     if ((ldx % 8) || (ldy % 8) || ldx < width || ldy < width || !al16(x) || !al16(y) || !al16(weight) || !al16(bias))
         return s1_fail(ctx, S1_EINVAL, "s1_norm: rows and weight must be 16-byte aligned, ld >= width");

@@ -9,7 +9,7 @@ import torch
 
 from . import device
 
-LAYER_NORM, RMS_NORM = 0, 1
+LAYER_NORM, RMS_NORM, COPY = 0, 1, 2
 
 
 def _rows(t: torch.Tensor, name: str) -> torch.Tensor:
@@ -28,7 +28,8 @@ def norm(x: torch.Tensor, weight: torch.Tensor, eps: float, kind: int = LAYER_NO
     width = x.shape[1]
     if gather is not None and (not gather.is_cuda or gather.dtype != torch.int32 or not gather.is_contiguous()):
         raise ValueError("gather must be a contiguous int32 CUDA vector")
-    if weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.numel() != width or not weight.is_contiguous():
+    if kind != COPY and (weight is None or weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.numel() != width
+                         or not weight.is_contiguous()):
         raise ValueError("weight must be a contiguous bf16 CUDA vector of the row width")
     if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_cuda or bias.numel() != width or not bias.is_contiguous()):
         raise ValueError("bias must be a contiguous bf16 CUDA vector of the row width")
@@ -39,7 +40,7 @@ def norm(x: torch.Tensor, weight: torch.Tensor, eps: float, kind: int = LAYER_NO
         return out
     ctx = device.load(x.device.index)
     rc = ctx._lib.s1_norm(ctx.handle, C.c_void_p(x.data_ptr()), x.stride(0), C.c_void_p(gather.data_ptr() if gather is not None else 0),
-                          x.shape[0] if gather is not None else 0, C.c_void_p(weight.data_ptr()),
+                          x.shape[0] if gather is not None else 0, C.c_void_p(weight.data_ptr() if weight is not None else 0),
                           C.c_void_p(bias.data_ptr() if bias is not None else 0), C.c_float(eps), int(kind),
                           C.c_void_p(out.data_ptr()), out.stride(0), rows, width)
     ctx.check(rc)
@@ -65,3 +66,9 @@ def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: torc
                           int(rotary_dim))
     ctx.check(rc)
     return x
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """`ids.apply(&embedding)` (src/archs/qwen35_text.rs:978-980): the rows `table[ids]` (ids int32 CUDA), through
+    `s1_norm` with kind 2 (rows copied through the index); an id outside the table is reported at the next sync."""
+    return norm(table, None, 0.0, COPY, gather=ids)

@@ -320,7 +320,7 @@ class Decoder:
         self.norm = RmsNorm(weights["norm"], cfg.rms_norm_eps)
 
     def forward(self, ids: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, collect: bool = False):
-        x = self.w["embed_tokens"][ids.long()]
+        x = _norm.embedding(self.w["embed_tokens"], ids.to(torch.int32).contiguous())
         pos = positions.to(torch.int32).contiguous()
         states = []
         for layer in self.layers:

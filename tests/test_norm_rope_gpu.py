@@ -77,7 +77,7 @@ def test_norm_rejects_bad_arguments(ctx):
     with pytest.raises(RuntimeError):
         norm.norm(x[:, :60], w[:60].contiguous(), 1e-5)  # width not a multiple of 8
     with pytest.raises(RuntimeError):
-        norm.norm(x, w, 1e-5, kind=2)
+        norm.norm(x, w, 1e-5, kind=3)
     assert norm.norm(x[:0], w, 1e-5).shape == (0, 64)
 
 
@@ -180,3 +180,12 @@ def test_layer_norm_with_bias_and_the_scorer_on_marker_rows(ctx):
     flat = torch.tensor([v for seq in got for v in seq])
     assert (flat - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max()))
     assert got[2][0] == got[2][1]  # the same marker twice gives the same logit
+
+
+def test_copy_kind_is_the_embedding_lookup(ctx):
+    g = torch.Generator().manual_seed(8)
+    table = torch.randn(500, 1024, generator=g).to(torch.bfloat16).to(DEV)
+    ids = torch.randint(0, 500, (300,), generator=g, dtype=torch.int32).to(DEV)
+    got = norm.embedding(table, ids)
+    ctx.sync()
+    assert torch.equal(got, table[ids.long()])
