@@ -5,15 +5,17 @@
 // output gate: out = bf16(a) * bf16(sigmoid(gate)) (:325-329, :408). The reference's eager path materialises
 // [128, L] score chunks with a -inf mask per chunk (:371-393); here scores never leave the chip.
 //
-// One CTA per (128-query block of one sequence, query head), 5 warps, one CTA per SM (208 KB shared memory):
-//   warp 4      : TMA loads (Q once: 4 column chunks of 64 dims; K and V tiles of 64 keys x 256 dims, each through
+// One CTA per (128-query block of one sequence, query head), 9 warps, one CTA per SM (208 KB shared memory):
+//   warp 8      : TMA loads (Q once: 4 column chunks of 64 dims; K and V tiles of 64 keys x 256 dims, each through
 //                 its own 2-stage ring) and the MMAs: S = Q K^T (M = 128, N = 64 keys, K = 256: 16 instructions)
 //                 and O += P V (M = 128, N = 4 x 64 dims, K = 64 keys: 16 instructions, V consumed as stored =
 //                 MN-major B operand); S (64 columns) and O (256 columns) live in TMEM
-//   warps 0..3  : thread = query row = TMEM lane: scores into registers in one go (which frees S for the next tile),
-//                 causal mask on the diagonal tiles only, row maximum, ex2 with the scale folded in, f32 row sum,
-//                 P rounded to bf16 into a swizzled A-operand tile; O is rescaled in TMEM only when a row maximum
-//                 has grown by more than 2^8 since the last rescale.
+//   warps 0..7  : two threads per query row (warps w and w + 4 read the same 32 TMEM lanes; one takes keys 0..31 of
+//                 a step, the other 32..63, and at the end dims 0..127 / 128..255 of the output): scores into
+//                 registers in one go (which frees S for the next tile), causal mask on the diagonal tiles only, the
+//                 pair agrees on the row maximum through two spare TMEM columns, ex2 with the scale folded in, f32
+//                 row sum, P rounded to bf16 into a swizzled A-operand tile; O is rescaled in TMEM only when a row
+//                 maximum has grown by more than 2^8 since the last rescale.
 // Key tiles past the diagonal of the query block are never loaded. Every mbarrier wait is bounded.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -83,7 +85,15 @@ __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(_
 
 constexpr float kRescaleLog2 = 8.f;
 
-__global__ void __launch_bounds__(160, 1)
+// Barrier of the two warps that share a quarter of the query rows (ids 1..4; 0 is __syncthreads).
+__device__ __forceinline__ void pair_barrier_gqa(int q4) {
+    if (q4 == 0) named_barrier<1, 64>();
+    else if (q4 == 1) named_barrier<2, 64>();
+    else if (q4 == 2) named_barrier<3, 64>();
+    else named_barrier<4, 64>();
+}
+
+__global__ void __launch_bounds__(288, 1)
 s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const GqaParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -94,7 +104,7 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     }
     const uint32_t sq = base, sk = base + kQBytes, sv = sk + 2 * kKVBytes, sp = sv + 2 * kKVBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + kQBytes + 4 * kKVBytes + kPBytes);
-    // bars: 0 Q full; 1,2 K full; 3,4 V full; 5 S ready; 6 S read (4 warps); 7 P ready (4 warps); 8 PV done
+    // bars: 0 Q full; 1,2 K full; 3,4 V full; 5 S ready; 6 S read (8 warps); 7 P ready (8 warps); 8 PV done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t b0 = smem_u32(bars);
@@ -114,8 +124,8 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         mbar_init(full_v, 1);
         mbar_init(full_v + 8, 1);
         mbar_init(bar_s, 1);
-        mbar_init(bar_sfree, 4);
-        mbar_init(bar_p, 4);
+        mbar_init(bar_sfree, 8);
+        mbar_init(bar_p, 8);
         mbar_init(bar_o, 1);
         *abort_flag = 0;
         fence_mbar_init();
@@ -123,17 +133,17 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
     }
-    if (warp == 4) {
+    if (warp == 8) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = *tmem_slot;  // columns 0..63: S, 64..319: O
+    const uint32_t tmem = *tmem_slot;  // columns 0..63: S, 64..319: O, 320..325: the row pairs' exchange
     int fail = 0;
 
-    if (warp == 4) {
+    if (warp == 8) {
         if (lane == 0) {
             const int xq = static_cast<int>(head * p.q_head_stride);
             const int xk = static_cast<int>(kv_head * p.k_head_stride), xv = static_cast<int>(kv_head * p.v_head_stride);
@@ -205,41 +215,49 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
         __syncwarp();
     } else {
-        const int row = threadIdx.x;
+        const int q4 = warp & 3, ch = warp >> 2;           // TMEM lane quarter; which 32 keys of a step / 128 output dims
+        const int row = q4 * 32 + lane;
         const bool q_ok = q_lo + row < qb.seq_len;
         const int qi = min(q_lo + row, qb.seq_len - 1);
-        const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        const uint32_t lane_addr = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
         const float c = p.scale_log2;
         const uint32_t prow = sp + static_cast<uint32_t>(row) * 128u, r7 = static_cast<uint32_t>(row) & 7u;
         float m_used = -INFINITY, l = 0.f;
 
         for (int i = 0; i < nkb; ++i) {
-            const int j0 = i * kKB;
+            const int j0 = i * kKB + ch * 32;              // first key of this thread's half of the step
             bool ok = mbar_wait(bar_s, i & 1, abort_flag);
             if (!__all_sync(0xffffffffu, ok)) { fail = 8; break; }
             tc_fence_after();
-            uint32_t s[64];
-            tmem_ld_32x32b_x32(lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_ld_32x32b_x32(lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+            uint32_t s[32];
+            tmem_ld_32x32b_x32(lane_addr + ch * 32, s);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sfree);
-            if (j0 + kKB - 1 > q_lo) {  // a tile that touches the diagonal of this query block
-                const int rel = qi - j0;  // keys 0 .. rel of the tile are visible
+            if (i * kKB + kKB - 1 > q_lo) {  // a tile that touches the diagonal of this query block
+                const int rel = qi - j0;     // keys 0 .. rel of this half are visible
 #pragma unroll
-                for (int e = 0; e < 64; ++e)
+                for (int e = 0; e < 32; ++e)
                     if (e > rel) s[e] = 0xff800000u;  // -inf
             }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < 64; e += 8) {
+            for (int e = 0; e < 32; e += 4) {
                 mx0 = max3(mx0, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
                 mx1 = max3(mx1, __uint_as_float(s[e + 2]), __uint_as_float(s[e + 3]));
-                mx2 = max3(mx2, __uint_as_float(s[e + 4]), __uint_as_float(s[e + 5]));
-                mx3 = max3(mx3, __uint_as_float(s[e + 6]), __uint_as_float(s[e + 7]));
             }
-            const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+            const float mx_own = fmaxf(mx0, mx1);
+            // the other half's maximum, through two spare TMEM columns (double-buffered by step parity)
+            const uint32_t xcol = lane_addr + 320 + 2 * (i & 1);
+            tmem_st_32x32b_x1(xcol + ch, __float_as_uint(mx_own));
+            tmem_st_wait();
+            tc_fence_before();
+            pair_barrier_gqa(q4);
+            tc_fence_after();
+            const float mx_other = __uint_as_float(tmem_ld_32x32b_x1(xcol + (ch ^ 1)));
+            tmem_ld_wait();
+            const float m_new = fmaxf(m_used, fmaxf(mx_own, mx_other));
             float alpha = 1.f;
             bool rescale = false;
             if (i == 0) {
@@ -252,10 +270,10 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                 }
             }
             const float neg_mc = (m_used == -INFINITY) ? 0.f : -m_used * c;
-            uint32_t pk[32];
+            uint32_t pk[16];
             float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-            for (int e = 0; e < 64; e += 2) {
+            for (int e = 0; e < 32; e += 2) {
                 const float p0 = ex2f(fmaf(__uint_as_float(s[e]), c, neg_mc));
                 const float p1 = ex2f(fmaf(__uint_as_float(s[e + 1]), c, neg_mc));
                 sum0 += p0;
@@ -267,22 +285,22 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                 ok = mbar_wait(bar_o, (i - 1) & 1, abort_flag);
                 if (!__all_sync(0xffffffffu, ok)) { fail = 9; break; }
                 tc_fence_after();
-                if (rescale) {
+                if (rescale) {  // this thread's 128 of the row's 256 output dims
 #pragma unroll 1
-                    for (int ch = 0; ch < 8; ++ch) {
+                    for (int k4 = 0; k4 < 4; ++k4) {
                         uint32_t o[32];
-                        tmem_ld_32x32b_x32(lane_addr + 64 + ch * 32, o);
+                        tmem_ld_32x32b_x32(lane_addr + 64 + ch * 128 + k4 * 32, o);
                         tmem_ld_wait();
 #pragma unroll
                         for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-                        tmem_st_32x32b_x32(lane_addr + 64 + ch * 32, o);
+                        tmem_st_32x32b_x32(lane_addr + 64 + ch * 128 + k4 * 32, o);
                     }
                     tmem_st_wait();
                 }
             }
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {  // 8 keys (16 bytes) per store
-                const uint32_t addr = prow + ((static_cast<uint32_t>(t) ^ r7) << 4);
+            for (int t = 0; t < 4; ++t) {  // 8 keys (16 bytes) per store: chunks ch * 4 .. ch * 4 + 3 of the row
+                const uint32_t addr = prow + ((static_cast<uint32_t>(ch * 4 + t) ^ r7) << 4);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * t]), "r"(pk[4 * t + 1]),
                              "r"(pk[4 * t + 2]), "r"(pk[4 * t + 3]) : "memory");
             }
@@ -297,14 +315,22 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
         if (!fail) {
             tc_fence_after();
-            const float inv = 1.f / l;
+            tmem_st_32x32b_x1(lane_addr + 324 + ch, __float_as_uint(l));  // the row sum is the two halves' sums, in a fixed order
+            tmem_st_wait();
+            tc_fence_before();
+            pair_barrier_gqa(q4);
+            tc_fence_after();
+            const float l0 = ch == 0 ? l : __uint_as_float(tmem_ld_32x32b_x1(lane_addr + 324));
+            const float l1 = ch == 1 ? l : __uint_as_float(tmem_ld_32x32b_x1(lane_addr + 325));
+            tmem_ld_wait();
+            const float inv = 1.f / (l0 + l1);
             const long long tok = static_cast<long long>(qb.seq_start + qi);
-            __nv_bfloat16* orow = p.out + tok * p.ldo + head * kD;
-            const __nv_bfloat16* grow = p.gate ? p.gate + tok * p.ldg + head * p.gate_head_stride : nullptr;
+            __nv_bfloat16* orow = p.out + tok * p.ldo + head * kD + ch * 128;
+            const __nv_bfloat16* grow = p.gate ? p.gate + tok * p.ldg + head * p.gate_head_stride + ch * 128 : nullptr;
 #pragma unroll 1
-            for (int ch = 0; ch < 8; ++ch) {
+            for (int k4 = 0; k4 < 4; ++k4) {
                 uint32_t o[32];
-                tmem_ld_32x32b_x32(lane_addr + 64 + ch * 32, o);
+                tmem_ld_32x32b_x32(lane_addr + 64 + ch * 128 + k4 * 32, o);
                 tmem_ld_wait();
                 if (q_ok) {
 #pragma unroll
@@ -313,7 +339,7 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 #pragma unroll
                         for (int u = 0; u < 8; ++u) f[u] = __uint_as_float(o[8 * e + u]) * inv;
                         if (grow) {  // bf16(a) * bf16(sigmoid(gate)), rounded again: the reference's tensor ops, one by one
-                            const uint4 graw = *reinterpret_cast<const uint4*>(grow + ch * 32 + 8 * e);
+                            const uint4 graw = *reinterpret_cast<const uint4*>(grow + k4 * 32 + 8 * e);
                             const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(&graw);
 #pragma unroll
                             for (int u = 0; u < 8; ++u) {
@@ -326,7 +352,7 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                         v.y = pack2(f[2], f[3]);
                         v.z = pack2(f[4], f[5]);
                         v.w = pack2(f[6], f[7]);
-                        *reinterpret_cast<uint4*>(orow + ch * 32 + 8 * e) = v;
+                        *reinterpret_cast<uint4*>(orow + k4 * 32 + 8 * e) = v;
                     }
                 }
             }
@@ -342,7 +368,7 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     if (*abort_flag) __nanosleep(200000);
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
@@ -420,7 +446,7 @@ extern "C" int s1_attention_gqa(s1_ctx* ctx, const void* q, long long ldq, long 
         S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_attention_gqa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGqaSmem));
         configured_device = ctx->device;
     }
-    s1_attention_gqa_kernel<<<dim3(nb, heads), 160, kGqaSmem, ctx->stream>>>(tq, tk, tv, gp);
+    s1_attention_gqa_kernel<<<dim3(nb, heads), 288, kGqaSmem, ctx->stream>>>(tq, tk, tv, gp);
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return S1_OK;
