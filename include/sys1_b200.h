@@ -34,7 +34,8 @@ enum {
     S1_EDEVICE = -3,  /* not an sm_100 device, or no device */
     S1_EKERNEL = -4,  /* a kernel recorded an error status (bounded wait ran out) */
     S1_ENOMEM = -5,
-    S1_ELIMIT = -6    /* s1_linear_static only: the problem is larger than that entry point supports */
+    S1_ELIMIT = -6,   /* s1_linear_static only: the problem is larger than that entry point supports */
+    S1_ETIMEOUT = -7  /* a host-side deadline passed (s1_comm_init: a rank never joined) */
 };
 
 /* Epilogue fused behind the contraction. */
@@ -63,12 +64,22 @@ int s1_device_count(int* out);
 long long s1_launch_count(const s1_ctx* ctx);
 /* Tuning knobs: "gemm_bn" = 0 (auto), 512 / 384 (CTA-pair 256x256 / 256x192 tiles), 256 or 128 (single-CTA 128xBN tiles);
  * "gemm_sms" = how many SMs the projections' persistent grids may occupy (0 = all; e.g. 132 leaves 16 SMs to the
- * all-reduce of the previous slab in a tensor-parallel layer); "comm_ctas" = how many blocks the collective may use
+ * exchange of the previous slab in a tensor-parallel layer); "comm_ctas" = how many blocks the collective may use
  * (0 = NCCL's default; takes effect at s1_comm_init); "pdl" = 1 (default) launches the projections with
  * programmatic stream serialization, so that a projection's set-up overlaps the tail of the kernel before it, 0 turns
- * that off; "debug" = measurement aids of the GEMM epilogue
- * (0 in production). */
+ * that off; "wait_limit_cycles" = SM clock cycles a single wait inside a projection kernel may last before the kernel
+ * gives up and s1_sync reports S1_EKERNEL (default 2e9, about a second); "comm_timeout_ms" = how long s1_comm_init
+ * waits for the other ranks before it gives up with S1_ETIMEOUT (default 120000; 0 = for ever). */
 int s1_set_option(s1_ctx* ctx, const char* name, long long value);
+
+/*
+ * Failure-detection self test. Launches a one-block kernel whose only wait can never be satisfied (nothing is in
+ * flight and nothing ever arrives on its barrier), so the bounded wait every kernel of this library goes through runs
+ * out after "wait_limit_cycles", the kernel records its status and returns by itself; the next `s1_sync` then reports
+ * S1_EKERNEL and the context stays usable. Set "wait_limit_cycles" to a few million first, or the call takes about a
+ * second. It has no counterpart in the reference, whose failure handling is host-side only (src/batching.rs:252-281).
+ */
+int s1_selftest_bounded_wait(s1_ctx* ctx);
 
 /*
  * One projection of the reference: a candle `Linear` (weight [N, K] as `vb.get((output, input), "weight")`
@@ -118,6 +129,7 @@ int s1_linear(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, long long l
  * recorded an error; with `wait` == 0 the call is asynchronous and a kernel-side error goes unreported.
  * `err` / `err_len`: optional buffer that receives the message of a failing call.
  * Limits: T <= S1_STATIC_MAX_TOKENS, N and K <= S1_STATIC_MAX_FEATURES; beyond them the call returns S1_ELIMIT.
+ * The call makes `device_ordinal` current while it runs and puts the caller's current device back before it returns.
  * The first call on a GPU looks up the array's device address and sets kernel attributes: make that first call
  * outside any stream capture. Every call shares the one array (each call clears the status words it needs
  * zeroed), so calls whose kernels may overlap on the GPU - other streams, other threads - race on it: keep the
@@ -164,6 +176,7 @@ int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const flo
  *                   the sum and each product rounded to bf16 tap by tap as in src/kernels/qwen35.cu:3-29
  *                   (CPU form src/archs/qwen35_text.rs:632-650). `positions` (DEVICE int32 [T], index of each token
  *                   inside its own sequence, from s1_pack_batch) gives the zero left padding per sequence.
+ *                   y must not overlap x (S1_EINVAL): a token reads the rows before it.
  *  s1_delta_inputs  `delta_inputs` (src/archs/qwen35_text.rs:528-579): split mixed = [q | k | v], repeat the key
  *                   heads over the value heads, q = l2norm(q) / sqrt(128), k = l2norm(k) (1e-6 inside the root),
  *                   beta = sigmoid(b), g = softplus(a + dt_bias) * neg_exp_a; outputs f32 [T, Hv, 128] / [T, Hv].
@@ -248,10 +261,28 @@ int s1_norm(s1_ctx* ctx, const void* x, long long ldx, const int32_t* gather, in
  * s1_sync as S1_EKERNEL (that token is left unrotated). Replaces `rope_qkv` (src/kernels/modernbert.cu:31-62,
  * called from `RotaryEmbedding::apply_qkv`): on the packed Wqkv output [T, 3 * H * D] call it with heads = 2 * H
  * (q and k lie side by side); v stays where it is and s1_attention reads the three column blocks in place.
- * Also `Attention::rotary` of src/archs/qwen35_text.rs:296-310 (rotary_dim < head_dim).
+ * Also `Attention::rotary` of src/archs/qwen35_text.rs:296-310 (rotary_dim < head_dim) with the products and the sum
+ * formed in f32 and rounded once, which is the arithmetic of the ModernBERT kernel; s1_head_norm_rope offers the
+ * per-operation bf16 rounding candle applies on that path.
  */
 int s1_rope(s1_ctx* ctx, void* x, long long ldx, const float* cos_table, const float* sin_table, const int32_t* positions,
             int max_positions, int total_tokens, int heads, long long head_stride, int rotary_dim);
+
+/*
+ * Per-head RMSNorm followed by the partial rotary embedding, in place, one pass: `q_norm` / `k_norm` and
+ * `Attention::rotary` of the reference's `FullAttention::forward` (src/archs/qwen35_text.rs:296-339):
+ *     y = bf16(x / sqrt(mean(x^2) + eps) * (1 + norm_weight))   over the head_dim columns of each (token, head)
+ *     then the rotate-half rotation of s1_rope on the first rotary_dim columns of y.
+ * x: bf16, head h of token t at x + t * ldx + h * head_stride (the query halves of the interleaved q_proj output with
+ * head_stride = 2 * head_dim, or the k_proj output with head_stride = head_dim). head_dim 64, 128 or 256; rotary_dim
+ * 16, 32, 64, 128 or 256 (<= head_dim). Tables and positions as for s1_rope.
+ * bf16_ops != 0: the rotation rounds as candle's bf16 tensor ops do - each product and the sum is a bf16 value
+ * (x * cos, rotate_half(x) * sin, their sum: three roundings, :302); bf16_ops = 0: products and sum in f32, one
+ * rounding, bit-identical to s1_norm followed by s1_rope.
+ */
+int s1_head_norm_rope(s1_ctx* ctx, void* x, long long ldx, long long head_stride, int heads, int head_dim,
+                      const void* norm_weight, float eps, const float* cos_table, const float* sin_table,
+                      const int32_t* positions, int max_positions, int rotary_dim, int total_tokens, int bf16_ops);
 
 /*
  * Tensor parallelism: the sum over ranks that follows a row-parallel projection (each rank holds a K range of the

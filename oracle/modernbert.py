@@ -103,6 +103,54 @@ def encoder_forward(ids: torch.Tensor, w: Dict[str, torch.Tensor], cfg: EncoderC
     return (y, states) if collect else y
 
 
+def local_attention_mask(length: int, max_distance: int) -> torch.Tensor:
+    """`local_attention_mask` (src/archs/modernbert.rs:1058-1076): `[L, L]`, -10000 where |i - j| > max_distance, else 0."""
+    idx = torch.arange(length)
+    return torch.where((idx.unsqueeze(0) - idx.unsqueeze(1)).abs() > max_distance, MASK_VALUE, 0.0)
+
+
+def global_attention_mask(keep: torch.Tensor, target_length: int) -> torch.Tensor:
+    """`global_attention_mask` (src/archs/modernbert.rs:1048-1056): `keep [B, S]` (1 = token, 0 = padding) ->
+    `[B, 1, target_length, S]` with -10000 on the padded keys."""
+    b, s = keep.shape
+    return (1.0 - keep.to(torch.float32).reshape(b, 1, 1, s).expand(b, 1, target_length, s)) * MASK_VALUE
+
+
+def attention_softmax(scores: torch.Tensor, dtype: str = "f32") -> torch.Tensor:
+    """`attention_softmax` (src/archs/modernbert.rs:393-399): half-precision scores are widened to f32 for the
+    softmax and the probabilities rounded back."""
+    p = torch.softmax(scores.to(torch.float32), dim=-1)
+    return round_bf16(p) if dtype == "bf16" else p
+
+
+def eager_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask=None, dtype: str = "f32") -> torch.Tensor:
+    """`eager_attention` (src/archs/modernbert.rs:337-351) in the reference's own layout: q, k, v `[B, H, L, D]`,
+    additive `mask` broadcastable to `[B, H, L, S]`; returns `[B, H, L, D]`."""
+    r = (lambda t: round_bf16(t)) if dtype == "bf16" else (lambda t: t)
+    scores = r(r(q.float() * scale) @ k.float().transpose(-2, -1))
+    if mask is not None:
+        scores = r(scores + mask)
+    return r(attention_softmax(scores, dtype) @ v.float())
+
+
+def windowed_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask, window: int, dtype: str = "f32") -> torch.Tensor:
+    """`cpu_windowed_attention` (src/archs/modernbert.rs:353-391): query blocks of ceil(window / 2) rows, each against
+    the keys within `window` of the block, the matching part of the mask cut out; short inputs take the dense path."""
+    length = q.shape[2]
+    if length <= window + window // 4:
+        return eager_attention(q, k, v, scale, mask, dtype)
+    block = max((window + 1) // 2, 1)
+    outs = []
+    for qs in range(0, length, block):
+        ql = min(block, length - qs)
+        ks, ke = max(qs - window, 0), min(qs + ql + window, length)
+        m = None
+        if mask is not None:
+            m = mask[qs:qs + ql, ks:ke].reshape(1, 1, ql, ke - ks) if mask.dim() == 2 else mask[:, :, qs:qs + ql, ks:ke]
+        outs.append(eager_attention(q[:, :, qs:qs + ql], k[:, :, ks:ke], v[:, :, ks:ke], scale, m, dtype))
+    return torch.cat(outs, dim=2)
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int = -1, dtype: str = "f32") -> torch.Tensor:
     """`eager_attention` with the local mask (src/archs/modernbert.rs:337-351, :1058-1076) for one unpadded sequence:
     q, k, v `[L, H, D]` -> `[L, H * D]`; keys with |i - j| > window get -10000 added (window < 0: no mask)."""

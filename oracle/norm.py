@@ -38,12 +38,18 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: str = "f3
     return round_bf16(y) if dtype == "bf16" else y
 
 
-def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int = -1) -> torch.Tensor:
-    """Rotate-half on `[L, H, D]` with tables `[L, rotary_dim / 2]`; columns past `rotary_dim` pass through."""
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int = -1, bf16_ops: bool = False) -> torch.Tensor:
+    """Rotate-half on `[L, H, D]` with tables `[L, rotary_dim / 2]`; columns past `rotary_dim` pass through.
+    `bf16_ops`: the Qwen3.5 path evaluates `x * cos + rotate_half(x) * sin` with bf16 tensor ops
+    (src/archs/qwen35_text.rs:296-310), so each product and the sum is rounded to bf16 (three roundings); without it
+    the products and the sum are f32 (the ModernBERT kernel, src/kernels/modernbert.cu:48-57) and the caller rounds."""
     d = x.shape[-1] if rotary_dim < 0 else rotary_dim
     h = d // 2
     x1, x2 = x[..., :h], x[..., h:d]
     c, s = cos.unsqueeze(1), sin.unsqueeze(1)
+    if bf16_ops:
+        r = round_bf16
+        return torch.cat([r(r(x1 * c) + r(-x2 * s)), r(r(x2 * c) + r(x1 * s)), x[..., d:]], dim=-1)
     return torch.cat([x1 * c - x2 * s, x1 * s + x2 * c, x[..., d:]], dim=-1)
 
 

@@ -120,10 +120,10 @@ def full_attention(x: torch.Tensor, w: Dict[str, torch.Tensor], p: str, cfg: Dec
     H, KV, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     cos, sin = rope_tables(cfg, L, dtype)
     qg = linear(x, w[p + "q_proj"], dtype=dtype).reshape(L, H, 2, D)
-    q = r(rope(rms_norm(qg[:, :, 0], w[p + "q_norm"], cfg.rms_norm_eps, dtype), cos, sin, cfg.rotary_dim))
+    q = r(rope(rms_norm(qg[:, :, 0], w[p + "q_norm"], cfg.rms_norm_eps, dtype), cos, sin, cfg.rotary_dim, bf16_ops=dtype == "bf16"))
     gate = r(torch.sigmoid(qg[:, :, 1])).reshape(L, H * D)
     k = r(rope(rms_norm(linear(x, w[p + "k_proj"], dtype=dtype).reshape(L, KV, D), w[p + "k_norm"], cfg.rms_norm_eps, dtype),
-               cos, sin, cfg.rotary_dim))
+               cos, sin, cfg.rotary_dim, bf16_ops=dtype == "bf16"))
     v = linear(x, w[p + "v_proj"], dtype=dtype).reshape(L, KV, D)
     attn = causal_attention(q, k, v, dtype).reshape(L, H * D)
     return linear(r(attn * gate), w[p + "o_proj"], dtype=dtype)

@@ -13,13 +13,13 @@ PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "libsys1_b200.so"
 
 S1_OK = 0
-S1_EINVAL, S1_ECUDA, S1_EDEVICE, S1_EKERNEL, S1_ENOMEM, S1_ELIMIT = -1, -2, -3, -4, -5, -6
+S1_EINVAL, S1_ECUDA, S1_EDEVICE, S1_EKERNEL, S1_ENOMEM, S1_ELIMIT, S1_ETIMEOUT = -1, -2, -3, -4, -5, -6, -7
 STATIC_MAX_TOKENS, STATIC_MAX_FEATURES = 262144, 32768
 COMM_ID_BYTES = 128
 EPI_NONE, EPI_GEGLU, EPI_SWIGLU = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
 
-_ERR_NAMES = {-1: "S1_EINVAL", -2: "S1_ECUDA", -3: "S1_EDEVICE", -4: "S1_EKERNEL", -5: "S1_ENOMEM", -6: "S1_ELIMIT"}
+_ERR_NAMES = {-1: "S1_EINVAL", -2: "S1_ECUDA", -3: "S1_EDEVICE", -4: "S1_EKERNEL", -5: "S1_ENOMEM", -6: "S1_ELIMIT", -7: "S1_ETIMEOUT"}
 
 
 class S1Error(RuntimeError):
@@ -83,6 +83,9 @@ SIGNATURES = {
                           C.c_longlong, C.c_longlong, C.c_int]),
     "s1_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                           C.c_longlong, C.c_int]),
+    "s1_selftest_bounded_wait": (C.c_int, [C.c_void_p]),
+    "s1_head_norm_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_float,
+                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]),
     "s1_linear_rope": (C.c_int, [C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_int,
                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "s1_linear": (C.c_int, [C.c_void_p, C.POINTER(LinearDesc), C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,

@@ -20,6 +20,7 @@ ROOT = PKG.parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libsys1_b200.so"
 STAMP = PKG / "csrc" / ".build_stamp"
+OBJ = PKG / "csrc" / ".obj"
 
 SOURCES = ["api.cu", "linear_static.cu", "batching.cu", "delta_rule.cu", "delta_chunked.cu", "delta_io.cu", "attention.cu", "attention_gqa.cu", "norm_rope.cu", "comm.cu"]
 NVCC_FLAGS = [
@@ -38,33 +39,64 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found; the native library cannot be built")
 
 
-def _fingerprint() -> str:
+def _deps_digest() -> str:
+    """Digest of everything every translation unit may include (headers) and of this script."""
     h = hashlib.sha256()
-    for f in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) +
-                    [ROOT / "include" / "sys1_b200.h", Path(__file__)]):
+    for f in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [ROOT / "include" / "sys1_b200.h", Path(__file__)]):
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()
+
+
+def _fingerprint() -> str:
+    h = hashlib.sha256(_deps_digest().encode())
+    for f in sorted(CSRC.glob("*.cu")):
         h.update(f.name.encode())
         h.update(f.read_bytes())
     return h.hexdigest()
 
 
 def build(verbose: bool = False, force: bool = False) -> Path:
-    """Compile the library if sources changed since the last build; returns the path of the .so."""
+    """Compile the library if sources changed since the last build; returns the path of the .so. Each `.cu` file is
+    compiled to an object of its own (in parallel, and only if it or a header changed), then the objects are linked."""
+    from concurrent.futures import ThreadPoolExecutor
     fp = _fingerprint()
     if not force and LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == fp:
         return LIB
-    srcs = [str(CSRC / s) for s in SOURCES if (CSRC / s).exists()]
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(ROOT / "include"), "-o", str(LIB), *srcs, "-lcudart", "-ldl"]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(res.stdout + res.stderr)
+    nvcc = _nvcc()
+    OBJ.mkdir(exist_ok=True)
+    deps = _deps_digest()
+    flags = [f for f in NVCC_FLAGS if f != "-shared"]
+
+    def compile_one(name: str):
+        src, obj, tag = CSRC / name, OBJ / (name + ".o"), OBJ / (name + ".stamp")
+        want = hashlib.sha256(deps.encode() + src.read_bytes()).hexdigest()
+        if not force and obj.exists() and tag.exists() and tag.read_text() == want:
+            return name, 0, ""
+        cmd = [nvcc, *flags, *(["-Xptxas", "-v"] if verbose else []), "-I", str(ROOT / "include"), "-c", str(src), "-o", str(obj)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode == 0:
+            tag.write_text(want)
+        return name, res.returncode, res.stdout + res.stderr
+
+    names = [s for s in SOURCES if (CSRC / s).exists()]
+    with ThreadPoolExecutor(max_workers=min(len(names), os.cpu_count() or 4)) as pool:
+        results = list(pool.map(compile_one, names))
+    failed = [n for n, rc, _ in results if rc != 0]
+    for n, rc, log in results:
+        if log and (verbose or rc != 0):
+            sys.stderr.write(f"--- {n}\n{log}")
+    if failed:
+        raise RuntimeError(f"nvcc failed on {failed}")
+    link = [nvcc, "-shared", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB),
+            *(str(OBJ / (n + ".o")) for n in names), "-lcudart", "-ldl"]
+    res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed building libsys1_b200.so")
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("linking libsys1_b200.so failed")
     STAMP.write_text(fp)
     return LIB
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, force=True))
+    print(build(verbose="-v" in sys.argv, force="--force" in sys.argv or "-v" in sys.argv))

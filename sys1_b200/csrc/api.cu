@@ -92,10 +92,22 @@ extern "C" int s1_set_option(s1_ctx* ctx, const char* name, long long value) {
         ctx->opt_pdl = value != 0;
         return S1_OK;
     }
+    if (strcmp(name, "wait_limit_cycles") == 0) {  // longest single wait inside a projection kernel, in SM clock cycles
+        if (value < 1000) return s1_fail(ctx, S1_EINVAL, "wait_limit_cycles must be at least 1000 (got %lld)", value);
+        ctx->opt_wait_limit = value;
+        return S1_OK;
+    }
+    if (strcmp(name, "comm_timeout_ms") == 0) {  // deadline of s1_comm_init (0 = wait for ever); set before s1_comm_init
+        if (value < 0) return s1_fail(ctx, S1_EINVAL, "comm_timeout_ms must not be negative (got %lld)", value);
+        ctx->opt_comm_timeout_ms = value;
+        return S1_OK;
+    }
+#ifdef S1_MEASURE
     if (strcmp(name, "debug") == 0) {
         ctx->opt_debug = static_cast<int>(value);
         return S1_OK;
     }
+#endif
     return s1_fail(ctx, S1_EINVAL, "unknown option '%s'", name);
 }
 
@@ -113,6 +125,39 @@ extern "C" int s1_sync(s1_ctx* ctx) {
         return s1_fail(ctx, S1_EKERNEL, "kernel gave up on a bounded wait: code %d block %d role %d tile %d", st[0],
                        st[1], st[2], st[3]);
     }
+    return S1_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- bounded-wait self test
+namespace {
+// One block whose only wait can never be satisfied: nothing (no copy, no MMA, no other thread) ever arrives on the
+// barrier, so the bounded wait every kernel of this library uses runs out after `limit` cycles, the thread records the
+// status the way the projection kernels do, and the kernel returns by itself.
+__global__ void s1_wait_probe_kernel(int* status, long long limit) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, limit);
+    if (!ok && atomicCAS(status, 0, 1) == 0) {
+        status[1] = static_cast<int>(blockIdx.x);
+        status[2] = 99;  // role: the self test
+        status[3] = -1;
+    }
+}
+}  // namespace
+
+extern "C" int s1_selftest_bounded_wait(s1_ctx* ctx) {
+    if (!ctx) return S1_EINVAL;
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    s1_wait_probe_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status_dev, ctx->opt_wait_limit);
+    S1_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 1;
     return S1_OK;
 }
 
@@ -257,14 +302,17 @@ static int linear_impl(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, lo
         return (n_out + w - 1) / w;
     };
 
-    GemmParams p;
+    GemmParams p{};
     p.M = T;
     p.n_out = n_out;
     p.K = lin->K;
     p.tiles_m = tiles_m;
     p.tiles_n = n_tiles_for(bn);
     p.act = lin->act;
+    p.wait_limit = ctx->opt_wait_limit;
+#ifdef S1_MEASURE
     p.debug = ctx->opt_debug;
+#endif
     p.ldr = ldr;
     p.residual = static_cast<const __nv_bfloat16*>(residual);
     p.bias = static_cast<const __nv_bfloat16*>(lin->bias);

@@ -378,6 +378,7 @@ extern "C" int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const voi
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out) |
          reinterpret_cast<uintptr_t>(workspace)) & 15u)
         return s1_fail(ctx, S1_EINVAL, "s1_attention: pointers must be 16-byte aligned");
+    if (!(scale > 0.f) || !(scale < 1e30f)) return s1_fail(ctx, S1_EINVAL, "s1_attention: scale must be positive and finite");
     if (workspace_bytes < s1_attention_workspace(num_seqs, total_tokens))
         return s1_fail(ctx, S1_EINVAL, "s1_attention: workspace of %zu bytes, %zu needed", workspace_bytes,
                        s1_attention_workspace(num_seqs, total_tokens));

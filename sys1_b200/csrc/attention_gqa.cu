@@ -400,6 +400,7 @@ extern "C" int s1_attention_gqa(s1_ctx* ctx, const void* q, long long ldq, long 
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out) |
          reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(workspace)) & 15u)
         return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: pointers must be 16-byte aligned");
+    if (!(scale > 0.f) || !(scale < 1e30f)) return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: scale must be positive and finite");
     if (workspace_bytes < s1_attention_gqa_workspace(num_seqs, total_tokens))
         return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: workspace of %zu bytes, %zu needed", workspace_bytes,
                        s1_attention_gqa_workspace(num_seqs, total_tokens));

@@ -14,38 +14,30 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "sys1_b200.h"
 #include "context.h"
+#include "comm_init.h"
 
 namespace {
 
-struct NcclApi {
-    void* handle = nullptr;
-    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
-    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
-    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;  // optional
-    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
-    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
-    const char* (*GetErrorString)(ncclResult_t) = nullptr;
-    const char* why = nullptr;
-};
+using s1::NcclApi;
 
-NcclApi* nccl_api() {
-    static NcclApi api;
-    static bool tried = false;
-    if (tried) return &api;
-    tried = true;
+void load_nccl(NcclApi& api) {
     for (const char* name : {"libnccl.so.2", "libnccl.so"}) {
         api.handle = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
         if (api.handle) break;
     }
     if (!api.handle) {
         api.why = "libnccl.so.2 not found";
-        return &api;
+        return;
     }
     api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
     api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
     api.CommInitRankConfig = reinterpret_cast<decltype(api.CommInitRankConfig)>(dlsym(api.handle, "ncclCommInitRankConfig"));
+    api.CommGetAsyncError = reinterpret_cast<decltype(api.CommGetAsyncError)>(dlsym(api.handle, "ncclCommGetAsyncError"));
+    api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(dlsym(api.handle, "ncclCommAbort"));
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
     api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
@@ -53,6 +45,12 @@ NcclApi* nccl_api() {
         api.why = "libnccl.so.2 lacks an expected symbol";
         api.handle = nullptr;
     }
+}
+
+NcclApi* nccl_api() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] { load_nccl(api); });
     return &api;
 }
 
@@ -93,16 +91,13 @@ extern "C" int s1_comm_init(s1_ctx* ctx, const void* id, int rank, int size) {
     ncclUniqueId uid;
     memcpy(&uid, id, sizeof(uid));
     ncclComm_t comm = nullptr;
-    ncclResult_t rc;
-    if (ctx->opt_comm_ctas > 0 && api->CommInitRankConfig) {
-        // a bounded number of blocks for the collective, so that it fits on the SMs the projections leave free ("gemm_sms")
-        ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
-        config.maxCTAs = ctx->opt_comm_ctas;
-        rc = api->CommInitRankConfig(&comm, size, uid, rank, &config);
-    } else {
-        rc = api->CommInitRank(&comm, size, uid, rank);
-    }
-    if (rc != ncclSuccess) return s1_fail(ctx, S1_ECUDA, "ncclCommInitRank failed: %s", api->GetErrorString(rc));
+    bool blocking = true;
+    // a bounded number of blocks for the collective ("comm_ctas"), so that it fits on the SMs the projections leave
+    // free ("gemm_sms"); a deadline ("comm_timeout_ms") so that a rank that never joins does not block this one for ever
+    const int st = s1::comm_init_with_deadline(*api, uid, rank, size, ctx->opt_comm_ctas, ctx->opt_comm_timeout_ms, &comm,
+                                               &blocking, ctx->err, sizeof(ctx->err));
+    if (st != S1_OK) return st;
+    ctx->comm_blocking = blocking;
     int prio_low = 0, prio_high = 0;  // the collective's blocks go first when SMs free up
     cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high);
     cudaError_t e = cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, prio_high);
@@ -144,7 +139,14 @@ extern "C" int s1_allreduce_bf16(s1_ctx* ctx, void* buf, size_t count) {
     S1_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->comm_ready, 0));
     NcclApi* api = nccl_api();
     const ncclResult_t rc = api->AllReduce(buf, buf, count, ncclBfloat16, ncclSum, static_cast<ncclComm_t>(ctx->comm), ctx->comm_stream);
-    if (rc != ncclSuccess) return s1_fail(ctx, S1_ECUDA, "ncclAllReduce failed: %s", api->GetErrorString(rc));
+    if (rc == ncclInProgress && !ctx->comm_blocking) {
+        // a communicator created with a deadline is non-blocking: the call is on the stream once its state says so
+        char why[160] = {0};
+        const int st = s1::comm_wait_enqueued(*api, static_cast<ncclComm_t>(ctx->comm), ctx->opt_comm_timeout_ms, why, sizeof(why));
+        if (st != S1_OK) return s1_fail(ctx, st, "ncclAllReduce: %s", why);
+    } else if (rc != ncclSuccess) {
+        return s1_fail(ctx, S1_ECUDA, "ncclAllReduce failed: %s", api->GetErrorString(rc));
+    }
     S1_CUDA_OK(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
     ctx->comm_pending = true;
     return S1_OK;

@@ -42,7 +42,9 @@ struct s1_ctx {
     int* status_dev = nullptr;  // int[4], written by kernels on failure
     long long launches = 0;
     int opt_gemm_bn = 0;
-    int opt_debug = 0;
+    int opt_debug = 0;                          // only read by builds with -DS1_MEASURE (timing ablations)
+    long long opt_wait_limit = 2000000000LL;    // SM clock cycles a wait inside a projection kernel may take (~1 s)
+    long long opt_comm_timeout_ms = 120000;     // deadline of s1_comm_init; 0 = none
     int opt_gemm_sms = 0;  // 0 = all SMs
     int opt_comm_ctas = 0;  // blocks the collective may use (0 = the library's default); read by s1_comm_init
     bool opt_pdl = true;   // launch the projections with programmatic stream serialization
@@ -54,6 +56,7 @@ struct s1_ctx {
     cudaEvent_t comm_ready = nullptr, comm_done = nullptr;
     int comm_rank = 0, comm_size = 0;
     bool comm_pending = false;
+    bool comm_blocking = true;                // false: created with a deadline (non-blocking NCCL communicator)
     char err[512] = {0};
 };
 

@@ -193,9 +193,19 @@ extern "C" int s1_conv_silu(s1_ctx* ctx, const void* x, long long ldx, const voi
         return s1_fail(ctx, S1_EINVAL, "s1_conv_silu: channels must be a multiple of 8, 1 <= taps <= 16");
     if ((ldx % 8) || (ldy % 8) || ldx < channels || ldy < channels || !al16(x) || !al16(y))
         return s1_fail(ctx, S1_EINVAL, "s1_conv_silu: rows must be 16-byte aligned");
+    {
+        // every token reads the `taps - 1` rows before it, which another thread of the same launch would be overwriting:
+        // the output must not overlap the input
+        const char* xb = static_cast<const char*>(x);
+        const char* yb = static_cast<const char*>(y);
+        const long long xs = 2LL * (static_cast<long long>(total_tokens > 0 ? total_tokens - 1 : 0) * ldx + channels);
+        const long long ys = 2LL * (static_cast<long long>(total_tokens > 0 ? total_tokens - 1 : 0) * ldy + channels);
+        if (xb < yb + ys && yb < xb + xs)
+            return s1_fail(ctx, S1_EINVAL, "s1_conv_silu: y overlaps x (the convolution cannot run in place)");
+    }
     if (total_tokens == 0) return S1_OK;
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
-    if (taps == 4 && al16(weight) && x != y) {
+    if (taps == 4 && al16(weight)) {
         constexpr int TT = 16;
         const long long n = static_cast<long long>((total_tokens + TT - 1) / TT) * (channels / 8);
         s1_conv_silu_walk_kernel<4, TT><<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(

@@ -43,7 +43,10 @@ struct GemmParams {
     int n_tile_stride;  // W rows advanced per n-tile for the first B box
     int half1_base;     // W row offset of the second B box (relative to tile_n * n_tile_stride)
     int act;            // ACT_* applied after bias (plain epilogue only)
-    int debug;          // measurement aid: bit0 = skip output stores, bit1 = skip the whole epilogue
+    long long wait_limit;  // SM clock cycles any single wait may take before the kernel gives up ("wait_limit_cycles")
+#ifdef S1_MEASURE
+    int debug;          // timing ablations (results wrong by design): bit0 = skip output stores, bit1 = skip the epilogue
+#endif
     long long ldr;      // elements between residual rows
     const __nv_bfloat16* residual;  // [M, n_out] or null
     const __nv_bfloat16* bias;      // [n_out] or null
@@ -209,7 +212,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     // staging + TMA store of one 32-column chunk of the warp's rows
     auto emit = [&](int cix, const uint32_t (&o)[16]) {
         const int ucol = col0 + (cix / UNIT) * SW;  // first column of the store this chunk belongs to
-        if (row0 < p.M && ucol < p.n_out && !(p.debug & 1)) {
+#ifdef S1_MEASURE
+        if (p.debug & 1) return;
+#endif
+        if (row0 < p.M && ucol < p.n_out) {
             const uint32_t buf = stage_buf + (nstore % NBUF) * TILE_BYTES;
             if (cix % UNIT == 0) {
                 // the staging tile about to be overwritten must have been read out by its TMA store
@@ -342,8 +348,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                 __nv_bfloat162 g2 = __floats2bfloat162_rn(__uint_as_float(w[2 * j]), __uint_as_float(w[2 * j + 1]));
                 const float a0 = __low2float(a2), a1 = __high2float(a2);
                 __nv_bfloat162 act2;
-                if (p.debug & 8) act2 = a2;  // measurement aid: no activation
-                else if constexpr (EPI == EPI_GEGLU) {
+#ifdef S1_MEASURE
+                if (p.debug & 8) act2 = a2;
+                else
+#endif
+                if constexpr (EPI == EPI_GEGLU) {
                     float g0, g1;
                     gelu_erf_pair(a0, a1, g0, g1);
                     act2 = __floats2bfloat162_rn(g0, g1);
@@ -473,7 +482,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int r1 = r0 + p.half1_base;
                 for (int kb = 0; kb < num_kb; ++kb, ++cnt) {
                     const uint32_t s = cnt % STAGES, ph = (cnt / STAGES) & 1u;
-                    if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag)) {
+                    if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag, p.wait_limit)) {
                         fail_role = 1;
                         fail_tile = tile;
                         break;
@@ -504,7 +513,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t cnt = 0, it = 0;
             for (int tile = unit; tile < num_tiles && !fail_role; tile += num_units, ++it) {
                 const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
-                if (!mbar_wait(tempty0 + 8u * acc, aph ^ 1u, abort_flag)) {
+                if (!mbar_wait(tempty0 + 8u * acc, aph ^ 1u, abort_flag, p.wait_limit)) {
                     fail_role = 2;
                     fail_tile = tile;
                     break;
@@ -513,7 +522,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++cnt) {
                     const uint32_t s = cnt % STAGES, ph = (cnt / STAGES) & 1u;
-                    if (!mbar_wait(full0 + 8u * s, ph, abort_flag)) {
+                    if (!mbar_wait(full0 + 8u * s, ph, abort_flag, p.wait_limit)) {
                         fail_role = 3;
                         fail_tile = tile;
                         break;
@@ -556,7 +565,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint4 res[(MODE & 1) ? CH * 4 : 1];
             if constexpr (!PAIRED && (MODE & 1)) fetch_residual<CH>(p, row0, col0, lane, res);
             // the whole warp must agree before any .sync.aligned tcgen05 instruction
-            const bool ready = mbar_wait(tfull0 + 8u * acc, aph, abort_flag);
+            const bool ready = mbar_wait(tfull0 + 8u * acc, aph, abort_flag, p.wait_limit);
             if (!__all_sync(0xffffffffu, ready)) {
                 fail_role = 4;
                 fail_tile = tile;
@@ -564,12 +573,14 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             tc_fence_after();
             const uint32_t tempty_bar = lead_tempty0 + 8u * acc;
+#ifdef S1_MEASURE
             if (p.debug & 2) {
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(tempty_bar);
                 continue;
             }
+#endif
             const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + hh * (CH * 32);
             epilogue_tile<BN, EPI, MODE, EW, Store::kCols, NBUF>(p, &tmY, taddr, row0, col0, stage_buf, nstore, tempty_bar, lane, res);
         }

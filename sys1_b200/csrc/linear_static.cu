@@ -16,6 +16,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "../../include/sys1_b200.h"
@@ -34,7 +35,8 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 struct PerDevice {
-    bool ready = false;
+    // set (release) once every other field is final; read (acquire) by callers without the mutex
+    std::atomic<bool> ready{false};
     int* scratch = nullptr;  // device address of s1_static_scratch on this GPU
     int sm_count = 0;
     PFN_cuTensorMapEncodeTiled encode = nullptr;
@@ -62,7 +64,7 @@ cudaError_t set_smem_attr() {
 int setup_device(int device, char* err, size_t err_len) {
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     PerDevice& d = g_dev[device];
-    if (d.ready) return S1_OK;
+    if (d.ready.load(std::memory_order_acquire)) return S1_OK;
     cudaDeviceProp prop;
     cudaError_t e = cudaGetDeviceProperties(&prop, device);
     if (e != cudaSuccess) return fail(err, err_len, S1_ECUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
@@ -87,7 +89,7 @@ int setup_device(int device, char* err, size_t err_len) {
     d.scratch = static_cast<int*>(ptr);
     d.sm_count = prop.multiProcessorCount;
     d.encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
-    d.ready = true;
+    d.ready.store(true, std::memory_order_release);
     return S1_OK;
 }
 
@@ -124,6 +126,23 @@ cudaError_t launch(const PerDevice& d, cudaStream_t stream, const CUtensorMap& a
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Makes a device current for the length of one call and restores the one the caller had.
+struct DeviceGuard {
+    int previous = -1;
+    bool switched = false;
+    cudaError_t enter(int device) {
+        cudaError_t e = cudaGetDevice(&previous);
+        if (e != cudaSuccess) return e;
+        if (previous == device) return cudaSuccess;
+        e = cudaSetDevice(device);
+        switched = (e == cudaSuccess);
+        return e;
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(previous);
+    }
+};
+
 }  // namespace
 
 extern "C" int s1_linear_static(int device_ordinal, void* cuda_stream, const s1_linear_desc* lin, const void* x,
@@ -156,9 +175,11 @@ extern "C" int s1_linear_static(int device_ordinal, void* cuda_stream, const s1_
     if (!aligned16(x) || !aligned16(lin->w) || !aligned16(y) || !aligned16(residual) || !aligned16(lin->w_up))
         return fail(err, err_len, S1_EINVAL, "s1_linear_static: pointers must be 16-byte aligned");
 
-    cudaError_t e = cudaSetDevice(device_ordinal);
+    // The call runs with `device_ordinal` current and puts the caller's device back before it returns.
+    DeviceGuard guard;
+    cudaError_t e = guard.enter(device_ordinal);
     if (e != cudaSuccess) return fail(err, err_len, S1_ECUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
-    if (!g_dev[device_ordinal].ready) {
+    if (!g_dev[device_ordinal].ready.load(std::memory_order_acquire)) {
         const int rc = setup_device(device_ordinal, err, err_len);
         if (rc != S1_OK) return rc;
     }
@@ -170,14 +191,14 @@ extern "C" int s1_linear_static(int device_ordinal, void* cuda_stream, const s1_
     const long long pair_tiles = static_cast<long long>((T + 2 * kBM - 1) / (2 * kBM)) * tiles_n;
     const int ctas = (pair_tiles >= d.sm_count / 2) ? 2 : 1;
 
-    GemmParams p;
+    GemmParams p{};
     p.M = T;
     p.n_out = n_out;
     p.K = lin->K;
     p.tiles_m = (T + ctas * kBM - 1) / (ctas * kBM);
     p.tiles_n = tiles_n;
     p.act = ACT_NONE;
-    p.debug = 0;
+    p.wait_limit = kWaitLimitCycles;
     p.ldr = ldr;
     p.residual = static_cast<const __nv_bfloat16*>(residual);
     p.bias = nullptr;

@@ -52,6 +52,8 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
     return raw;
 }
 
+__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
 template <int LPR>
 __device__ __forceinline__ float group_sum(float v) {
 #pragma unroll
@@ -230,6 +232,81 @@ __global__ void __launch_bounds__(256) s1_rope_kernel(__nv_bfloat16* __restrict_
     *reinterpret_cast<uint4*>(hi_p) = pack8(b);
 }
 
+
+// ------------------------------------------------------------------------------------------- per-head norm + rope
+// RMSNorm scaled by (1 + weight) over the head_dim columns of every (token, head), rounded to bf16 as the reference
+// materialises it, then the partial rotate-half rotation of the first `rot` columns, all in one pass over the data
+// (`q_norm` / `k_norm` followed by `Attention::rotary`, src/archs/qwen35_text.rs:296-339). LPR lanes share a head.
+// bf16_ops = 1 rounds the way candle's bf16 tensor ops do (:302): each product and the sum are bf16 values;
+// bf16_ops = 0 forms the rotation in f32 and rounds once (the arithmetic of s1_rope).
+template <int LPR>
+__global__ void __launch_bounds__(256) s1_head_norm_rope_kernel(__nv_bfloat16* __restrict__ x, long long ldx, long long head_stride,
+                                                               int heads, const __nv_bfloat16* __restrict__ w, float eps,
+                                                               const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                               const int32_t* __restrict__ positions, int max_pos, int rot,
+                                                               long long rows, int bf16_ops, int* __restrict__ status) {
+    constexpr int RPW = 32 / LPR;
+    const int lane = threadIdx.x & 31, sub = lane % LPR;
+    const long long warp = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 5;
+    const long long row = warp * RPW + lane / LPR;
+    const bool live = row < rows;
+    const long long t = live ? row / heads : 0;
+    const int h = live ? static_cast<int>(row % heads) : 0;
+    __nv_bfloat16* ptr = x + t * ldx + h * head_stride + sub * 8;
+    float f[8];
+    unpack8(live ? *reinterpret_cast<const uint4*>(ptr) : make_uint4(0, 0, 0, 0), f);
+    float sq = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sq += f[e] * f[e];
+    const float rstd = 1.f / sqrtf(group_sum<LPR>(sq) * (1.f / static_cast<float>(8 * LPR)) + eps);
+    float g[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(w + sub * 8)), g);
+    uint4 normed;
+    {
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = f[e] * rstd * (g[e] + 1.f);
+        normed = pack8(y);
+        unpack8(normed, f);  // the bf16 values the rotation starts from
+    }
+    // the partner half of the rotated span sits rot / 16 lanes away (every lane takes part in the exchange)
+    const int halfc = rot / 16;
+    uint4 other_raw;
+    other_raw.x = __shfl_xor_sync(0xffffffffu, normed.x, halfc);
+    other_raw.y = __shfl_xor_sync(0xffffffffu, normed.y, halfc);
+    other_raw.z = __shfl_xor_sync(0xffffffffu, normed.z, halfc);
+    other_raw.w = __shfl_xor_sync(0xffffffffu, normed.w, halfc);
+    if (!live) return;
+    if (sub < 2 * halfc) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= max_pos) {
+            if (atomicCAS(status, 0, 102) == 0) {
+                status[1] = static_cast<int>(blockIdx.x);
+                status[2] = static_cast<int>(t);
+                status[3] = pos;
+            }
+        } else {
+            float o[8], c[8], sn[8];
+            unpack8(other_raw, o);
+            const bool is_lo = sub < halfc;
+            const long long tb = static_cast<long long>(pos) * (rot / 2) + (sub % halfc) * 8;
+            *reinterpret_cast<float4*>(c) = __ldg(reinterpret_cast<const float4*>(cos_t + tb));
+            *reinterpret_cast<float4*>(c + 4) = __ldg(reinterpret_cast<const float4*>(cos_t + tb) + 1);
+            *reinterpret_cast<float4*>(sn) = __ldg(reinterpret_cast<const float4*>(sin_t + tb));
+            *reinterpret_cast<float4*>(sn + 4) = __ldg(reinterpret_cast<const float4*>(sin_t + tb) + 1);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float own_c = __fmul_rn(f[e], c[e]);
+                const float oth_s = __fmul_rn(is_lo ? -o[e] : o[e], sn[e]);  // rotate_half = [-second, first]
+                if (bf16_ops) f[e] = __fadd_rn(bf16r(own_c), bf16r(oth_s));
+                else f[e] = is_lo ? __fsub_rn(own_c, __fmul_rn(o[e], sn[e])) : __fadd_rn(__fmul_rn(o[e], sn[e]), own_c);
+            }
+            normed = pack8(f);
+        }
+    }
+    *reinterpret_cast<uint4*>(ptr) = normed;
+}
+
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -276,6 +353,39 @@ extern "C" int s1_rope(s1_ctx* ctx, void* x, long long ldx, const float* cos_tab
     s1_rope_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
         static_cast<__nv_bfloat16*>(x), ldx, cos_table, sin_table, positions, max_positions, total_tokens, heads, head_stride,
         rotary_dim, ctx->status_dev);
+    S1_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return S1_OK;
+}
+
+extern "C" int s1_head_norm_rope(s1_ctx* ctx, void* x, long long ldx, long long head_stride, int heads, int head_dim,
+                                 const void* norm_weight, float eps, const float* cos_table, const float* sin_table,
+                                 const int32_t* positions, int max_positions, int rotary_dim, int total_tokens, int bf16_ops) {
+    if (!ctx) return S1_EINVAL;
+    if (!x || !norm_weight || !cos_table || !sin_table || !positions) return s1_fail(ctx, S1_EINVAL, "s1_head_norm_rope: null pointer");
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256)
+        return s1_fail(ctx, S1_EINVAL, "s1_head_norm_rope: head_dim must be 64, 128 or 256 (got %d)", head_dim);
+    if (rotary_dim != 16 && rotary_dim != 32 && rotary_dim != 64 && rotary_dim != 128 && rotary_dim != 256)
+        return s1_fail(ctx, S1_EINVAL, "s1_head_norm_rope: rotary_dim must be 16, 32, 64, 128 or 256 (got %d)", rotary_dim);
+    if (rotary_dim > head_dim) return s1_fail(ctx, S1_EINVAL, "s1_head_norm_rope: rotary_dim exceeds head_dim");
+    if (total_tokens < 0 || heads < 1 || max_positions < 1) return s1_fail(ctx, S1_EINVAL, "s1_head_norm_rope: bad sizes");
+    if (head_stride < head_dim || (head_stride % 8) || (ldx % 8) || ldx < (heads - 1) * head_stride + head_dim || !al16(x) ||
+        !al16(norm_weight) || !al16(cos_table) || !al16(sin_table))
+        return s1_fail(ctx, S1_EINVAL, "s1_head_norm_rope: heads must be 16-byte aligned and lie inside a row");
+    if (total_tokens == 0) return S1_OK;
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    const long long rows = static_cast<long long>(total_tokens) * heads;
+    auto* xp = static_cast<__nv_bfloat16*>(x);
+    auto* wp = static_cast<const __nv_bfloat16*>(norm_weight);
+    const int lpr = head_dim / 8;
+    const unsigned blocks = static_cast<unsigned>((rows + 8 * (32 / lpr) - 1) / (8 * (32 / lpr)));
+#define S1_HNR(LPR_)                                                                                                       \
+    s1_head_norm_rope_kernel<LPR_><<<blocks, 256, 0, ctx->stream>>>(xp, ldx, head_stride, heads, wp, eps, cos_table, sin_table, \
+                                                                    positions, max_positions, rotary_dim, rows, bf16_ops, ctx->status_dev)
+    if (lpr == 8) S1_HNR(8);
+    else if (lpr == 16) S1_HNR(16);
+    else S1_HNR(32);
+#undef S1_HNR
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return S1_OK;

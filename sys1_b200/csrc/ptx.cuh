@@ -53,14 +53,15 @@ constexpr long long kWaitLimitCycles = 2000000000LL;
 
 // Bounded wait. `abort_flag` lives in shared memory and is raised by whichever thread
 // times out first; every other waiter sees it and unwinds as well.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit_cycles = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit_cycles) {
                 *abort_flag = 1;
                 return false;
             }

@@ -58,6 +58,18 @@ class Context:
     def sync(self) -> None:
         self.check(self._lib.s1_sync(self.handle))
 
+    def workspace(self, nbytes: int) -> torch.Tensor:
+        """Device scratch of this context (uint8, 1024-byte aligned start, at least `nbytes`), grown on demand. It
+        belongs to the context - that is, to one stream - so kernels that use it are ordered one after the other; two
+        contexts on one GPU never share it. The library itself allocates nothing: a Rust caller would hand it a
+        buffer from candle's pool the same way."""
+        ws = getattr(self, "_ws", None)
+        if ws is None or ws.numel() < nbytes + 1024:
+            ws = torch.empty(max(nbytes + 1024, 1 << 16), dtype=torch.uint8, device=torch.device("cuda", self.ordinal))
+            self._ws = ws
+        off = (-ws.data_ptr()) % 1024
+        return ws[off:]
+
     def launch_count(self) -> int:
         return int(self._lib.s1_launch_count(self.handle))
 

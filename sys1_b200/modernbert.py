@@ -84,9 +84,6 @@ class AttentionProjections:
         return self.wo.forward(attended, residual=residual)
 
 
-_attn_ws = {}
-
-
 def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_host, window: int = -1,
                      scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`scaled_dot_product_attention` + `merge_heads` (src/archs/modernbert.rs:249-351) on a packed batch through
@@ -106,10 +103,7 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
         return out
     ctx = device.load(q.device.index)
     need = int(ctx._lib.s1_attention_workspace(len(cu) - 1, T))
-    ws = _attn_ws.get(q.device)
-    if ws is None or ws.numel() < need:
-        ws = torch.empty(max(need, 1 << 16), dtype=torch.uint8, device=q.device)
-        _attn_ws[q.device] = ws
+    ws = ctx.workspace(need)
     rc = ctx._lib.s1_attention(ctx.handle, C.c_void_p(q.data_ptr()), q.stride(0), C.c_void_p(k.data_ptr()), k.stride(0),
                                C.c_void_p(v.data_ptr()), v.stride(0), cu.ctypes.data_as(C.POINTER(C.c_int32)), len(cu) - 1, T, H, D,
                                int(window), C.c_float(D ** -0.5 if scale is None else scale), C.c_void_p(out.data_ptr()),
@@ -120,22 +114,23 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
 
 class Encoder:
     """`Encoder::forward` (src/archs/modernbert.rs:958-989) on a token-packed batch, every stage through the C ABI:
-    embedding lookup + embedding norm (`s1_norm` with a row index), per layer attn_norm -> Wqkv -> RoPE in place
-    (`s1_rope`) -> flash-form attention (`s1_attention`) -> Wo with the residual stream updated in place ->
-    mlp_norm -> Wi with GeGLU -> MLP-out with the residual stream updated in place, and the final norm.
+    embedding lookup + embedding norm (`s1_norm` with a row index), per layer attn_norm -> Wqkv with RoPE in its
+    epilogue (`s1_linear_rope`) -> flash-form attention (`s1_attention`) -> Wo with the residual stream updated in
+    place -> mlp_norm -> Wi with GeGLU -> MLP-out with the residual stream updated in place, and the final norm.
 
-    `weights`: dict with the names of `oracle.modernbert.init_weights` (bf16 CUDA tensors); `cfg`: any object with
-    the fields of `oracle.modernbert.EncoderConfig`."""
+    `weights`: dict of bf16 CUDA tensors under the checkpoint's names: `tok_embeddings [vocab, hidden]`,
+    `embeddings_norm [hidden]`, `final_norm [hidden]` and, for every layer i, `layers.i.Wqkv [3 hidden, hidden]`,
+    `layers.i.Wo [hidden, hidden]`, `layers.i.Wi [2 I, hidden]`, `layers.i.mlp_Wo [hidden, I]`, `layers.i.mlp_norm
+    [hidden]` and (i > 0; layer 0 has none, :846-851) `layers.i.attn_norm [hidden]`.
+    `cfg`: any object with the fields `hidden_size`, `num_hidden_layers`, `num_attention_heads`, `layer_norm_eps`,
+    `global_attn_every_n_layers` (layer i is global iff i % n == 0, :920), `local_attention` (window = half of it,
+    :977), `global_rope_theta`, `local_rope_theta`. Head dim must be 64."""
 
-    def __init__(self, weights, cfg, attention: str = "s1"):
-        """`attention`: "s1" = this library's kernels throughout; "torch" = attention, norms and RoPE as PyTorch
-        operators (`scaled_dot_product_attention` per sequence with an explicit band mask), kept only as a
-        comparison arm for measurements - the projections still go through the C ABI."""
-        self.attention = attention
+    def __init__(self, weights, cfg):
         self.cfg = cfg
         self.w = weights
         self.head_dim = cfg.hidden_size // cfg.num_attention_heads
-        if attention == "s1" and self.head_dim != 64:
+        if self.head_dim != 64:
             raise ValueError("s1_attention is built for head_dim 64")
         self.layers = []
         self.norms = {}
@@ -147,7 +142,6 @@ class Encoder:
             if name.endswith("norm"):
                 self.norms[name] = Norm(t, cfg.layer_norm_eps)
         self._rotary = {}
-        self._bands = {}
 
     def _rope(self, theta: float, length: int, dev) -> RotaryEmbedding:
         key = (theta, dev)
@@ -155,19 +149,8 @@ class Encoder:
             self._rotary[key] = RotaryEmbedding(theta, self.head_dim, max(length, 8192), dev)
         return self._rotary[key]
 
-    def _band(self, length: int, dev):
-        key = (length, dev)
-        if key not in self._bands:
-            idx = torch.arange(length, device=dev)
-            self._bands[key] = (idx.unsqueeze(0) - idx.unsqueeze(1)).abs() <= self.cfg.local_attention // 2
-        return self._bands[key]
-
     def _ln(self, x: torch.Tensor, name: str, gather: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if self.attention == "s1":
-            return self.norms[name](x, gather=gather)
-        if gather is not None:
-            x = x[gather.long()]
-        return torch.nn.functional.layer_norm(x, (self.cfg.hidden_size,), self.w[name], None, self.cfg.layer_norm_eps)
+        return self.norms[name](x, gather=gather)
 
     def _layer(self, i: int, x: torch.Tensor, bounds, pos: torch.Tensor, max_len: int) -> torch.Tensor:
         """`Layer::forward` (src/archs/modernbert.rs:857-887) for layer `i`; updates the residual stream `x` in place."""
@@ -180,29 +163,9 @@ class Encoder:
         n = x if i == 0 else self._ln(x, p + "attn_norm")
         rotary = self._rope(cfg.local_rope_theta if local else cfg.global_rope_theta, max_len, dev)
         attn = torch.empty((T, H * D), dtype=torch.bfloat16, device=dev)
-        if self.attention == "s1":
-            qkv = rotary.project_qkv(n, proj.wqkv, pos, H)   # Wqkv with RoPE in its epilogue
-            q, k, v = qkv.view(T, 3, H, D).unbind(1)
-            attention_varlen(q, k, v, bounds, window=cfg.local_attention // 2 if local else -1, out=attn)
-        else:
-            F = torch.nn.functional
-            qkv = proj.qkv(n)
-            c, s = rotary.cos[pos.long()].unsqueeze(1), rotary.sin[pos.long()].unsqueeze(1)
-
-            def rot(t):
-                t = t.float()
-                t1, t2 = t[..., : D // 2], t[..., D // 2:]
-                return torch.cat([t1 * c - t2 * s, t1 * s + t2 * c], dim=-1).to(torch.bfloat16)
-
-            qkv = qkv.view(T, 3, H, D)
-            q, k, v = rot(qkv[:, 0]), rot(qkv[:, 1]), qkv[:, 2]
-            for a, b in zip(bounds[:-1], bounds[1:]):
-                if a == b:
-                    continue
-                mask = self._band(b - a, dev) if local else None
-                o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1).unsqueeze(0), k[a:b].transpose(0, 1).unsqueeze(0),
-                                                   v[a:b].transpose(0, 1).unsqueeze(0), attn_mask=mask)
-                attn[a:b] = o[0].transpose(0, 1).reshape(b - a, H * D)
+        qkv = rotary.project_qkv(n, proj.wqkv, pos, H)   # Wqkv with RoPE in its epilogue
+        q, k, v = qkv.view(T, 3, H, D).unbind(1)
+        attention_varlen(q, k, v, bounds, window=cfg.local_attention // 2 if local else -1, out=attn)
         proj.wo.forward(attn, residual=x, out=x)                                        # x += attn Wo^T
         mlp.output.forward(mlp.gated(self._ln(x, p + "mlp_norm")), residual=x, out=x)   # x += geglu(LN(x) Wi^T) Wout^T
         return x

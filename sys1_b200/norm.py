@@ -68,6 +68,31 @@ def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: torc
     return x
 
 
+def head_norm_rope_(x: torch.Tensor, heads: int, head_stride: int, head_dim: int, weight: torch.Tensor, eps: float,
+                    cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor, rotary_dim: int, bf16_ops: bool = True) -> torch.Tensor:
+    """`q_norm` / `k_norm` followed by `Attention::rotary` (src/archs/qwen35_text.rs:296-339) in one pass, in place
+    (`s1_head_norm_rope`): per-head RMSNorm x (1 + weight) over `head_dim` columns of `heads` heads per row of
+    `x [T, ld]` (head h at column `h * head_stride`), then the partial rotation of the first `rotary_dim` columns.
+    `bf16_ops`: round each product and the sum to bf16 as candle's bf16 tensor ops do (the reference's arithmetic)."""
+    _rows(x, "x")
+    for name, t in (("cos", cos), ("sin", sin)):
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or not t.is_contiguous() or t.shape[1] != rotary_dim // 2:
+            raise ValueError(f"{name} must be a contiguous f32 CUDA table [positions, rotary_dim / 2]")
+    if not positions.is_cuda or positions.dtype != torch.int32 or not positions.is_contiguous() or positions.numel() != x.shape[0]:
+        raise ValueError("positions must be a contiguous int32 CUDA vector with one entry per row")
+    if weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.numel() != head_dim or not weight.is_contiguous():
+        raise ValueError("weight must be a contiguous bf16 CUDA vector of length head_dim")
+    if x.shape[0] == 0:
+        return x
+    ctx = device.load(x.device.index)
+    rc = ctx._lib.s1_head_norm_rope(ctx.handle, C.c_void_p(x.data_ptr()), x.stride(0), int(head_stride), int(heads), int(head_dim),
+                                    C.c_void_p(weight.data_ptr()), C.c_float(eps), C.c_void_p(cos.data_ptr()), C.c_void_p(sin.data_ptr()),
+                                    C.c_void_p(positions.data_ptr()), min(cos.shape[0], sin.shape[0]), int(rotary_dim), x.shape[0],
+                                    1 if bf16_ops else 0)
+    ctx.check(rc)
+    return x
+
+
 def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     """`ids.apply(&embedding)` (src/archs/qwen35_text.rs:978-980): the rows `table[ids]` (ids int32 CUDA), through
     `s1_norm` with kind 2 (rows copied through the index); an id outside the table is reported at the next sync."""

@@ -47,19 +47,6 @@ class Mlp:
     __call__ = forward
 
 
-_workspaces = {}
-
-
-def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
-    """Device scratch for the chunked kernels, grown on demand and kept per device (the library itself never
-    allocates; a Rust caller would hand it a buffer from candle's pool the same way)."""
-    ws = _workspaces.get(dev)
-    if ws is None or ws.numel() < nbytes + 1024:
-        ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
-        _workspaces[dev] = ws
-    return ws
-
-
 def delta_rule_chunked_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
                               cu_seqlens_host, ctx: Optional[device.Context] = None) -> torch.Tensor:
     """The recurrence in 64-token chunks on the tensor cores (`s1_delta_rule_chunked`): bf16 operand precision,
@@ -79,8 +66,7 @@ def delta_rule_chunked_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         ctx = device.load(q.device.index)
     nseq = int(cu.shape[0] - 1)
     need = int(ctx._lib.s1_delta_rule_chunked_workspace(nseq, T, H))
-    ws = _workspace(q.device, need)
-    ptr = (ws.data_ptr() + 1023) // 1024 * 1024
+    ptr = ctx.workspace(need).data_ptr()
     rc = ctx._lib.s1_delta_rule_chunked(ctx.handle, *(C.c_void_p(t.data_ptr()) for t in (q, k, v, g, beta)),
                                         cu.ctypes.data_as(C.POINTER(C.c_int32)), nseq, T, H, Dk, Dv,
                                         C.c_void_p(out.data_ptr()), C.c_void_p(ptr), need)
@@ -153,13 +139,20 @@ class LinearAttention:
 
     def __init__(self, qkv: Linear, z: Linear, b: Linear, a: Linear, conv: torch.Tensor, decay: torch.Tensor,
                  dt_bias: torch.Tensor, norm: torch.Tensor, output: Linear, key_heads: int, value_heads: int, eps: float,
-                 merge_inputs: bool = True):
-        """`merge_inputs`: stack the four input projections, which share their input, into one weight `[N_qkv + N_z + 2 Hv,
+                 merge_inputs: bool = True, recurrence: str = "chunked"):
+        """`recurrence`: "chunked" (default) evaluates the gated delta rule in 64-token chunks on the tensor cores with
+        bf16 operands and f32 state (`s1_gated_delta_rule`; within 2e-2 of the output scale of the f32 recurrence, which
+        is the layer-level bound of this path); "exact" runs the token-sequential f32 kernel (`s1_delta_rule`, the
+        reference's own arithmetic and its 1e-4 bound), about three times slower.
+        `merge_inputs`: stack the four input projections, which share their input, into one weight `[N_qkv + N_z + 2 Hv,
         K]` at load time, so that they run as one contraction (two of them are only `Hv` = 16 or 48 columns wide, a
         launch each for next to no work); the outputs are column views of one buffer."""
         self.qkv, self.z, self.b, self.a, self.output = qkv, z, b, a, output
         self.conv, self.decay, self.dt_bias, self.norm = conv, decay.float().contiguous(), dt_bias.float().contiguous(), norm
         self.key_heads, self.value_heads, self.eps = key_heads, value_heads, eps
+        if recurrence not in ("chunked", "exact"):
+            raise ValueError("recurrence must be 'chunked' or 'exact'")
+        self.recurrence = recurrence
         self.merged = None
         if merge_inputs and all(l.bias is None for l in (qkv, z, b, a)):
             parts = [qkv.weight, z.weight, b.weight, a.weight]
@@ -187,16 +180,33 @@ class LinearAttention:
         pre, zz, bb, aa = self._inputs(x)
         mixed = conv_silu(pre, self.conv, positions, ctx)                         # project_and_mix (:515-526)
         y = torch.empty((T, self.value_heads * 128), dtype=torch.bfloat16, device=x.device)
-        need = int(ctx._lib.s1_gated_delta_rule_workspace(len(cu) - 1, T, self.value_heads))
-        ws = _workspace(x.device, need)
-        ptr = (ws.data_ptr() + 1023) // 1024 * 1024
-        rc = ctx._lib.s1_gated_delta_rule(
-            ctx.handle, C.c_void_p(mixed.data_ptr()), mixed.stride(0), C.c_void_p(bb.data_ptr()), C.c_void_p(aa.data_ptr()),
-            bb.stride(0), C.c_void_p(self.dt_bias.data_ptr()), C.c_void_p(self.decay.data_ptr()), C.c_void_p(zz.data_ptr()),
-            zz.stride(0), C.c_void_p(self.norm.data_ptr()), C.c_float(self.eps), cu.ctypes.data_as(C.POINTER(C.c_int32)),
-            len(cu) - 1, T, self.key_heads, self.value_heads, C.c_void_p(y.data_ptr()), y.stride(0), C.c_void_p(ptr), need)
-        ctx.check(rc)
+        if self.recurrence == "exact":
+            self._exact(ctx, mixed, zz, bb, aa, cu, y)
+        else:
+            need = int(ctx._lib.s1_gated_delta_rule_workspace(len(cu) - 1, T, self.value_heads))
+            ptr = ctx.workspace(need).data_ptr()
+            rc = ctx._lib.s1_gated_delta_rule(
+                ctx.handle, C.c_void_p(mixed.data_ptr()), mixed.stride(0), C.c_void_p(bb.data_ptr()), C.c_void_p(aa.data_ptr()),
+                bb.stride(0), C.c_void_p(self.dt_bias.data_ptr()), C.c_void_p(self.decay.data_ptr()), C.c_void_p(zz.data_ptr()),
+                zz.stride(0), C.c_void_p(self.norm.data_ptr()), C.c_float(self.eps), cu.ctypes.data_as(C.POINTER(C.c_int32)),
+                len(cu) - 1, T, self.key_heads, self.value_heads, C.c_void_p(y.data_ptr()), y.stride(0), C.c_void_p(ptr), need)
+            ctx.check(rc)
         return self.output.forward(y, residual=residual, out=residual if inplace else None)  # out_proj (+ the layer's residual, :938)
+
+    def _exact(self, ctx, mixed, zz, bb, aa, cu, y) -> None:
+        """The reference's own precision: `delta_inputs` -> token-sequential f32 recurrence -> `finish_delta`
+        (`s1_delta_inputs`, `s1_delta_rule`, `s1_delta_finish`), f32 between the three."""
+        T, Hv = mixed.shape[0], self.value_heads
+        f32 = dict(dtype=torch.float32, device=mixed.device)
+        q, k, v = (torch.empty((T, Hv, 128), **f32) for _ in range(3))
+        g, beta = (torch.empty((T, Hv), **f32) for _ in range(2))
+        P = lambda t: C.c_void_p(t.data_ptr())
+        ctx.check(ctx._lib.s1_delta_inputs(ctx.handle, P(mixed), mixed.stride(0), P(bb), P(aa), bb.stride(0), P(self.dt_bias),
+                                           P(self.decay), T, self.key_heads, Hv, P(q), P(k), P(v), P(g), P(beta)))
+        cu_dev = torch.from_numpy(cu).to(mixed.device)
+        o = delta_rule_packed(q, k, v, g, beta, cu_dev, ctx)
+        ctx.check(ctx._lib.s1_delta_finish(ctx.handle, P(o), P(zz), zz.stride(0), P(self.norm), C.c_float(self.eps), T, Hv,
+                                           P(y), y.stride(0)))
 
 
 class RopeParams:
@@ -230,7 +240,7 @@ def attention_causal_gqa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_s
             raise ValueError(f"{name} must be a bf16 CUDA tensor [T, heads, 256] with contiguous head rows (no CPU fallback)")
     ctx = device.load(q.device.index)
     need = int(ctx._lib.s1_attention_gqa_workspace(len(cu) - 1, T))
-    ws = _workspace(q.device, need)
+    ws = ctx.workspace(need)
     rc = ctx._lib.s1_attention_gqa(
         ctx.handle, C.c_void_p(q.data_ptr()), q.stride(0), q.stride(1), C.c_void_p(k.data_ptr()), k.stride(0), k.stride(1),
         C.c_void_p(v.data_ptr()), v.stride(0), v.stride(1), C.c_void_p(gate.data_ptr() if gate is not None else 0),
@@ -243,37 +253,32 @@ def attention_causal_gqa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_s
 
 class FullAttention:
     """`FullAttention` (src/archs/qwen35_text.rs:242-411) on a packed batch, same member names: `q` (query and output
-    gate interleaved per head), `k`, `v`, `output`, `q_norm`, `k_norm`."""
+    gate interleaved per head), `k`, `v`, `output`, `q_norm`, `k_norm`. The three input projections share their input and
+    run as one contraction over the stacked weight `[q | k | v]`; `q_norm` / `k_norm` and the partial rotation are one
+    pass each over the query halves and the key heads (`s1_head_norm_rope`), rounding as candle's bf16 ops do."""
 
     def __init__(self, q: Linear, k: Linear, v: Linear, output: Linear, q_norm: RmsNorm, k_norm: RmsNorm, heads: int, kv_heads: int,
-                 head_dim: int, rope: RopeParams, core: str = "s1"):
+                 head_dim: int, rope: RopeParams):
         self.q, self.k, self.v, self.output, self.q_norm, self.k_norm = q, k, v, output, q_norm, k_norm
-        self.heads, self.kv_heads, self.head_dim, self.rope, self.core = heads, kv_heads, head_dim, rope, core
+        self.heads, self.kv_heads, self.head_dim, self.rope = heads, kv_heads, head_dim, rope
+        self.merged = None
+        if all(l.bias is None for l in (q, k, v)):
+            self.merged = Linear(torch.cat([q.weight, k.weight, v.weight], dim=0).contiguous())
 
     def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None,
                 inplace: bool = False) -> torch.Tensor:
         T, H, KV, D = x.shape[0], self.heads, self.kv_heads, self.head_dim
-        qg = self.q.forward(x)                                  # [T, H * 2 * D]: per head [query | gate]
-        k, v = self.k.forward(x), self.v.forward(x)             # [T, KV * D]
-        heads_q = qg.view(T * H, 2 * D)
-        self.q_norm.forward(heads_q[:, :D], out=heads_q[:, :D])  # per-head RMS norm of the query halves, in place
-        self.k_norm.forward(k.view(T * KV, D), out=k.view(T * KV, D))
-        _norm.rope_(qg, self.rope.cos, self.rope.sin, positions, H, 2 * D, self.rope.rotary_dim)
-        _norm.rope_(k, self.rope.cos, self.rope.sin, positions, KV, D, self.rope.rotary_dim)
-        q4 = qg.view(T, H, 2, D)
-        if self.core == "s1":
-            gated = attention_causal_gqa(q4[:, :, 0], k.view(T, KV, D), v.view(T, KV, D), cu_seqlens_host, gate=q4[:, :, 1])
-        else:  # comparison arm: PyTorch attention per sequence
-            F = torch.nn.functional
-            attn = torch.empty((T, H, D), dtype=torch.bfloat16, device=x.device)
-            bounds = [int(b) for b in cu_seqlens_host]
-            for a, b in zip(bounds[:-1], bounds[1:]):
-                if a == b:
-                    continue
-                o = F.scaled_dot_product_attention(q4[a:b, :, 0].transpose(0, 1).unsqueeze(0), k.view(T, KV, D)[a:b].transpose(0, 1).unsqueeze(0),
-                                                   v.view(T, KV, D)[a:b].transpose(0, 1).unsqueeze(0), is_causal=True, enable_gqa=True)
-                attn[a:b] = o[0].transpose(0, 1)
-            gated = (attn * torch.sigmoid(q4[:, :, 1])).reshape(T, H * D)
+        if self.merged is not None:
+            qkv = self.merged.forward(x)                        # [T, H * 2 * D + 2 * KV * D]
+            qg, k, v = qkv[:, :2 * H * D], qkv[:, 2 * H * D:2 * H * D + KV * D], qkv[:, 2 * H * D + KV * D:]
+        else:
+            qg, k, v = self.q.forward(x), self.k.forward(x), self.v.forward(x)
+        r = self.rope
+        # per head [query | gate]: norm + rotation of the query halves, then of the key heads, each where it lies
+        _norm.head_norm_rope_(qg, H, 2 * D, D, self.q_norm.weight, self.q_norm.eps, r.cos, r.sin, positions, r.rotary_dim)
+        _norm.head_norm_rope_(k, KV, D, D, self.k_norm.weight, self.k_norm.eps, r.cos, r.sin, positions, r.rotary_dim)
+        q4 = qg.unflatten(1, (H, 2, D))
+        gated = attention_causal_gqa(q4[:, :, 0], k.unflatten(1, (KV, D)), v.unflatten(1, (KV, D)), cu_seqlens_host, gate=q4[:, :, 1])
         return self.output.forward(gated, residual=residual, out=residual if inplace else None)
 
 
@@ -291,11 +296,22 @@ class Layer:
 
 
 class Decoder:
-    """`Decoder::forward` (src/archs/qwen35_text.rs:942-1005) on a token-packed batch. `weights`: dict with the names of
-    `oracle.qwen35.init_weights` (bf16 CUDA tensors; A_log / dt_bias f32); `cfg`: the fields of
-    `oracle.qwen35.DecoderConfig`. `core`: "s1" (this library's attention kernel) or "torch" (comparison arm)."""
+    """`Decoder::forward` (src/archs/qwen35_text.rs:942-1005) on a token-packed batch.
 
-    def __init__(self, weights, cfg, core: str = "s1", max_positions: int = 8192):
+    `weights`: dict of CUDA tensors under the checkpoint's names (bf16 unless noted): `embed_tokens [vocab, hidden]`,
+    `norm [hidden]` and per layer i `layers.i.input_layernorm`, `layers.i.post_attention_layernorm` `[hidden]`,
+    `layers.i.mlp.{gate_proj, up_proj} [I, hidden]`, `layers.i.mlp.down_proj [hidden, I]`; full-attention layers:
+    `layers.i.self_attn.q_proj [2 H D, hidden]` (query and gate interleaved per head), `.k_proj`, `.v_proj [KV D, hidden]`,
+    `.o_proj [hidden, H D]`, `.q_norm`, `.k_norm [D]`; linear-attention layers: `layers.i.linear_attn.in_proj_qkv
+    [2 Hk 128 + Hv 128, hidden]`, `.in_proj_z [Hv 128, hidden]`, `.in_proj_b`, `.in_proj_a [Hv, hidden]`, `.conv1d
+    [C, 1, taps]`, `.A_log`, `.dt_bias [Hv]` (f32), `.norm [128]`, `.out_proj [hidden, Hv 128]`.
+    `cfg`: any object with `num_hidden_layers`, `layer_type(i)` ("full_attention" / "linear_attention"),
+    `num_attention_heads`, `num_key_value_heads`, `head_dim`, `rms_norm_eps`, `rope_theta`, `rotary_dim`,
+    `linear_num_key_heads`, `linear_num_value_heads`.
+    `recurrence`: "chunked" (default; tensor cores, bf16 operands) or "exact" (f32, token-sequential) for the
+    linear-attention layers, see `LinearAttention`."""
+
+    def __init__(self, weights, cfg, max_positions: int = 8192, recurrence: str = "chunked"):
         self.cfg, self.w = cfg, weights
         dev = weights["embed_tokens"].device
         lin = lambda name: Linear(weights[name])
@@ -307,13 +323,13 @@ class Decoder:
                 a = p + "self_attn."
                 mixer = FullAttention(lin(a + "q_proj"), lin(a + "k_proj"), lin(a + "v_proj"), lin(a + "o_proj"),
                                       RmsNorm(weights[a + "q_norm"], cfg.rms_norm_eps), RmsNorm(weights[a + "k_norm"], cfg.rms_norm_eps),
-                                      cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, rope, core)
+                                      cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, rope)
             else:
                 a = p + "linear_attn."
                 mixer = LinearAttention(lin(a + "in_proj_qkv"), lin(a + "in_proj_z"), lin(a + "in_proj_b"), lin(a + "in_proj_a"),
                                         weights[a + "conv1d"], -torch.exp(weights[a + "A_log"].float()), weights[a + "dt_bias"].float(),
                                         weights[a + "norm"], lin(a + "out_proj"), cfg.linear_num_key_heads, cfg.linear_num_value_heads,
-                                        cfg.rms_norm_eps)
+                                        cfg.rms_norm_eps, recurrence=recurrence)
             self.layers.append(Layer(RmsNorm(weights[p + "input_layernorm"], cfg.rms_norm_eps), mixer,
                                      RmsNorm(weights[p + "post_attention_layernorm"], cfg.rms_norm_eps),
                                      Mlp(lin(p + "mlp.gate_proj"), lin(p + "mlp.up_proj"), lin(p + "mlp.down_proj"))))

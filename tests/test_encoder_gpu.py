@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _run(cfg, lens, seed):
+def _run(cfg, lens, seed, ids=None):
     w = oracle.init_weights(cfg, seed)
     g = torch.Generator().manual_seed(seed + 1)
     for k in w:  # norm weights away from 1 so that they matter
@@ -27,7 +27,8 @@ def _run(cfg, lens, seed):
             w[k] = w[k] + 0.1 * torch.randn(w[k].shape, generator=g)
     w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}  # both sides start from the same bf16 values
     b, _ = batching.pack_next(lens, batching.BatcherConfig(token_budget=1 << 20))
-    ids = torch.randint(0, cfg.vocab_size, (b.total_tokens,), generator=g)
+    if ids is None:
+        ids = torch.randint(0, cfg.vocab_size, (b.total_tokens,), generator=g)
     enc = modernbert.Encoder({k: v.to(torch.bfloat16).to(DEV) for k, v in w.items()}, cfg)
     y, states = enc.forward(ids.to(DEV), b.cu_seqlens, torch.from_numpy(b.positions).to(DEV), collect=True)
     out = {}

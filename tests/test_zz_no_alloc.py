@@ -73,6 +73,53 @@ def test_static_entry_point_matches_the_regular_one_twice():
             assert torch.equal(got, want)
 
 
+def test_static_entry_point_leaves_device_memory_as_it_found_it():
+    """The property the entry point is named for: once its one-time set-up has run, a call neither takes nor gives
+    back device memory. The driver's count of free bytes and PyTorch's own allocator are read before and after a
+    second round of calls (every tensor the calls touch exists before the first reading)."""
+    lib = _lib.load_library()
+    g = torch.Generator().manual_seed(7)
+    T, N, K = 4096, 768, 768
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    w2 = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    res = torch.randn(T, N, generator=g).to(torch.bfloat16).to(DEV)
+    y, yg = torch.empty(T, N, dtype=torch.bfloat16, device=DEV), torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
+
+    def calls():
+        for kw, out in ((dict(), y), (dict(residual=res), y), (dict(epilogue=EPI_GEGLU), yg), (dict(w_up=w2, epilogue=EPI_SWIGLU), y)):
+            rc, msg = _static(lib, w, x, out, **kw)
+            assert rc == _lib.S1_OK, msg
+
+    calls()  # first round: includes the per-device set-up and the loading of the kernels
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(0)
+    alloc0, reserved0 = torch.cuda.memory_allocated(0), torch.cuda.memory_reserved(0)
+    calls()
+    calls()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info(0)
+    assert free1 == free0
+    assert torch.cuda.memory_allocated(0) == alloc0 and torch.cuda.memory_reserved(0) == reserved0
+
+
+def test_static_entry_point_keeps_the_callers_device():
+    """With more than one GPU visible the call makes its device current only for its own duration."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    lib = _lib.load_library()
+    x = torch.randn(256, 64).to(torch.bfloat16).to(DEV)
+    w = torch.randn(64, 64).to(torch.bfloat16).to(DEV)
+    y = torch.empty(256, 64, dtype=torch.bfloat16, device=DEV)
+    torch.cuda.set_device(1)
+    try:
+        rc, msg = _static(lib, w, x, y)
+        assert rc == _lib.S1_OK, msg
+        assert torch.cuda.current_device() == 1
+    finally:
+        torch.cuda.set_device(0)
+
+
 def test_static_entry_point_rejects_what_it_does_not_cover():
     lib = _lib.load_library()
     x = torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV)
