@@ -155,10 +155,15 @@ class LinearAttention:
         self.recurrence = recurrence
         self.merged = None
         if merge_inputs and all(l.bias is None for l in (qkv, z, b, a)):
-            parts = [qkv.weight, z.weight, b.weight, a.weight]
+            # b and a are only `value_heads` rows each (6 on a tensor-parallel rank of the large model): padded with zero
+            # rows to a multiple of 8, the width the projection kernel stores in
+            def pad8(w):
+                extra = (-w.shape[0]) % 8
+                return w if extra == 0 else torch.cat([w, torch.zeros(extra, w.shape[1], dtype=w.dtype, device=w.device)], dim=0)
+            parts = [qkv.weight, z.weight, pad8(b.weight), pad8(a.weight)]
             if all(w.shape[0] % 8 == 0 for w in parts):
                 self.merged = Linear(torch.cat(parts, dim=0).contiguous())
-                self._splits = [w.shape[0] for w in parts]
+                self._splits = [(w.shape[0], n) for w, n in zip(parts, (qkv.weight.shape[0], z.weight.shape[0], b.weight.shape[0], a.weight.shape[0]))]
 
     def _inputs(self, x: torch.Tensor):
         """mixed-pre-conv, z, b, a: the four input projections of `x` (`project_and_mix` up to the conv, :515-526, :567-568)."""
@@ -166,13 +171,18 @@ class LinearAttention:
             return self.qkv.forward(x), self.z.forward(x), self.b.forward(x), self.a.forward(x)
         y = self.merged.forward(x)
         outs, at = [], 0
-        for n in self._splits:
+        for padded, n in self._splits:
             outs.append(y[:, at:at + n])
-            at += n
+            at += padded
         return tuple(outs)
 
     def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None,
                 inplace: bool = False) -> torch.Tensor:
+        y = self.mix(x, cu_seqlens_host, positions)
+        return self.output.forward(y, residual=residual, out=residual if inplace else None)  # out_proj (+ the layer's residual, :938)
+
+    def mix(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor) -> torch.Tensor:
+        """Everything up to the input of `out_proj`: `[T, value_heads * 128]` bf16."""
         import numpy as np
         ctx = device.load(x.device.index)
         T = x.shape[0]
@@ -191,7 +201,7 @@ class LinearAttention:
                 zz.stride(0), C.c_void_p(self.norm.data_ptr()), C.c_float(self.eps), cu.ctypes.data_as(C.POINTER(C.c_int32)),
                 len(cu) - 1, T, self.key_heads, self.value_heads, C.c_void_p(y.data_ptr()), y.stride(0), C.c_void_p(ptr), need)
             ctx.check(rc)
-        return self.output.forward(y, residual=residual, out=residual if inplace else None)  # out_proj (+ the layer's residual, :938)
+        return y
 
     def _exact(self, ctx, mixed, zz, bb, aa, cu, y) -> None:
         """The reference's own precision: `delta_inputs` -> token-sequential f32 recurrence -> `finish_delta`
@@ -267,6 +277,11 @@ class FullAttention:
 
     def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, residual: Optional[torch.Tensor] = None,
                 inplace: bool = False) -> torch.Tensor:
+        gated = self.mix(x, cu_seqlens_host, positions)
+        return self.output.forward(gated, residual=residual, out=residual if inplace else None)
+
+    def mix(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor) -> torch.Tensor:
+        """Everything up to the input of `o_proj`: the gated attention output `[T, heads * head_dim]` bf16."""
         T, H, KV, D = x.shape[0], self.heads, self.kv_heads, self.head_dim
         if self.merged is not None:
             qkv = self.merged.forward(x)                        # [T, H * 2 * D + 2 * KV * D]
@@ -278,8 +293,7 @@ class FullAttention:
         _norm.head_norm_rope_(qg, H, 2 * D, D, self.q_norm.weight, self.q_norm.eps, r.cos, r.sin, positions, r.rotary_dim)
         _norm.head_norm_rope_(k, KV, D, D, self.k_norm.weight, self.k_norm.eps, r.cos, r.sin, positions, r.rotary_dim)
         q4 = qg.unflatten(1, (H, 2, D))
-        gated = attention_causal_gqa(q4[:, :, 0], k.unflatten(1, (KV, D)), v.unflatten(1, (KV, D)), cu_seqlens_host, gate=q4[:, :, 1])
-        return self.output.forward(gated, residual=residual, out=residual if inplace else None)
+        return attention_causal_gqa(q4[:, :, 0], k.unflatten(1, (KV, D)), v.unflatten(1, (KV, D)), cu_seqlens_host, gate=q4[:, :, 1])
 
 
 class Layer:

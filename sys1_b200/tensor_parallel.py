@@ -59,7 +59,11 @@ class RowParallelLinear:
         previous slab can run beside them (a persistent grid over every SM would hold it back until it ends)."""
         self.weight, self.tp, self.slabs, self.comm_sms = weight_shard, tp, max(1, int(slabs)), int(comm_sms)
 
-    def forward(self, x_shard: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x_shard: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                exchange: bool = True) -> torch.Tensor:
+        """`out` may be `residual` (the replicated residual stream updated in place on every rank: rank 0 adds into it,
+        the other ranks overwrite it with their partial product, the sum over ranks restores `x + ...` everywhere).
+        `exchange=False` skips the sum (timing the local math alone)."""
         T, N = x_shard.shape[0], self.weight.shape[0]
         if out is None:
             out = torch.empty((T, N), dtype=torch.bfloat16, device=x_shard.device)
@@ -69,19 +73,19 @@ class RowParallelLinear:
         step = -(-T // self.slabs)
         step = max(128, -(-step // 128) * 128)  # whole 128-row tiles per slab
         ctx = self.tp.ctx
-        share = self.tp.size > 1 and self.comm_sms > 0 and T > step
+        share = exchange and self.tp.size > 1 and self.comm_sms > 0 and T > step
         try:
             for a in range(0, T, step):
                 b = min(T, a + step)
                 if share and a > 0:
                     ctx.set_option("gemm_sms", max(2, device.sm_count(ctx) - self.comm_sms))
                 fused_linear(x_shard[a:b], self.weight, residual=None if res is None else res[a:b], out=out[a:b], ctx=ctx)
-                if self.tp.size > 1:
+                if exchange and self.tp.size > 1:
                     ctx.all_reduce_(out[a:b], wait=False)
         finally:
             if share:
                 ctx.set_option("gemm_sms", 0)
-        if self.tp.size > 1:
+        if exchange and self.tp.size > 1:
             ctx.all_reduce_wait()
         return out
 
@@ -133,3 +137,128 @@ class Mlp:
         return out
 
     __call__ = forward
+
+
+# ------------------------------------------------------------------------------------------------ whole layers
+def local_heads(cfg, size: int):
+    """Head counts one rank of `size` owns: (query heads, KV heads, delta-rule key heads, delta-rule value heads).
+    Query heads and delta-rule value heads are split evenly; the delta-rule key heads follow their value heads (the
+    repeat factor `Hv / Hk` is the same on every rank, src/archs/qwen35_text.rs:552-559); with fewer KV heads than ranks
+    a rank holds the one KV head its query heads read (`repeat_kv`, :363-369) - KV heads are then replicated."""
+    H, KV, Hk, Hv = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    if H % size or Hk % size or Hv % size:
+        raise ValueError(f"{H} query / {Hk} key / {Hv} value heads do not split over {size} ranks")
+    Hr, group = H // size, H // KV
+    if KV % size == 0:
+        KVr = KV // size
+    elif group % Hr == 0:
+        KVr = 1
+    else:
+        raise ValueError(f"{KV} KV heads cannot serve {size} ranks of {Hr} query heads")
+    return Hr, KVr, Hk // size, Hv // size
+
+
+def shard_layer_weights(w, prefix: str, cfg, layer_type: str, rank: int, size: int):
+    """The tensors of one decoder layer as rank `rank` of `size` holds them, under the layer's own names (`prefix`
+    stripped): column-parallel projections are row ranges of the full matrices (heads, or matching gate / up columns),
+    row-parallel ones (`o_proj`, `out_proj`, `down_proj`) K ranges taken as strided views - the library reads them through
+    `ldw`, nothing is copied - and the per-head vectors (`A_log`, `dt_bias`, conv channels) follow their heads. Norm weights
+    are replicated. Works on any device (the shard arithmetic is checked on CPU against the oracle)."""
+    Hr, KVr, Hkr, Hvr = local_heads(cfg, size)
+    H, KV, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    Hk, Hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+    g = lambda name: w[prefix + name]
+    out = {"input_layernorm": g("input_layernorm"), "post_attention_layernorm": g("post_attention_layernorm")}
+    inter = g("mlp.gate_proj").shape[0]
+    if inter % size:
+        raise ValueError(f"intermediate size {inter} does not split over {size} ranks")
+    lo, hi = rank * inter // size, (rank + 1) * inter // size
+    out["mlp.gate_proj"], out["mlp.up_proj"] = g("mlp.gate_proj")[lo:hi], g("mlp.up_proj")[lo:hi]
+    out["mlp.down_proj"] = g("mlp.down_proj")[:, lo:hi]
+    if layer_type == "full_attention":
+        a = "self_attn."
+        kv0 = (rank * Hr) // (H // KV) if KV % size else rank * KVr   # first KV head this rank's query heads read
+        out[a + "q_proj"] = g(a + "q_proj")[rank * Hr * 2 * D:(rank + 1) * Hr * 2 * D]
+        out[a + "k_proj"] = g(a + "k_proj")[kv0 * D:(kv0 + KVr) * D]
+        out[a + "v_proj"] = g(a + "v_proj")[kv0 * D:(kv0 + KVr) * D]
+        out[a + "o_proj"] = g(a + "o_proj")[:, rank * Hr * D:(rank + 1) * Hr * D]
+        out[a + "q_norm"], out[a + "k_norm"] = g(a + "q_norm"), g(a + "k_norm")
+    else:
+        a = "linear_attn."
+        kq = slice(rank * Hkr * 128, (rank + 1) * Hkr * 128)
+        kk = slice(Hk * 128 + rank * Hkr * 128, Hk * 128 + (rank + 1) * Hkr * 128)
+        vv = slice(2 * Hk * 128 + rank * Hvr * 128, 2 * Hk * 128 + (rank + 1) * Hvr * 128)
+        hv = slice(rank * Hvr, (rank + 1) * Hvr)
+        cat = lambda t: torch.cat([t[kq], t[kk], t[vv]], dim=0)
+        out[a + "in_proj_qkv"] = cat(g(a + "in_proj_qkv"))
+        out[a + "conv1d"] = cat(g(a + "conv1d"))
+        out[a + "in_proj_z"] = g(a + "in_proj_z")[rank * Hvr * 128:(rank + 1) * Hvr * 128]
+        out[a + "in_proj_b"], out[a + "in_proj_a"] = g(a + "in_proj_b")[hv], g(a + "in_proj_a")[hv]
+        out[a + "A_log"], out[a + "dt_bias"] = g(a + "A_log")[hv], g(a + "dt_bias")[hv]
+        out[a + "norm"] = g(a + "norm")
+        out[a + "out_proj"] = g(a + "out_proj")[:, rank * Hvr * 128:(rank + 1) * Hvr * 128]
+    return out
+
+
+class Layer:
+    """One decoder layer (`Layer::forward`, src/archs/qwen35_text.rs:932-940) under tensor parallelism: every rank runs
+    the mixer and the MLP on its own heads / columns (`sys1_b200.qwen35.FullAttention` / `LinearAttention` built from this
+    rank's shard, `Mlp` above), and the two row-parallel projections (`o_proj` / `out_proj`, `down_proj`) are followed by
+    the sum over ranks. The residual stream is replicated; rank 0 adds it in its projection epilogue, so that the sum
+    over ranks is `x + sum_r partial_r`. `forward` updates `x` in place on every rank."""
+
+    def __init__(self, shard, cfg, layer_type: str, tp: TensorParallel, rope, slabs: int = 4, comm_sms: int = 16, recurrence: str = "chunked"):
+        from . import qwen35
+        from .linear import Linear
+        Hr, KVr, Hkr, Hvr = local_heads(cfg, tp.size)
+        lin = lambda name: Linear(shard[name])
+        eps = cfg.rms_norm_eps
+        self.tp = tp
+        self.input_norm = qwen35.RmsNorm(shard["input_layernorm"], eps)
+        self.post_norm = qwen35.RmsNorm(shard["post_attention_layernorm"], eps)
+        if layer_type == "full_attention":
+            a = "self_attn."
+            self.mixer = qwen35.FullAttention(lin(a + "q_proj"), lin(a + "k_proj"), lin(a + "v_proj"), lin(a + "o_proj"),
+                                              qwen35.RmsNorm(shard[a + "q_norm"], eps), qwen35.RmsNorm(shard[a + "k_norm"], eps),
+                                              Hr, KVr, cfg.head_dim, rope)
+        else:
+            a = "linear_attn."
+            self.mixer = qwen35.LinearAttention(lin(a + "in_proj_qkv"), lin(a + "in_proj_z"), lin(a + "in_proj_b"), lin(a + "in_proj_a"),
+                                                shard[a + "conv1d"].contiguous(), -torch.exp(shard[a + "A_log"].float()),
+                                                shard[a + "dt_bias"].float(), shard[a + "norm"], lin(a + "out_proj"), Hkr, Hvr, eps,
+                                                recurrence=recurrence)
+        self.mixer_out = RowParallelLinear(self.mixer.output.weight, tp, slabs=slabs, comm_sms=comm_sms)
+        self.mlp = Mlp(shard["mlp.gate_proj"], shard["mlp.up_proj"], shard["mlp.down_proj"], tp, slabs=slabs, sharded=True, comm_sms=comm_sms)
+
+    def forward(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, exchange: bool = True) -> torch.Tensor:
+        y = self.mixer.mix(self.input_norm(x), cu_seqlens_host, positions)
+        self.mixer_out.forward(y, residual=x, out=x, exchange=exchange)       # x <- x + sum_r y_r W_r^T
+        n = self.post_norm(x)
+        self.mlp.forward(n, residual=x, out=x, exchange=exchange)             # x <- x + sum_r mlp_r(n)
+        return x
+
+
+class Decoder:
+    """A stack of tensor-parallel layers over a packed batch (`Decoder::forward_embeds`, src/archs/qwen35_text.rs:986-1005,
+    from the embedded tokens to the final norm). `weights`: the FULL tensors under the checkpoint's names (see
+    `sys1_b200.qwen35.Decoder`); every rank cuts its own shards out of them."""
+
+    def __init__(self, weights, cfg, tp: TensorParallel, max_positions: int = 8192, slabs: int = 4, comm_sms: int = 16,
+                 recurrence: str = "chunked"):
+        from . import qwen35
+        dev = weights["norm"].device
+        rope = qwen35.RopeParams(cfg.rope_theta, cfg.rotary_dim, max_positions, dev)
+        self.cfg, self.tp = cfg, tp
+        self.layers = []
+        for i in range(cfg.num_hidden_layers):
+            kind = cfg.layer_type(i)
+            shard = shard_layer_weights(weights, f"layers.{i}.", cfg, kind, tp.rank, tp.size)
+            self.layers.append(Layer(shard, cfg, kind, tp, rope, slabs=slabs, comm_sms=comm_sms, recurrence=recurrence))
+        self.norm = qwen35.RmsNorm(weights["norm"], cfg.rms_norm_eps)
+
+    def forward_embeds(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, exchange: bool = True) -> torch.Tensor:
+        """`x [T, hidden]` bf16: the embedded tokens, identical on every rank; it is updated in place layer by layer."""
+        pos = positions.to(torch.int32).contiguous()
+        for layer in self.layers:
+            x = layer.forward(x, cu_seqlens_host, pos, exchange=exchange)
+        return self.norm(x)

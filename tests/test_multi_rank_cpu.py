@@ -58,11 +58,73 @@ def _worker(rank, world, port, q):
         got = oracle.geglu(oracle.linear(x, shard, dtype="f32"), dtype="f32")
         full = oracle.geglu(oracle.linear(x, wi, dtype="f32"), dtype="f32")
         assert torch.allclose(got, full[:, rank * I // world:(rank + 1) * I // world], atol=1e-6)
+        # a whole (linear-attention, full-attention) pair of layers: this rank's shard through the oracle, summed over ranks
+        _check_layer_shards(world, [rank], reduce=device.all_reduce_sum_)
         q.put((rank, "ok"))
     except Exception as exc:  # pragma: no cover
         q.put((rank, repr(exc)))
     finally:
         dist.destroy_process_group()
+
+
+def _tp_cfg():
+    # the 27B head pattern (24 query / 4 KV heads, 16 key / 48 value delta-rule heads) at a small width
+    return oracle.DecoderConfig(vocab_size=50, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=24,
+                                num_key_value_heads=4, head_dim=32, partial_rotary_factor=0.5, linear_num_key_heads=16,
+                                linear_num_value_heads=48)
+
+
+def _check_layer_shards(world, ranks, reduce=None):
+    """Mixer and MLP of a linear-attention layer (index 0) and a full-attention layer (index 3): the oracle run on each
+    rank's shard (a layer of a narrower model), partial outputs summed over the ranks, against the oracle on the full layer."""
+    import dataclasses
+    from sys1_b200 import tensor_parallel as tpar
+    cfg = _tp_cfg()
+    w = oracle.qwen35.init_weights(cfg, 7)
+    Hr, KVr, Hkr, Hvr = tpar.local_heads(cfg, world)
+    cfg_r = dataclasses.replace(cfg, num_attention_heads=Hr, num_key_value_heads=KVr, linear_num_key_heads=Hkr, linear_num_value_heads=Hvr)
+    x = torch.randn(37, cfg.hidden_size, generator=torch.Generator().manual_seed(3))
+    for i in (0, 3):
+        kind = cfg.layer_type(i)
+        p = f"layers.{i}."
+        n = oracle.rms_norm(x, w[p + "input_layernorm"], cfg.rms_norm_eps)
+        if kind == "full_attention":
+            full = oracle.qwen35.full_attention(n, w, p + "self_attn.", cfg)
+        else:
+            full = oracle.qwen35.linear_attention(n, w, p + "linear_attn.", cfg)
+        full_mlp = oracle.mlp_qwen35(n, w[p + "mlp.gate_proj"], w[p + "mlp.up_proj"], w[p + "mlp.down_proj"], dtype="f32")
+        part, part_mlp = torch.zeros_like(full), torch.zeros_like(full_mlp)
+        for r in ranks:
+            sh = tpar.shard_layer_weights(w, p, cfg, kind, r, world)
+            if kind == "full_attention":
+                part += oracle.qwen35.full_attention(n, sh, "self_attn.", cfg_r)
+            else:
+                part += oracle.qwen35.linear_attention(n, sh, "linear_attn.", cfg_r)
+            part_mlp += oracle.mlp_qwen35(n, sh["mlp.gate_proj"], sh["mlp.up_proj"], sh["mlp.down_proj"], dtype="f32")
+            assert sh["mlp.down_proj"].stride(0) == cfg.intermediate_size  # a view of the full matrix, read through its row stride
+        if reduce is not None:
+            part, part_mlp = reduce(part), reduce(part_mlp)
+        assert torch.allclose(part, full, atol=2e-5), f"{kind} over {world} ranks: {float((part - full).abs().max()):.2e}"
+        assert torch.allclose(part_mlp, full_mlp, atol=2e-5)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_layer_shards_sum_to_the_unsharded_layer(world):
+    """All ranks emulated in one process: query heads with the KV head they read (replicated when there are fewer KV
+    heads than ranks), delta-rule value heads with their key heads, conv channels, A_log / dt_bias slices, gate / up
+    columns, and the K ranges of the three row-parallel projections."""
+    _check_layer_shards(world, list(range(world)))
+
+
+def test_local_heads_of_the_27b_shape():
+    from types import SimpleNamespace
+    from sys1_b200 import tensor_parallel as tpar
+    cfg = SimpleNamespace(num_attention_heads=24, num_key_value_heads=4, linear_num_key_heads=16, linear_num_value_heads=48)
+    assert tpar.local_heads(cfg, 8) == (3, 1, 2, 6)
+    assert tpar.local_heads(cfg, 4) == (6, 1, 4, 12)
+    assert tpar.local_heads(cfg, 2) == (12, 2, 8, 24)
+    with pytest.raises(ValueError):
+        tpar.local_heads(cfg, 16)
 
 
 @pytest.mark.timeout(120)
