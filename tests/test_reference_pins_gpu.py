@@ -43,8 +43,9 @@ def test_windowed_attention_reference_inputs(ctx):
 
 
 def test_local_mask_only_exposes_nearby_tokens(ctx):
-    """The property `local_attention_mask` states (:1408-1422): with window w a query's output does not change, bit for
-    bit, when keys and values farther than w are replaced."""
+    """The property `local_attention_mask` states (:1408-1422): with window w a query's output does not depend on keys
+    and values farther than w. (Not bit for bit: the kernel rescales its accumulator when ANY row of a warp has seen its
+    maximum grow, so a neighbour row's band can move the reference point a row's probabilities are rounded against.)"""
     g = torch.Generator().manual_seed(3)
     L, H, w = 300, 2, 64
     q, k, v = (torch.randn(L, H, 64, generator=g).to(torch.bfloat16).to(DEV) for _ in range(3))
@@ -56,8 +57,9 @@ def test_local_mask_only_exposes_nearby_tokens(ctx):
     k2[far] = 9.0
     v2[far] = -7.0
     moved = modernbert.attention_varlen(q, k2, v2, cu, window=w)
-    assert torch.equal(base[i], moved[i])
-    assert not torch.equal(base[i + w + 5], moved[i + w + 5])
+    scale = float(base[i].float().abs().max())
+    assert float((base[i].float() - moved[i].float()).abs().max()) <= 2 ** -7 * scale
+    assert float((base[i + w + 5].float() - moved[i + w + 5].float()).abs().max()) > 0.5   # that row does see replaced keys
     ctx.sync()
 
 
