@@ -427,13 +427,14 @@ def tp_block(args, rank, world, dev, steps, warmup):
 
     # ---- parity on a small batch: sharded against unsharded on this GPU; all ranks bit-identical
     pb, px, ppos = batch_of(2048, 2005)
-    y_tp = dec.forward_embeds(px.clone(), pb.cu_seqlens, ppos)
+    y_tp = dec.forward_embeds(px.clone(), pb.cu_seqlens, ppos, micro_batches=args.micro_batches if world > 1 else 1)
     ctx.sync()
     single = qwen35.Decoder({**w, "embed_tokens": px}, cfg)      # the embedded tokens stand in for the table: ids = arange
     y_one = single.forward(torch.arange(2048, device=dev, dtype=torch.int32), pb.cu_seqlens, ppos)
     ctx.sync()
     scale = float(y_one.float().abs().max())
     max_rel = float((y_tp.float() - y_one.float()).abs().max()) / scale
+    rel_rms = float((y_tp.float() - y_one.float()).square().mean().sqrt() / y_one.float().square().mean().sqrt())
     digest = y_tp.view(torch.int16).to(torch.int64).sum().reshape(1)
     same = True
     if world > 1:
@@ -446,21 +447,29 @@ def tp_block(args, rank, world, dev, steps, warmup):
     T = args.tp_tokens
     b, x0, pos = batch_of(T, 1005)
     x = torch.empty_like(x0)
-    if args.tp_pdl >= 0:
-        ctx.set_option("pdl", args.tp_pdl)
-
-    def step(exchange=True):
-        x.copy_(x0)   # the stream is updated in place; the copy is part of neither variant's difference
-        dec.forward_embeds(x, b.cu_seqlens, pos, exchange=exchange)
-
-    for _ in range(warmup):
-        step()
-    ctx.sync()
-    l0 = ctx.launch_count()
-    ms = _timed(step, steps, world, dev)
-    launches = ctx.launch_count() - l0
-    ms_math = _timed(lambda: step(False), steps, world, dev)
+    mbs = args.micro_batches if world > 1 else 1
     n_ar = 2 * cfg.num_hidden_layers
+
+    def measure(decoder, micro_batches, pdl, n_steps):
+        ctx.set_option("pdl", pdl)
+
+        def step(exchange=True):
+            x.copy_(x0)   # the stream is updated in place; the copy is part of neither variant's difference
+            decoder.forward_embeds(x, b.cu_seqlens, pos, exchange=exchange, micro_batches=micro_batches)
+
+        for _ in range(warmup):
+            step()
+        ctx.sync()
+        l0 = ctx.launch_count()
+        ms_ = _timed(step, n_steps, world, dev)
+        launches_ = ctx.launch_count() - l0
+        ms_math_ = _timed(lambda: step(False), n_steps, world, dev)
+        ctx.sync()
+        ctx.set_option("pdl", 1)
+        return ms_, ms_math_, launches_
+
+    pdl = 1 if args.tp_pdl < 0 else args.tp_pdl
+    ms, ms_math, launches = measure(dec, mbs, pdl, steps)
     ms_ar = 0.0
     if world > 1:
         def bare():
@@ -469,21 +478,34 @@ def tp_block(args, rank, world, dev, steps, warmup):
         bare()
         ms_ar = _timed(bare, max(2, steps // 2), world, dev)
     ctx.sync()
-    ctx.set_option("pdl", 1)
+    sweep = None
+    if args.tp_sweep and world > 1:
+        sweep = []
+        for comm_sms in (8, 16, 32):
+            d2 = tensor_parallel.Decoder(w, cfg, tp, slabs=args.slabs, comm_sms=comm_sms)
+            for m in (1, 2, 4):
+                for p_ in (0, 1):
+                    a_, b_, _ = measure(d2, m, p_, 3)
+                    sweep.append({"comm_sms": comm_sms, "micro_batches": m, "pdl": p_, "ms": a_, "ms_without_exchange": b_,
+                                  "hidden_frac": 1.0 - (a_ - b_) / ms_ar if ms_ar > 0 else None})
+            del d2
     flops = T * (3 * 766_443_520 + 744_488_960)   # projection flops of the group (three linear-attention + one full layer)
     bytes_ar = n_ar * T * H * 2
     return {"metric": "tensor-parallel layer-group TFLOP/s", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
             "steps": steps, "scaling": "strong",
             "config": {"workload": f"27B-shaped (linear, linear, linear, full) layer group, packed T={T}, lengths U[256,8192], "
-                                   f"tensor parallel x{world}; row-parallel outputs exchanged in {args.slabs} row slabs, "
-                                   f"{args.comm_sms} SMs left to the exchange ({args.comm_ctas or 'default'} blocks)",
+                                   f"tensor parallel x{world}; " +
+                                   (f"{mbs} micro-batches of whole sequences alternate between computing and exchanging their partial sums"
+                                    if mbs > 1 else f"row-parallel outputs exchanged in {args.slabs} row slabs") +
+                                   f", {args.comm_sms} SMs left to the exchange ({args.comm_ctas or 'default'} blocks)",
                        "sequences": int(b.num_sequences), "parallelism": f"tp{world}"},
             "ms_without_exchange": ms_math, "ms_allreduce_alone": ms_ar, "allreduces_per_step": n_ar if world > 1 else 0,
             "allreduce_busbw_gbs": (2.0 * (world - 1) / world * bytes_ar / (ms_ar * 1e-3) / 1e9) if world > 1 and ms_ar > 0 else None,
             "exchange_hidden_frac": (1.0 - (ms - ms_math) / ms_ar) if world > 1 and ms_ar > 0 else None,
-            "parity": {"tokens": 2048, "max_rel_vs_unsharded": max_rel, "ranks_bit_identical": bool(same), "bound": 3e-2,
-                       "ok": bool(same and max_rel <= 3e-2)},
-            "gpu_launches": launches}
+            "parity": {"tokens": 2048, "max_rel_vs_unsharded": max_rel, "rel_rms_vs_unsharded": rel_rms, "ranks_bit_identical": bool(same),
+                       "bound_max_rel": 5e-2, "bound_rel_rms": 1e-2, "ok": bool(same and max_rel <= 5e-2 and rel_rms <= 1e-2),
+                       "note": "two bf16 evaluations of four layers (per-rank partial sums are rounded to bf16 before they are added)"},
+            "gpu_launches": launches, **({"sweep": sweep} if sweep is not None else {})}
 
 
 # ================================================================================================ main workload
@@ -794,9 +816,20 @@ def main():
     ap.add_argument("--comm-ctas", type=int, default=0, help="tp: blocks the all-reduce may use (0 = NCCL's default)")
     ap.add_argument("--comm-sms", type=int, default=16, help="tp: SMs the projections leave to the exchange of the previous slab")
     ap.add_argument("--tp-pdl", type=int, default=-1, help="tp: 0 / 1 turns programmatic dependent launch of the projections off / on (-1: default)")
+    ap.add_argument("--micro-batches", type=int, default=2, help="tp: groups of whole sequences that alternate between computing and exchanging (1: row slabs inside each projection instead)")
+    ap.add_argument("--tp-sweep", action="store_true", help="tp: also time the group for a grid of comm-sms x micro-batches x pdl settings")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step from a CUDA graph (for small token budgets, where launching from Python is the bottleneck)")
     args = ap.parse_args()
+    # stdout carries the one JSON line and nothing else: whatever libraries print (NCCL's version banner, for one) goes
+    # to stderr from here on
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line):
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -805,7 +838,7 @@ def main():
     if args.impl == "reference":
         if rank != 0:  # rank 0 alone runs the CPU arm; the other ranks leave without work
             return
-        print(json.dumps(reference_line(args, warmup)))
+        emit(reference_line(args, warmup))
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: there is no CPU fallback for the product path (use --impl reference for the CPU arm)")
@@ -830,7 +863,7 @@ def main():
                         "data": "synthetic"}
                 line.update(block)
         if rank == 0 and line is not None:
-            print(json.dumps(line))
+            emit(line)
     finally:
         if world > 1:
             torch.distributed.barrier()

@@ -253,6 +253,16 @@ int s1_norm(s1_ctx* ctx, const void* x, long long ldx, const int32_t* gather, in
             const void* bias, float eps, int kind, void* y, long long ldy, long long rows, int width);
 
 /*
+ * y[r, :] = bf16(x[r, :] + table[index[r], :]): a row of a small table added to every row of x, chosen by a DEVICE
+ * int32 index [rows]. The type-embedding add of the decision model (`hidden.broadcast_add(type_ids.apply(&type_embedding))`,
+ * src/models/laya.rs:431) on the packed layout: index[r] is the question kind of the sequence token r belongs to.
+ * x, y: bf16 [rows, width] (y may be x); table: bf16 [table_rows, width]. An index outside the table is reported by
+ * s1_sync as S1_EKERNEL (that row is left unwritten).
+ */
+int s1_add_rows(s1_ctx* ctx, const void* x, long long ldx, const void* table, long long ldt, const int32_t* index,
+                int table_rows, void* y, long long ldy, long long rows, int width);
+
+/*
  * Rotate-half rotary embedding, in place, on `heads` consecutive heads of every token row:
  *     lo' = lo * cos - hi * sin,  hi' = lo * sin + hi * cos     for the column pairs (j, j + rotary_dim / 2)
  * of the first `rotary_dim` columns of each head; the rest of the head is left as it is. x: bf16 [T, ldx], head h
@@ -295,6 +305,10 @@ int s1_head_norm_rope(s1_ctx* ctx, void* x, long long ldx, long long head_stride
  *                       context's own, after everything queued on the context's stream so far; returns at once.
  *                       Called slab by slab it overlaps the exchange of one slab with the projection of the next.
  *   s1_allreduce_wait : orders the context's stream after every all-reduce issued so far (no host blocking)
+ *   s1_allreduce_ticket / s1_allreduce_wait_ticket : the sequence number of the all-reduce issued last (1, 2, ...), and
+ *                       the wait for one of them only: the context's stream is ordered after that all-reduce and not
+ *                       after the ones issued later, so that two micro-batches can alternate - one computes while the
+ *                       other's sum travels
  *   s1_comm_destroy   : also done by s1_ctx_destroy
  * Every rank must issue the same sequence of all-reduces with the same counts.
  */
@@ -304,6 +318,8 @@ int s1_comm_init(s1_ctx* ctx, const void* id, int rank, int size);
 int s1_comm_destroy(s1_ctx* ctx);
 int s1_allreduce_bf16(s1_ctx* ctx, void* buf, size_t count);
 int s1_allreduce_wait(s1_ctx* ctx);
+long long s1_allreduce_ticket(const s1_ctx* ctx);
+int s1_allreduce_wait_ticket(s1_ctx* ctx, long long ticket);
 
 /*
  * s1_linear followed by s1_rope on the first `rotated_heads` heads (64 columns each) of the output, the rotation done

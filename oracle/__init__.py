@@ -31,3 +31,4 @@ from .modernbert import (EncoderConfig, attention, attention_softmax, eager_atte
                          global_attention_mask, init_weights, local_attention_mask, windowed_attention)
 from .qwen35 import DecoderConfig, causal_attention, decoder_forward, decoder_layer  # noqa: F401,E402
 from . import qwen35  # noqa: F401,E402
+from . import laya  # noqa: F401,E402

@@ -79,10 +79,14 @@ SIGNATURES = {
     "s1_comm_destroy": (C.c_int, [C.c_void_p]),
     "s1_allreduce_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "s1_allreduce_wait": (C.c_int, [C.c_void_p]),
+    "s1_allreduce_ticket": (C.c_longlong, [C.c_void_p]),
+    "s1_allreduce_wait_ticket": (C.c_int, [C.c_void_p, C.c_longlong]),
     "s1_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
                           C.c_longlong, C.c_longlong, C.c_int]),
     "s1_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                           C.c_longlong, C.c_int]),
+    "s1_add_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_void_p, C.c_int, C.c_void_p,
+                              C.c_longlong, C.c_longlong, C.c_int]),
     "s1_selftest_bounded_wait": (C.c_int, [C.c_void_p]),
     "s1_head_norm_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_float,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]),

@@ -103,6 +103,7 @@ extern "C" int s1_comm_init(s1_ctx* ctx, const void* id, int rank, int size) {
     cudaError_t e = cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, prio_high);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_ready, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming);
+    for (int i = 0; i < s1_ctx::kCommTickets && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&ctx->comm_ticket[i], cudaEventDisableTiming);
     if (e != cudaSuccess) {
         api->CommDestroy(comm);
         return s1_fail(ctx, S1_ECUDA, "s1_comm_init: %s", cudaGetErrorString(e));
@@ -122,6 +123,8 @@ extern "C" int s1_comm_destroy(s1_ctx* ctx) {
     nccl_api()->CommDestroy(static_cast<ncclComm_t>(ctx->comm));
     cudaEventDestroy(ctx->comm_ready);
     cudaEventDestroy(ctx->comm_done);
+    for (int i = 0; i < s1_ctx::kCommTickets; ++i)
+        if (ctx->comm_ticket[i]) cudaEventDestroy(ctx->comm_ticket[i]), ctx->comm_ticket[i] = nullptr;
     cudaStreamDestroy(ctx->comm_stream);
     ctx->comm = nullptr;
     ctx->comm_stream = nullptr;
@@ -148,7 +151,24 @@ extern "C" int s1_allreduce_bf16(s1_ctx* ctx, void* buf, size_t count) {
         return s1_fail(ctx, S1_ECUDA, "ncclAllReduce failed: %s", api->GetErrorString(rc));
     }
     S1_CUDA_OK(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
+    ctx->comm_issued += 1;
+    S1_CUDA_OK(ctx, cudaEventRecord(ctx->comm_ticket[ctx->comm_issued % s1_ctx::kCommTickets], ctx->comm_stream));
     ctx->comm_pending = true;
+    return S1_OK;
+}
+
+extern "C" long long s1_allreduce_ticket(const s1_ctx* ctx) { return ctx ? ctx->comm_issued : 0; }
+
+extern "C" int s1_allreduce_wait_ticket(s1_ctx* ctx, long long ticket) {
+    if (!ctx) return S1_EINVAL;
+    if (!ctx->comm) return s1_fail(ctx, S1_EINVAL, "s1_allreduce_wait_ticket: the context has no communicator (s1_comm_init)");
+    if (ticket < 1 || ticket > ctx->comm_issued)
+        return s1_fail(ctx, S1_EINVAL, "s1_allreduce_wait_ticket: ticket %lld was never issued (last: %lld)", ticket, ctx->comm_issued);
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    // a ticket older than the ring has been overwritten by a later all-reduce of the same (in-order) stream: waiting for
+    // that later one covers it
+    const long long t = (ctx->comm_issued - ticket >= s1_ctx::kCommTickets) ? ctx->comm_issued : ticket;
+    S1_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->comm_ticket[t % s1_ctx::kCommTickets], 0));
     return S1_OK;
 }
 

@@ -54,6 +54,9 @@ struct s1_ctx {
     void* comm = nullptr;                     // ncclComm_t once s1_comm_init has run
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t comm_ready = nullptr, comm_done = nullptr;
+    static constexpr int kCommTickets = 64;
+    cudaEvent_t comm_ticket[kCommTickets] = {};  // completion of the all-reduce with sequence number n sits in slot n % 64
+    long long comm_issued = 0;                // all-reduces issued so far (the last one's ticket)
     int comm_rank = 0, comm_size = 0;
     bool comm_pending = false;
     bool comm_blocking = true;                // false: created with a deadline (non-blocking NCCL communicator)

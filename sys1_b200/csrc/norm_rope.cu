@@ -307,6 +307,35 @@ __global__ void __launch_bounds__(256) s1_head_norm_rope_kernel(__nv_bfloat16* _
     *reinterpret_cast<uint4*>(ptr) = normed;
 }
 
+// ------------------------------------------------------------------------------------------- indexed row add
+// y[r, :] = bf16(x[r, :] + table[index[r], :]): one thread per 8 columns.
+__global__ void __launch_bounds__(256) s1_add_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                         const __nv_bfloat16* __restrict__ table, long long ldt,
+                                                         const int32_t* __restrict__ index, int table_rows,
+                                                         __nv_bfloat16* __restrict__ y, long long ldy, long long rows, int width,
+                                                         int* __restrict__ status) {
+    const int groups = width / 8;
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= rows * groups) return;
+    const long long r = idx / groups;
+    const int c = static_cast<int>(idx % groups) * 8;
+    const int id = index[r];
+    if (id < 0 || id >= table_rows) {
+        if (atomicCAS(status, 0, 101) == 0) {
+            status[1] = static_cast<int>(blockIdx.x);
+            status[2] = static_cast<int>(r);
+            status[3] = id;
+        }
+        return;
+    }
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + r * ldx + c), a);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(table + static_cast<long long>(id) * ldt + c)), b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] += b[e];
+    *reinterpret_cast<uint4*>(y + r * ldy + c) = pack8(a);
+}
+
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -386,6 +415,24 @@ extern "C" int s1_head_norm_rope(s1_ctx* ctx, void* x, long long ldx, long long 
     else if (lpr == 16) S1_HNR(16);
     else S1_HNR(32);
 #undef S1_HNR
+    S1_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return S1_OK;
+}
+
+extern "C" int s1_add_rows(s1_ctx* ctx, const void* x, long long ldx, const void* table, long long ldt, const int32_t* index,
+                           int table_rows, void* y, long long ldy, long long rows, int width) {
+    if (!ctx) return S1_EINVAL;
+    if (!x || !table || !index || !y) return s1_fail(ctx, S1_EINVAL, "s1_add_rows: null pointer");
+    if (rows < 0 || table_rows < 1 || width < 8 || (width % 8)) return s1_fail(ctx, S1_EINVAL, "s1_add_rows: width must be a multiple of 8");
+    if ((ldx % 8) || (ldy % 8) || (ldt % 8) || ldx < width || ldy < width || ldt < width || !al16(x) || !al16(y) || !al16(table))
+        return s1_fail(ctx, S1_EINVAL, "s1_add_rows: rows must be 16-byte aligned, ld >= width");
+    if (rows == 0) return S1_OK;
+    S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    const long long n = rows * (width / 8);
+    s1_add_rows_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
+        static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(table), ldt, index, table_rows,
+        static_cast<__nv_bfloat16*>(y), ldy, rows, width, ctx->status_dev);
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return S1_OK;

@@ -98,6 +98,15 @@ class Context:
     def all_reduce_wait(self) -> None:
         self.check(self._lib.s1_allreduce_wait(self.handle))
 
+    def all_reduce_async_(self, t: torch.Tensor) -> int:
+        """Issues the in-place sum over the ranks and returns its ticket; the context's stream is not held back.
+        `all_reduce_wait_ticket(ticket)` orders the stream after this sum alone (later ones may still be in flight)."""
+        self.all_reduce_(t, wait=False)
+        return int(self._lib.s1_allreduce_ticket(self.handle))
+
+    def all_reduce_wait_ticket(self, ticket: int) -> None:
+        self.check(self._lib.s1_allreduce_wait_ticket(self.handle, int(ticket)))
+
     def close(self) -> None:
         if getattr(self, "_h", None) is not None:
             self._lib.s1_ctx_destroy(self._h)

@@ -88,3 +88,47 @@ class Scorer:
             out.append(flat[at:at + n])
             at += n
         return out
+
+
+class HeadLayer:
+    """`HeadLayer` (src/models/laya.rs:56-158), a pre-norm transformer layer with biased Linears and a ReLU feed-forward of
+    4 x hidden, on the packed layout. Same member names: `qkv` (`self_attn.in_proj_weight / _bias`), `projection`
+    (`self_attn.out_proj`), `norm1`, `norm2` (LayerNorm with bias, eps 1e-5), `linear1`, `linear2`; heads of 64.
+        x = x + projection(attention(qkv(norm1(x))));   x = x + linear2(relu(linear1(norm2(x))))
+    The reference masks padded keys with -inf (:411-424); a packed batch has none, so the attention is `s1_attention`
+    over each sequence's own tokens. Bias, ReLU and both residual adds ride in the projections' epilogues."""
+
+    def __init__(self, qkv: Linear, projection: Linear, norm1, norm2, linear1: Linear, linear2: Linear, eps: float = 1e-5):
+        self.qkv, self.projection, self.linear1, self.linear2 = qkv, projection, linear1, linear2
+        self.norm1, self.norm2, self.eps = norm1, norm2, float(eps)   # (weight, bias) pairs
+        self.heads = qkv.weight.shape[1] // 64
+
+    def forward(self, x: torch.Tensor, cu_seqlens_host) -> torch.Tensor:
+        from .modernbert import attention_varlen
+        T, hidden = x.shape
+        n = _norm.norm(x, self.norm1[0], self.eps, _norm.LAYER_NORM, bias=self.norm1[1])
+        qkv = self.qkv.forward(n).view(T, 3, self.heads, 64)
+        attn = attention_varlen(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu_seqlens_host, window=-1)
+        x = self.projection.forward(attn, residual=x)
+        n = _norm.norm(x, self.norm2[0], self.eps, _norm.LAYER_NORM, bias=self.norm2[1])
+        return self.linear2.forward(self.linear1.forward(n, act="relu"), residual=x)
+
+
+class DecisionHead:
+    """What `Laya::forward` runs after the encoder (src/models/laya.rs:431-441) on a packed batch: the type embedding of
+    each sequence's question kind added to all its tokens, the `HeadLayer`s, then the scorer at the marker rows."""
+
+    def __init__(self, type_embedding: torch.Tensor, layers: Sequence[HeadLayer], scorer: Scorer):
+        self.type_embedding, self.layers, self.scorer = type_embedding.contiguous(), list(layers), scorer
+
+    def forward(self, hidden: torch.Tensor, cu_seqlens_host, kinds: Sequence[int], markers: Sequence[Sequence[int]]) -> List[List[float]]:
+        """hidden bf16 `[T, hidden]` (the encoder's output, packed), `kinds[s]` the question kind of sequence s, `markers[s]`
+        its marker positions. Returns one list of logits per sequence."""
+        cu = np.asarray(cu_seqlens_host, dtype=np.int64)
+        if len(kinds) != len(cu) - 1:
+            raise ValueError("one question kind per sequence")
+        per_token = np.repeat(np.asarray(kinds, dtype=np.int32), np.diff(cu))
+        x = _norm.add_rows(hidden, self.type_embedding, torch.from_numpy(per_token).to(hidden.device))
+        for layer in self.layers:
+            x = layer.forward(x, cu_seqlens_host)
+        return self.scorer.score_packed(x, cu_seqlens_host, markers)

@@ -93,6 +93,25 @@ def head_norm_rope_(x: torch.Tensor, heads: int, head_stride: int, head_dim: int
     return x
 
 
+def add_rows(x: torch.Tensor, table: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`x + table[index]` row by row through `s1_add_rows` (`hidden.broadcast_add(type_ids.apply(&type_embedding))`,
+    src/models/laya.rs:431, with one index per packed token). `out` may be `x`."""
+    _rows(x, "x")
+    _rows(table, "table")
+    if not index.is_cuda or index.dtype != torch.int32 or not index.is_contiguous() or index.numel() != x.shape[0]:
+        raise ValueError("index must be a contiguous int32 CUDA vector with one entry per row")
+    if out is None:
+        out = torch.empty_like(x)
+    _rows(out, "out")
+    if x.shape[0] == 0:
+        return out
+    ctx = device.load(x.device.index)
+    ctx.check(ctx._lib.s1_add_rows(ctx.handle, C.c_void_p(x.data_ptr()), x.stride(0), C.c_void_p(table.data_ptr()), table.stride(0),
+                                   C.c_void_p(index.data_ptr()), table.shape[0], C.c_void_p(out.data_ptr()), out.stride(0), x.shape[0],
+                                   x.shape[1]))
+    return out
+
+
 def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     """`ids.apply(&embedding)` (src/archs/qwen35_text.rs:978-980): the rows `table[ids]` (ids int32 CUDA), through
     `s1_norm` with kind 2 (rows copied through the index); an id outside the table is reported at the next sync."""

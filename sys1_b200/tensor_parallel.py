@@ -237,6 +237,18 @@ class Layer:
         self.mlp.forward(n, residual=x, out=x, exchange=exchange)             # x <- x + sum_r mlp_r(n)
         return x
 
+    # The two halves of the layer for the micro-batch schedule of `Decoder.forward_embeds`: each leaves this rank's partial
+    # (rank 0: partial + residual) in `x`, starts the sum over ranks without waiting for it, and returns its ticket.
+    def mixer_part(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, exchange: bool = True):
+        y = self.mixer.mix(self.input_norm(x), cu_seqlens_host, positions)
+        fused_linear(y, self.mixer.output.weight, residual=x if self.tp.rank == 0 else None, out=x, ctx=self.tp.ctx)
+        return self.tp.ctx.all_reduce_async_(x) if exchange and self.tp.size > 1 else None
+
+    def mlp_part(self, x: torch.Tensor, exchange: bool = True):
+        h = fused_linear(self.post_norm(x), self.mlp.gate, weight_up=self.mlp.up, epilogue=EPI_SWIGLU, ctx=self.tp.ctx)
+        fused_linear(h, self.mlp.down, residual=x if self.tp.rank == 0 else None, out=x, ctx=self.tp.ctx)
+        return self.tp.ctx.all_reduce_async_(x) if exchange and self.tp.size > 1 else None
+
 
 class Decoder:
     """A stack of tensor-parallel layers over a packed batch (`Decoder::forward_embeds`, src/archs/qwen35_text.rs:986-1005,
@@ -248,7 +260,7 @@ class Decoder:
         from . import qwen35
         dev = weights["norm"].device
         rope = qwen35.RopeParams(cfg.rope_theta, cfg.rotary_dim, max_positions, dev)
-        self.cfg, self.tp = cfg, tp
+        self.cfg, self.tp, self.comm_sms = cfg, tp, int(comm_sms)
         self.layers = []
         for i in range(cfg.num_hidden_layers):
             kind = cfg.layer_type(i)
@@ -256,9 +268,58 @@ class Decoder:
             self.layers.append(Layer(shard, cfg, kind, tp, rope, slabs=slabs, comm_sms=comm_sms, recurrence=recurrence))
         self.norm = qwen35.RmsNorm(weights["norm"], cfg.rms_norm_eps)
 
-    def forward_embeds(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, exchange: bool = True) -> torch.Tensor:
-        """`x [T, hidden]` bf16: the embedded tokens, identical on every rank; it is updated in place layer by layer."""
+    def forward_embeds(self, x: torch.Tensor, cu_seqlens_host, positions: torch.Tensor, exchange: bool = True,
+                       micro_batches: int = 1) -> torch.Tensor:
+        """`x [T, hidden]` bf16: the embedded tokens, identical on every rank; it is updated in place layer by layer.
+
+        `micro_batches` > 1: the batch is cut into that many groups of whole sequences (sequences never interact), which
+        move through every layer one after the other; a group's sum over ranks is started without waiting and only the
+        group itself waits for it (by ticket) before its next stage, so one group computes while the other's partial sums
+        travel: mixer(0), [sum(0) | mixer(1)], [sum(1) | mlp(0)], [sum(0) | mlp(1)], [sum(1) | next mixer(0)], ...
+        The projections run on `SMs - comm_sms` SMs meanwhile so that the collective always finds room."""
         pos = positions.to(torch.int32).contiguous()
-        for layer in self.layers:
-            x = layer.forward(x, cu_seqlens_host, pos, exchange=exchange)
+        ctx = self.tp.ctx
+        if micro_batches <= 1:
+            for layer in self.layers:
+                x = layer.forward(x, cu_seqlens_host, pos, exchange=exchange)
+            return self.norm(x)
+        if not x.is_contiguous():
+            raise ValueError("the residual stream must be contiguous")
+        groups = []
+        for s0, s1 in split_sequences(cu_seqlens_host, micro_batches):
+            a, b = int(cu_seqlens_host[s0]), int(cu_seqlens_host[s1])
+            if b > a:
+                groups.append((x[a:b], [int(c) - a for c in cu_seqlens_host[s0:s1 + 1]], pos[a:b]))
+        tickets = [None] * len(groups)
+        carve = exchange and self.tp.size > 1 and self.comm_sms > 0
+        if carve:
+            ctx.set_option("gemm_sms", max(2, device.sm_count(ctx) - self.comm_sms))
+        try:
+            for layer in self.layers:
+                for stage in (0, 1):
+                    for i, (xg, cu, pg) in enumerate(groups):
+                        if tickets[i] is not None:
+                            ctx.all_reduce_wait_ticket(tickets[i])
+                        tickets[i] = layer.mixer_part(xg, cu, pg, exchange) if stage == 0 else layer.mlp_part(xg, exchange)
+            for t in tickets:
+                if t is not None:
+                    ctx.all_reduce_wait_ticket(t)
+        finally:
+            if carve:
+                ctx.set_option("gemm_sms", 0)
         return self.norm(x)
+
+
+def split_sequences(cu_seqlens_host, parts: int):
+    """Cuts the sequences of a packed batch into at most `parts` consecutive groups of about the same number of tokens:
+    [(first sequence, one past the last), ...]. Groups are runs of whole sequences, so each is a packed batch of its own."""
+    cu = [int(c) for c in cu_seqlens_host]
+    n, total = len(cu) - 1, cu[-1]
+    bounds = [0]
+    for k in range(1, parts):
+        target = total * k / parts
+        # the sequence boundary closest to the k-th share of the tokens, never before the previous cut
+        best = min(range(bounds[-1], n + 1), key=lambda s: abs(cu[s] - target))
+        bounds.append(max(best, bounds[-1]))
+    bounds.append(n)
+    return [(a, b) for a, b in zip(bounds[:-1], bounds[1:]) if b > a]

@@ -155,3 +155,17 @@ def test_shard_helpers_reject_uneven_splits():
         device.column_parallel_shard(w, 0, 4)
     with pytest.raises(ValueError):
         device.row_parallel_shard(w, 0, 2)
+
+
+def test_split_sequences_into_micro_batches():
+    from sys1_b200.tensor_parallel import split_sequences
+    assert split_sequences([0, 10, 20, 30, 40], 2) == [(0, 2), (2, 4)]
+    assert split_sequences([0, 100, 101, 102], 2) == [(0, 1), (1, 3)]
+    assert split_sequences([0, 5], 3) == [(0, 1)]                     # fewer sequences than groups
+    lens = batching.synthetic_lengths(1005, 256, 8192, 65536)
+    cu = [0] + [int(v) for v in lens.cumsum()]
+    for parts in (2, 4):
+        groups = split_sequences(cu, parts)
+        assert groups[0][0] == 0 and groups[-1][1] == len(lens) and all(a[1] == b[0] for a, b in zip(groups, groups[1:]))
+        sizes = [cu[b] - cu[a] for a, b in groups]
+        assert sum(sizes) == 65536 and max(sizes) - min(sizes) <= 2 * 8192  # cuts fall on sequence boundaries

@@ -83,7 +83,11 @@ def _layer_group(rank, world, dev, tp, dist):
     for _ in range(2):
         y = dec.forward_embeds(x0.clone(), b.cu_seqlens, pos)
     tp.ctx.sync()
+    # two micro-batches of whole sequences alternating between computing and exchanging (ticketed waits)
+    y2 = dec.forward_embeds(x0.clone(), b.cu_seqlens, pos, micro_batches=2)
+    tp.ctx.sync()
     torch.cuda.synchronize()
+    assert float((y2.float() - y.float()).abs().max()) <= 3e-2 * float(y.float().abs().max())
     single = qwen35.Decoder(dw, cfg).forward(ids.to(dev), b.cu_seqlens, pos)
     want = torch.empty(b.total_tokens, cfg.hidden_size)
     for a, z in zip(b.cu_seqlens[:-1], b.cu_seqlens[1:]):
@@ -91,6 +95,9 @@ def _layer_group(rank, world, dev, tp, dist):
     scale = float(want.abs().max())
     gathered = [torch.zeros_like(y.cpu()) for _ in range(world)]
     dist.all_gather(gathered, y.cpu())
+    gathered2 = [torch.zeros_like(y2.cpu()) for _ in range(world)]
+    dist.all_gather(gathered2, y2.cpu())
+    assert all(torch.equal(gathered2[0], t) for t in gathered2[1:])
     return (float((y.float() - single.float()).abs().max()) / scale, float((y.float().cpu() - want).abs().max()) / scale,
             all(torch.equal(gathered[0], t) for t in gathered[1:]))
 
