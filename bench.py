@@ -425,23 +425,32 @@ def tp_block(args, rank, world, dev, steps, warmup):
         g = torch.Generator(device=dev).manual_seed(seed)
         return b, torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16), torch.from_numpy(b.positions).to(dev)
 
-    # ---- parity on a small batch: sharded against unsharded on this GPU; all ranks bit-identical
+    # ---- parity on a small batch, layer by layer on identical inputs (the acceptance rule: max-relative 2e-2 per layer):
+    #      every layer of the sharded group gets the residual stream the unsharded stack has before that layer; all ranks
+    #      must hold bit-identical results. The whole group end to end is reported as well (two bf16 trajectories drift).
     pb, px, ppos = batch_of(2048, 2005)
-    y_tp = dec.forward_embeds(px.clone(), pb.cu_seqlens, ppos, micro_batches=args.micro_batches if world > 1 else 1)
-    ctx.sync()
+    mbp = args.micro_batches if world > 1 else 1
     single = qwen35.Decoder({**w, "embed_tokens": px}, cfg)      # the embedded tokens stand in for the table: ids = arange
-    y_one = single.forward(torch.arange(2048, device=dev, dtype=torch.int32), pb.cu_seqlens, ppos)
+    y_one, states = single.forward(torch.arange(2048, device=dev, dtype=torch.int32), pb.cu_seqlens, ppos, collect=True)
+    y_tp = dec.forward_embeds(px.clone(), pb.cu_seqlens, ppos, micro_batches=mbp)
     ctx.sync()
-    scale = float(y_one.float().abs().max())
-    max_rel = float((y_tp.float() - y_one.float()).abs().max()) / scale
+    rel = lambda a, b_: float((a.float() - b_.float()).abs().max() / b_.float().abs().max())
+    per_layer, digest = [], y_tp.view(torch.int16).to(torch.int64).sum().reshape(1)
+    x_in = px
+    for i, layer in enumerate(dec.layers):
+        got = layer.forward(x_in.clone(), pb.cu_seqlens, ppos)
+        per_layer.append(rel(got, states[i]))
+        digest = digest + got.view(torch.int16).to(torch.int64).sum()
+        x_in = states[i]
+    ctx.sync()
+    max_rel = rel(y_tp, y_one)
     rel_rms = float((y_tp.float() - y_one.float()).square().mean().sqrt() / y_one.float().square().mean().sqrt())
-    digest = y_tp.view(torch.int16).to(torch.int64).sum().reshape(1)
     same = True
     if world > 1:
         all_d = [torch.zeros_like(digest) for _ in range(world)]
         torch.distributed.all_gather(all_d, digest)
         same = all(int(d) == int(all_d[0]) for d in all_d)
-    del single, y_one, y_tp
+    del single, y_one, y_tp, states
 
     # ---- timing at the configured budget
     T = args.tp_tokens
@@ -502,9 +511,11 @@ def tp_block(args, rank, world, dev, steps, warmup):
             "ms_without_exchange": ms_math, "ms_allreduce_alone": ms_ar, "allreduces_per_step": n_ar if world > 1 else 0,
             "allreduce_busbw_gbs": (2.0 * (world - 1) / world * bytes_ar / (ms_ar * 1e-3) / 1e9) if world > 1 and ms_ar > 0 else None,
             "exchange_hidden_frac": (1.0 - (ms - ms_math) / ms_ar) if world > 1 and ms_ar > 0 else None,
-            "parity": {"tokens": 2048, "max_rel_vs_unsharded": max_rel, "rel_rms_vs_unsharded": rel_rms, "ranks_bit_identical": bool(same),
-                       "bound_max_rel": 5e-2, "bound_rel_rms": 1e-2, "ok": bool(same and max_rel <= 5e-2 and rel_rms <= 1e-2),
-                       "note": "two bf16 evaluations of four layers (per-rank partial sums are rounded to bf16 before they are added)"},
+            "parity": {"tokens": 2048, "per_layer_max_rel_vs_unsharded": per_layer, "bound": 2e-2, "ranks_bit_identical": bool(same),
+                       "ok": bool(same and max(per_layer) <= 2e-2),
+                       "whole_group_max_rel": max_rel, "whole_group_rel_rms": rel_rms,
+                       "note": "per layer: the sharded layer and the unsharded layer on the same input; whole group: two bf16 "
+                               "trajectories of four layers (per-rank partial sums are rounded to bf16 before they are added)"},
             "gpu_launches": launches, **({"sweep": sweep} if sweep is not None else {})}
 
 
@@ -655,12 +666,16 @@ def projections_line(args, rank, world, local_rank):
                 "frac_of_sustained": tf / world / peaks["sustained"], "frac_of_burst": tf / world / peaks["burst"],
                 "peak_source": f"{peaks['kind']} bf16: sustained {peaks['sustained']}, burst {peaks['burst']} TFLOP/s per GPU", "clocks": clk}
 
-    attempt("sustained", sustained)
+    if not args.profile:
+        attempt("sustained", sustained)
     t1w = time.time()
     clocks = sampler.summary(t0w - 0.05, t1w + 0.05)
     clocks["window"] = "timed region and the sustained loop that follows it"
     sampler.stop()
 
+    if args.profile:
+        return {"metric": "projection GEMM TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "ms_per_step": ms_step, "per_projection_us": {n: per[n] * 1e3 for n in names}, "profile_run": True} if rank == 0 else None
     # ---- end-to-end arm: host buffers in, host buffer out, copies inside the timed region ----------------------------
     # (copy-in of batch i+1 and copy-out of batch i-1 overlap the compute of batch i: sys1_b200.pipeline)
     host_y = [torch.empty(T, HIDDEN, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
@@ -805,6 +820,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="a short run for a profiler: the timed loop only (no sustained loop, budgets, library GEMMs, end-to-end arm, "
+                         "secondary workloads or CPU baseline)")
     ap.add_argument("--no-secondary", action="store_true", help="projections workload: leave out the encoder / decoder / tp blocks")
     ap.add_argument("--workload", default="projections", choices=["projections", "encoder", "decoder", "tp"],
                     help="projections (default): the headline line with every block; encoder / decoder / tp: that block alone, as a line")
@@ -849,7 +867,7 @@ def main():
     try:
         if args.workload == "projections":
             line = projections_line(args, rank, world, local_rank)
-            if line is not None and world == 1 and not args.no_cpu_baseline:
+            if line is not None and world == 1 and not args.no_cpu_baseline and not args.profile:
                 val, dt, n, cores = cpu_projections(args.cpu_sample_tokens, 1000, 1, budget_s=12.0)
                 line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                         "sample": f"{args.cpu_sample_tokens} of the {args.tokens} token rows, same four projections, "

@@ -161,7 +161,7 @@ int s1_delta_rule(s1_ctx* ctx, const float* q, const float* k, const float* v, c
  * state): the form of the reference's CPU fallback (src/archs/qwen35_text.rs:809-880), which it evaluates in f32.
  * Results agree with `s1_delta_rule` to bf16 operand precision (relative 2e-2 of the output scale is the bound the
  * tests hold it to), not to 1e-4. key_dim = value_dim = 128 only. `cu_seqlens_host` is a HOST array here (the chunk
- * tables are built on the host); `workspace` is device memory, 1024-byte aligned, of at least
+ * tables are built on the host; NULL while a batch plan for this batch is in use); `workspace` is device memory, 1024-byte aligned, of at least
  * `s1_delta_rule_chunked_workspace(num_seqs, total_tokens, heads)` bytes, owned by the caller.
  */
 size_t s1_delta_rule_chunked_workspace(int num_seqs, int total_tokens, int heads);
@@ -183,6 +183,9 @@ int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const flo
  *  s1_delta_finish  `finish_delta` up to out_proj (:597-626): o / sqrt(mean(o^2) + eps) * norm_weight * silu(z) -> bf16.
  *  s1_gated_delta_rule  the three in a row around s1_delta_rule_chunked, from the conv output to the out_proj
  *                   input; `workspace` (device, 1024-byte aligned) of s1_gated_delta_rule_workspace(...) bytes.
+ *                   Its recurrence is the chunk form (bf16 operands, f32 state): within 2e-2 of the output scale of the
+ *                   exact f32 recurrence, not within the reference's 1e-4; s1_delta_inputs -> s1_delta_rule ->
+ *                   s1_delta_finish is the same path at the reference's own precision.
  */
 int s1_conv_silu(s1_ctx* ctx, const void* x, long long ldx, const void* weight, const int32_t* positions, int total_tokens,
                  int channels, int taps, void* y, long long ldy);
@@ -198,6 +201,27 @@ int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const voi
                         int value_heads, void* y, long long ldy, void* workspace, size_t workspace_bytes);
 
 /*
+ * Batch plan: the tables the attention and delta-rule kernels walk - the 128-query blocks of every sequence in the order
+ * each attention kernel starts them, and the 64-token chunks of the delta rule - built once per packed batch instead of
+ * once per kernel call. Every layer of a stack sees the same batch, so the per-call form costs one small host-to-device
+ * copy per layer and keeps those calls out of CUDA graphs; the reference likewise derives its `cu_seqlens` once per batch
+ * (src/archs/modernbert.rs:431-443).
+ *   s1_batch_plan_bytes : size of the device buffer a plan needs
+ *   s1_batch_plan       : builds the tables from the HOST offsets and copies them into `plan` (device memory, 256-byte
+ *                         aligned, owned by the caller) on the context's stream
+ *   s1_use_batch_plan   : makes a plan built on this context the one in use (NULL: none). While a plan is in use,
+ *                         s1_attention, s1_attention_gqa, s1_delta_rule_chunked and s1_gated_delta_rule may be called
+ *                         with `cu_seqlens_host` = NULL for the same (num_seqs, total_tokens): they then read their
+ *                         tables from the plan and copy nothing (the attentions need no workspace then).
+ * The caller keeps the buffer alive and unchanged while the plan is in use. A call that does pass `cu_seqlens_host`
+ * ignores the plan and behaves as before (and refuses to run under stream capture, where its copy from host memory
+ * would be recorded with a pointer that does not outlive the call).
+ */
+size_t s1_batch_plan_bytes(int num_seqs, int total_tokens);
+int s1_batch_plan(s1_ctx* ctx, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens, void* plan, size_t plan_bytes);
+int s1_use_batch_plan(s1_ctx* ctx, const void* plan);
+
+/*
  * Bidirectional softmax attention over a packed batch in flash form (scores stay on chip), head_dim = 64:
  *     out_i = sum_j softmax_j(scale * q_i . k_j) v_j   over the keys j of the same sequence with |i - j| <= window
  * (`window` < 0: all keys of the sequence). This is `scaled_dot_product_attention` of the reference
@@ -205,7 +229,8 @@ int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const voi
  * layout has no padded keys, so the global mask (:1048-1056) has nothing to mask. q, k, v: bf16 [T, heads * 64]
  * views with row strides ldq / ldk / ldv (they may be the three column blocks of the Wqkv output, after RoPE);
  * out: bf16 [T, heads * 64] = the merged-heads layout Wo consumes (`merge_heads`, :249-260).
- * `cu_seqlens_host`: HOST int32 [num_seqs + 1]; `workspace`: device memory of s1_attention_workspace(...) bytes.
+ * `cu_seqlens_host`: HOST int32 [num_seqs + 1]; `workspace`: device memory of s1_attention_workspace(...) bytes
+ * (both may be NULL while a batch plan for this batch is in use). `scale` must be positive.
  * Softmax in f32, probabilities rounded to bf16 before they multiply V (as the reference does, :349-350).
  */
 size_t s1_attention_workspace(int num_seqs, int total_tokens);
@@ -222,7 +247,8 @@ int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const void* k, long 
  * q: bf16, head h of token t at q + t * ldq + h * q_head_stride (so the query halves of the interleaved q_proj
  * output, [T, heads, 2, 256], are read in place with q_head_stride = 512, and gate = q + 256 likewise);
  * k, v: bf16 [T, kv_heads * 256] views with their own strides; out: bf16 [T, heads * 256] (what o_proj consumes).
- * `cu_seqlens_host`: HOST int32 [num_seqs + 1]; `workspace`: device memory of s1_attention_gqa_workspace(...) bytes.
+ * `cu_seqlens_host`: HOST int32 [num_seqs + 1]; `workspace`: device memory of s1_attention_gqa_workspace(...) bytes
+ * (both may be NULL while a batch plan for this batch is in use). `scale` must be positive.
  */
 size_t s1_attention_gqa_workspace(int num_seqs, int total_tokens);
 int s1_attention_gqa(s1_ctx* ctx, const void* q, long long ldq, long long q_head_stride, const void* k, long long ldk,

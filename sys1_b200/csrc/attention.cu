@@ -369,7 +369,11 @@ extern "C" int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const voi
                             const int32_t* cu_seqlens_host, int num_seqs, int total_tokens, int heads, int head_dim, int window,
                             float scale, void* out, long long ldo, void* workspace, size_t workspace_bytes) {
     if (!ctx) return S1_EINVAL;
-    if (!q || !k || !v || !cu_seqlens_host || !out || !workspace) return s1_fail(ctx, S1_EINVAL, "s1_attention: null pointer");
+    if (!q || !k || !v || !out) return s1_fail(ctx, S1_EINVAL, "s1_attention: null pointer");
+    const S1BatchPlan* plan = cu_seqlens_host ? nullptr : ctx->active_plan(num_seqs, total_tokens);
+    if (!cu_seqlens_host && !plan)
+        return s1_fail(ctx, S1_EINVAL, "s1_attention: cu_seqlens_host is NULL and no batch plan for this batch is in use");
+    if (!plan && !workspace) return s1_fail(ctx, S1_EINVAL, "s1_attention: null workspace");
     if (head_dim != kHD) return s1_fail(ctx, S1_EINVAL, "s1_attention: head_dim must be 64 (got %d)", head_dim);
     if (heads < 1 || num_seqs < 0 || total_tokens < 0) return s1_fail(ctx, S1_EINVAL, "s1_attention: bad sizes");
     const long long width = 1LL * heads * kHD;
@@ -378,27 +382,41 @@ extern "C" int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const voi
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out) |
          reinterpret_cast<uintptr_t>(workspace)) & 15u)
         return s1_fail(ctx, S1_EINVAL, "s1_attention: pointers must be 16-byte aligned");
+    static_assert(sizeof(QBlock) == sizeof(S1QBlock), "the plan's query-block table has this kernel's layout");
     if (!(scale > 0.f) || !(scale < 1e30f)) return s1_fail(ctx, S1_EINVAL, "s1_attention: scale must be positive and finite");
-    if (workspace_bytes < s1_attention_workspace(num_seqs, total_tokens))
+    if (!plan && workspace_bytes < s1_attention_workspace(num_seqs, total_tokens))
         return s1_fail(ctx, S1_EINVAL, "s1_attention: workspace of %zu bytes, %zu needed", workspace_bytes,
                        s1_attention_workspace(num_seqs, total_tokens));
     if (num_seqs == 0 || total_tokens == 0) return S1_OK;
-    if (cu_seqlens_host[0] != 0 || cu_seqlens_host[num_seqs] != total_tokens)
-        return s1_fail(ctx, S1_EINVAL, "s1_attention: cu_seqlens must run from 0 to total_tokens");
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
-    const size_t max_blocks = static_cast<size_t>(total_tokens / kQB + num_seqs + 1);
-    ctx->host_scratch.resize(sizeof(QBlock) * max_blocks);
-    QBlock* blocks = reinterpret_cast<QBlock*>(ctx->host_scratch.data());
     int nb = 0;
-    for (int s = 0; s < num_seqs; ++s) {
-        const int a = cu_seqlens_host[s], len = cu_seqlens_host[s + 1] - a;
-        if (len < 0) return s1_fail(ctx, S1_EINVAL, "s1_attention: cu_seqlens must not decrease");
-        for (int b = 0; b * kQB < len; ++b) blocks[nb++] = QBlock{a, len, b, 0};
+    const QBlock* blocks_dev = nullptr;
+    if (plan) {
+        // the query-block table was built and copied once for the whole batch (s1_batch_plan)
+        nb = plan->num_blocks;
+        blocks_dev = reinterpret_cast<const QBlock*>(plan->dev + (window < 0 ? plan->attn_global_off : plan->attn_local_off));
+    } else {
+        if (cu_seqlens_host[0] != 0 || cu_seqlens_host[num_seqs] != total_tokens)
+            return s1_fail(ctx, S1_EINVAL, "s1_attention: cu_seqlens must run from 0 to total_tokens");
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return s1_fail(ctx, S1_EINVAL, "s1_attention: with cu_seqlens_host the call copies a table from host memory and "
+                                           "cannot be captured; build a batch plan first (s1_batch_plan)");
+        const size_t max_blocks = static_cast<size_t>(total_tokens / kQB + num_seqs + 1);
+        ctx->host_scratch.resize(sizeof(QBlock) * max_blocks);
+        QBlock* blocks = reinterpret_cast<QBlock*>(ctx->host_scratch.data());
+        for (int s = 0; s < num_seqs; ++s) {
+            const int a = cu_seqlens_host[s], len = cu_seqlens_host[s + 1] - a;
+            if (len < 0) return s1_fail(ctx, S1_EINVAL, "s1_attention: cu_seqlens must not decrease");
+            for (int b = 0; b * kQB < len; ++b) blocks[nb++] = QBlock{a, len, b, 0};
+        }
+        if (nb == 0) return S1_OK;
+        // without a window the work of a block grows with its sequence: longest sequences first
+        if (window < 0) std::stable_sort(blocks, blocks + nb, [](const QBlock& x, const QBlock& y) { return x.seq_len > y.seq_len; });
+        S1_CUDA_OK(ctx, cudaMemcpyAsync(workspace, blocks, sizeof(QBlock) * nb, cudaMemcpyHostToDevice, ctx->stream));
+        blocks_dev = static_cast<const QBlock*>(workspace);
     }
     if (nb == 0) return S1_OK;
-    // without a window the work of a block grows with its sequence: longest sequences first
-    if (window < 0) std::stable_sort(blocks, blocks + nb, [](const QBlock& x, const QBlock& y) { return x.seq_len > y.seq_len; });
-    S1_CUDA_OK(ctx, cudaMemcpyAsync(workspace, blocks, sizeof(QBlock) * nb, cudaMemcpyHostToDevice, ctx->stream));
 
     CUtensorMap tq, tk, tv;
     int rc = s1_get_tmap(ctx, q, total_tokens, width, ldq, kQB, kHD, 2, 128, &tq);
@@ -408,7 +426,7 @@ extern "C" int s1_attention(s1_ctx* ctx, const void* q, long long ldq, const voi
     rc = s1_get_tmap(ctx, v, total_tokens, width, ldv, kQB, kHD, 2, 128, &tv);
     if (rc) return rc;
     AttnParams ap;
-    ap.blocks = static_cast<const QBlock*>(workspace);
+    ap.blocks = blocks_dev;
     ap.out = static_cast<__nv_bfloat16*>(out);
     ap.ldo = ldo;
     ap.window = window;

@@ -387,7 +387,12 @@ extern "C" int s1_attention_gqa(s1_ctx* ctx, const void* q, long long ldq, long 
                                 int total_tokens, int heads, int kv_heads, int head_dim, float scale, void* out, long long ldo,
                                 void* workspace, size_t workspace_bytes) {
     if (!ctx) return S1_EINVAL;
-    if (!q || !k || !v || !cu_seqlens_host || !out || !workspace) return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: null pointer");
+    if (!q || !k || !v || !out) return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: null pointer");
+    static_assert(sizeof(QBlock) == sizeof(S1QBlock), "the plan's query-block table has this kernel's layout");
+    const S1BatchPlan* plan = cu_seqlens_host ? nullptr : ctx->active_plan(num_seqs, total_tokens);
+    if (!cu_seqlens_host && !plan)
+        return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: cu_seqlens_host is NULL and no batch plan for this batch is in use");
+    if (!plan && !workspace) return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: null workspace");
     if (head_dim != kD) return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: head_dim must be 256 (got %d)", head_dim);
     if (heads < 1 || kv_heads < 1 || (heads % kv_heads) || num_seqs < 0 || total_tokens < 0)
         return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: heads must be a multiple of kv_heads");
@@ -401,26 +406,38 @@ extern "C" int s1_attention_gqa(s1_ctx* ctx, const void* q, long long ldq, long 
          reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(workspace)) & 15u)
         return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: pointers must be 16-byte aligned");
     if (!(scale > 0.f) || !(scale < 1e30f)) return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: scale must be positive and finite");
-    if (workspace_bytes < s1_attention_gqa_workspace(num_seqs, total_tokens))
+    if (!plan && workspace_bytes < s1_attention_gqa_workspace(num_seqs, total_tokens))
         return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: workspace of %zu bytes, %zu needed", workspace_bytes,
                        s1_attention_gqa_workspace(num_seqs, total_tokens));
     if (num_seqs == 0 || total_tokens == 0) return S1_OK;
-    if (cu_seqlens_host[0] != 0 || cu_seqlens_host[num_seqs] != total_tokens)
-        return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: cu_seqlens must run from 0 to total_tokens");
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
-    const size_t max_blocks = static_cast<size_t>(total_tokens / kQB + num_seqs + 1);
-    ctx->host_scratch.resize(sizeof(QBlock) * max_blocks);
-    QBlock* blocks = reinterpret_cast<QBlock*>(ctx->host_scratch.data());
     int nb = 0;
-    for (int s = 0; s < num_seqs; ++s) {
-        const int a = cu_seqlens_host[s], len = cu_seqlens_host[s + 1] - a;
-        if (len < 0) return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: cu_seqlens must not decrease");
-        for (int b = 0; b * kQB < len; ++b) blocks[nb++] = QBlock{a, len, b, 0};
+    const QBlock* blocks_dev = nullptr;
+    if (plan) {
+        nb = plan->num_blocks;
+        blocks_dev = reinterpret_cast<const QBlock*>(plan->dev + plan->gqa_off);
+    } else {
+        if (cu_seqlens_host[0] != 0 || cu_seqlens_host[num_seqs] != total_tokens)
+            return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: cu_seqlens must run from 0 to total_tokens");
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: with cu_seqlens_host the call copies a table from host memory and "
+                                           "cannot be captured; build a batch plan first (s1_batch_plan)");
+        const size_t max_blocks = static_cast<size_t>(total_tokens / kQB + num_seqs + 1);
+        ctx->host_scratch.resize(sizeof(QBlock) * max_blocks);
+        QBlock* blocks = reinterpret_cast<QBlock*>(ctx->host_scratch.data());
+        for (int s = 0; s < num_seqs; ++s) {
+            const int a = cu_seqlens_host[s], len = cu_seqlens_host[s + 1] - a;
+            if (len < 0) return s1_fail(ctx, S1_EINVAL, "s1_attention_gqa: cu_seqlens must not decrease");
+            for (int b = 0; b * kQB < len; ++b) blocks[nb++] = QBlock{a, len, b, 0};
+        }
+        if (nb == 0) return S1_OK;
+        // a causal block's work grows with its position in the sequence: latest blocks first
+        std::stable_sort(blocks, blocks + nb, [](const QBlock& x, const QBlock& y) { return x.qb > y.qb; });
+        S1_CUDA_OK(ctx, cudaMemcpyAsync(workspace, blocks, sizeof(QBlock) * nb, cudaMemcpyHostToDevice, ctx->stream));
+        blocks_dev = static_cast<const QBlock*>(workspace);
     }
     if (nb == 0) return S1_OK;
-    // a causal block's work grows with its position in the sequence: latest blocks first
-    std::stable_sort(blocks, blocks + nb, [](const QBlock& x, const QBlock& y) { return x.qb > y.qb; });
-    S1_CUDA_OK(ctx, cudaMemcpyAsync(workspace, blocks, sizeof(QBlock) * nb, cudaMemcpyHostToDevice, ctx->stream));
 
     CUtensorMap tq, tk, tv;
     int rc = s1_get_tmap(ctx, q, total_tokens, qw, ldq, kQB, 64, 2, 128, &tq);
@@ -430,7 +447,7 @@ extern "C" int s1_attention_gqa(s1_ctx* ctx, const void* q, long long ldq, long 
     rc = s1_get_tmap(ctx, v, total_tokens, vw, ldv, kKB, 64, 2, 128, &tv);
     if (rc) return rc;
     GqaParams gp;
-    gp.blocks = static_cast<const QBlock*>(workspace);
+    gp.blocks = blocks_dev;
     gp.out = static_cast<__nv_bfloat16*>(out);
     gp.ldo = ldo;
     gp.gate = static_cast<const __nv_bfloat16*>(gate);

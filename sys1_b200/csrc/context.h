@@ -35,6 +35,30 @@ struct S1TmapKeyHash {
     }
 };
 
+// Tables of one packed batch that the attention and delta-rule kernels walk (s1_batch_plan): built once per batch on the
+// host, copied to the device once, reused by every layer. The record below is the host's note of where they lie.
+struct S1QBlock {      // one 128-query block of one sequence
+    int seq_start;     // first token of the sequence
+    int seq_len;
+    int qb;            // query block inside the sequence
+    int pad;
+};
+struct S1ChunkSlot {   // one 64-token chunk of the delta rule
+    int tok_start;     // first token (row of the packed batch)
+    int len;           // valid tokens in the chunk (1..64)
+};
+struct S1SeqChunks {
+    int first_slot;
+    int num_chunks;
+};
+struct S1BatchPlan {
+    const unsigned char* dev = nullptr;
+    int num_seqs = 0, total_tokens = 0;
+    int num_blocks = 0;   // 128-query blocks (both attentions)
+    int num_slots = 0;    // 64-token chunks
+    size_t attn_global_off = 0, attn_local_off = 0, gqa_off = 0, slots_off = 0, seqs_off = 0;
+};
+
 struct s1_ctx {
     int device = 0;
     int sm_count = 0;
@@ -51,6 +75,14 @@ struct s1_ctx {
     PFN_cuTensorMapEncodeTiled encode = nullptr;
     std::unordered_map<S1TmapKey, CUtensorMap, S1TmapKeyHash> tmaps;
     std::vector<unsigned char> host_scratch;  // host staging for small tables copied to the device
+    std::vector<S1BatchPlan> plans;           // plans built on this context (a few: one per batch in flight)
+    int plan_in_use = -1;                     // index into `plans`, or -1
+    // the plan in use if it describes this batch, else null
+    const S1BatchPlan* active_plan(int num_seqs, int total_tokens) const {
+        if (plan_in_use < 0 || plan_in_use >= static_cast<int>(plans.size())) return nullptr;
+        const S1BatchPlan& p = plans[plan_in_use];
+        return (p.num_seqs == num_seqs && p.total_tokens == total_tokens) ? &p : nullptr;
+    }
     void* comm = nullptr;                     // ncclComm_t once s1_comm_init has run
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t comm_ready = nullptr, comm_done = nullptr;

@@ -745,35 +745,54 @@ extern "C" size_t s1_delta_rule_chunked_workspace(int num_seqs, int total_tokens
 static int run_chunked(s1_ctx* ctx, const char* who, PrepParams pp, bool fused, const int32_t* cu_seqlens_host, int num_seqs,
                        int total_tokens, int heads, float* out, void* workspace, size_t workspace_bytes) {
     if (num_seqs == 0 || total_tokens == 0) return S1_OK;
-    if (cu_seqlens_host[0] != 0 || cu_seqlens_host[num_seqs] != total_tokens)
-        return s1_fail(ctx, S1_EINVAL, "%s: cu_seqlens must run from 0 to total_tokens", who);
+    static_assert(sizeof(SlotInfo) == sizeof(S1ChunkSlot) && sizeof(SeqInfo) == sizeof(S1SeqChunks), "the plan's chunk tables have this kernel's layout");
+    const S1BatchPlan* plan = cu_seqlens_host ? nullptr : ctx->active_plan(num_seqs, total_tokens);
+    if (!cu_seqlens_host && !plan)
+        return s1_fail(ctx, S1_EINVAL, "%s: cu_seqlens_host is NULL and no batch plan for this batch is in use", who);
     const int max_slots = total_tokens / kC + num_seqs + 1;
     const WorkspaceLayout L = layout(num_seqs, max_slots, heads);
     if (workspace_bytes < L.total) return s1_fail(ctx, S1_EINVAL, "%s: workspace of %zu bytes, %zu needed", who, workspace_bytes, L.total);
     if ((reinterpret_cast<uintptr_t>(workspace) & 1023u) != 0) return s1_fail(ctx, S1_EINVAL, "%s: the workspace must be 1024-byte aligned", who);
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
-
-    // chunk tables, built on the host from the host copy of the offsets
-    ctx->host_scratch.resize(sizeof(SlotInfo) * max_slots + sizeof(SeqInfo) * num_seqs);
-    SlotInfo* slots = reinterpret_cast<SlotInfo*>(ctx->host_scratch.data());
-    SeqInfo* seqs = reinterpret_cast<SeqInfo*>(ctx->host_scratch.data() + sizeof(SlotInfo) * max_slots);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
     int num_slots = 0;
-    for (int s = 0; s < num_seqs; ++s) {
-        const int a = cu_seqlens_host[s], b = cu_seqlens_host[s + 1];
-        if (b < a) return s1_fail(ctx, S1_EINVAL, "%s: cu_seqlens must not decrease", who);
-        seqs[s].first_slot = num_slots;
-        seqs[s].num_chunks = (b - a + kC - 1) / kC;
-        for (int t = a; t < b; t += kC) slots[num_slots++] = SlotInfo{t, (b - t < kC) ? b - t : kC};
+    const SlotInfo* slots_dev = nullptr;
+    const SeqInfo* seqs_dev = nullptr;
+    if (plan) {
+        // chunk tables built and copied once for the whole batch (s1_batch_plan)
+        num_slots = plan->num_slots;
+        slots_dev = reinterpret_cast<const SlotInfo*>(plan->dev + plan->slots_off);
+        seqs_dev = reinterpret_cast<const SeqInfo*>(plan->dev + plan->seqs_off);
+    } else {
+        if (cu_seqlens_host[0] != 0 || cu_seqlens_host[num_seqs] != total_tokens)
+            return s1_fail(ctx, S1_EINVAL, "%s: cu_seqlens must run from 0 to total_tokens", who);
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return s1_fail(ctx, S1_EINVAL, "%s: with cu_seqlens_host the call copies tables from host memory and cannot be "
+                                           "captured; build a batch plan first (s1_batch_plan)", who);
+        // chunk tables, built on the host from the host copy of the offsets
+        ctx->host_scratch.resize(sizeof(SlotInfo) * max_slots + sizeof(SeqInfo) * num_seqs);
+        SlotInfo* slots = reinterpret_cast<SlotInfo*>(ctx->host_scratch.data());
+        SeqInfo* seqs = reinterpret_cast<SeqInfo*>(ctx->host_scratch.data() + sizeof(SlotInfo) * max_slots);
+        for (int s = 0; s < num_seqs; ++s) {
+            const int a = cu_seqlens_host[s], b = cu_seqlens_host[s + 1];
+            if (b < a) return s1_fail(ctx, S1_EINVAL, "%s: cu_seqlens must not decrease", who);
+            seqs[s].first_slot = num_slots;
+            seqs[s].num_chunks = (b - a + kC - 1) / kC;
+            for (int t = a; t < b; t += kC) slots[num_slots++] = SlotInfo{t, (b - t < kC) ? b - t : kC};
+        }
+        if (num_slots == 0) return S1_OK;
+        // the scan kernel runs one CTA per (sequence, head): start the longest sequences first
+        std::stable_sort(seqs, seqs + num_seqs, [](const SeqInfo& a, const SeqInfo& b) { return a.num_chunks > b.num_chunks; });
+        // (copies from pageable memory are staged before the call returns, so the host buffer can be reused at once)
+        S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.slots_off, slots, sizeof(SlotInfo) * num_slots, cudaMemcpyHostToDevice, ctx->stream));
+        S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.seqs_off, seqs, sizeof(SeqInfo) * num_seqs, cudaMemcpyHostToDevice, ctx->stream));
+        slots_dev = reinterpret_cast<const SlotInfo*>(ws + L.slots_off);
+        seqs_dev = reinterpret_cast<const SeqInfo*>(ws + L.seqs_off);
     }
     if (num_slots == 0) return S1_OK;
-    // the scan kernel runs one CTA per (sequence, head): start the longest sequences first
-    std::stable_sort(seqs, seqs + num_seqs, [](const SeqInfo& a, const SeqInfo& b) { return a.num_chunks > b.num_chunks; });
-    uint8_t* ws = static_cast<uint8_t*>(workspace);
-    // (copies from pageable memory are staged before the call returns, so the host buffer can be reused at once)
-    S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.slots_off, slots, sizeof(SlotInfo) * num_slots, cudaMemcpyHostToDevice, ctx->stream));
-    S1_CUDA_OK(ctx, cudaMemcpyAsync(ws + L.seqs_off, seqs, sizeof(SeqInfo) * num_seqs, cudaMemcpyHostToDevice, ctx->stream));
 
-    pp.slots = reinterpret_cast<const SlotInfo*>(ws + L.slots_off);
+    pp.slots = slots_dev;
     pp.num_slots = num_slots, pp.H = heads;
     pp.wq = reinterpret_cast<__nv_bfloat16*>(ws + L.wq_off);
     pp.ut = reinterpret_cast<__nv_bfloat16*>(ws + L.ut_off);
@@ -805,7 +824,7 @@ static int run_chunked(s1_ctx* ctx, const char* who, PrepParams pp, bool fused, 
     rc = s1_get_tmap(ctx, pp.p, hs_rows * 64, 64, 64, 64, 64, 2, 128, &tP);
     if (rc) return rc;
     ScanParams sp;
-    sp.seqs = reinterpret_cast<const SeqInfo*>(ws + L.seqs_off);
+    sp.seqs = seqs_dev;
     sp.slots = pp.slots;
     sp.decay = pp.decay;
     sp.out = out;
@@ -822,7 +841,7 @@ extern "C" int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k
                                      int heads, int key_dim, int value_dim, float* out, void* workspace,
                                      size_t workspace_bytes) {
     if (!ctx) return S1_EINVAL;
-    if (!q || !k || !v || !g || !beta || !cu_seqlens_host || !out || !workspace)
+    if (!q || !k || !v || !g || !beta || !out || !workspace)
         return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: null pointer");
     if (key_dim != kD || value_dim != kD)
         return s1_fail(ctx, S1_EINVAL, "s1_delta_rule_chunked: key_dim and value_dim must be 128 (got %d, %d); use s1_delta_rule", key_dim, value_dim);
@@ -850,7 +869,7 @@ extern "C" int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm
                                    int total_tokens, int key_heads, int value_heads, void* y, long long ldy, void* workspace,
                                    size_t workspace_bytes) {
     if (!ctx) return S1_EINVAL;
-    if (!mixed || !b_proj || !a_proj || !dt_bias || !neg_exp_a || !z || !norm_weight || !cu_seqlens_host || !y || !workspace)
+    if (!mixed || !b_proj || !a_proj || !dt_bias || !neg_exp_a || !z || !norm_weight || !y || !workspace)
         return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: null pointer");
     if (key_heads < 1 || value_heads < key_heads || value_heads % key_heads)
         return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: value_heads must be a multiple of key_heads");

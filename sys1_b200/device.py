@@ -70,6 +70,30 @@ class Context:
         off = (-ws.data_ptr()) % 1024
         return ws[off:]
 
+    # -- batch plans ------------------------------------------------------------------------------
+    def batch_plan(self, cu_seqlens_host, total_tokens: int) -> torch.Tensor:
+        """Builds the per-batch tables of the attention / delta-rule kernels once (`s1_batch_plan`) and returns the
+        device buffer that holds them; `use_plan(plan)` then lets every layer's calls skip their own table copy."""
+        import numpy as np
+        cu = np.ascontiguousarray(cu_seqlens_host, dtype=np.int32)
+        need = int(self._lib.s1_batch_plan_bytes(len(cu) - 1, int(total_tokens)))
+        buf = torch.empty(need + 256, dtype=torch.uint8, device=torch.device("cuda", self.ordinal))
+        plan = buf[(-buf.data_ptr()) % 256:]
+        self.check(self._lib.s1_batch_plan(self.handle, cu.ctypes.data_as(C.POINTER(C.c_int32)), len(cu) - 1, int(total_tokens),
+                                           C.c_void_p(plan.data_ptr()), need))
+        plan._s1_shape = (len(cu) - 1, int(total_tokens))   # (num_seqs, total_tokens) the plan describes
+        plan._s1_owner = buf
+        return plan
+
+    def use_plan(self, plan: Optional[torch.Tensor]) -> None:
+        self.check(self._lib.s1_use_batch_plan(self.handle, C.c_void_p(0 if plan is None else plan.data_ptr())))
+        self._plan = plan
+
+    def plan_covers(self, num_seqs: int, total_tokens: int) -> bool:
+        """Whether the plan in use describes a batch of this shape (the caller vouches that it is the same batch)."""
+        plan = getattr(self, "_plan", None)
+        return plan is not None and plan._s1_shape == (int(num_seqs), int(total_tokens))
+
     def launch_count(self) -> int:
         return int(self._lib.s1_launch_count(self.handle))
 

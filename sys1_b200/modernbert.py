@@ -104,8 +104,9 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     ctx = device.load(q.device.index)
     need = int(ctx._lib.s1_attention_workspace(len(cu) - 1, T))
     ws = ctx.workspace(need)
+    planned = ctx.plan_covers(len(cu) - 1, T)   # the batch's tables are already on the device: no per-call copy
     rc = ctx._lib.s1_attention(ctx.handle, C.c_void_p(q.data_ptr()), q.stride(0), C.c_void_p(k.data_ptr()), k.stride(0),
-                               C.c_void_p(v.data_ptr()), v.stride(0), cu.ctypes.data_as(C.POINTER(C.c_int32)), len(cu) - 1, T, H, D,
+                               C.c_void_p(v.data_ptr()), v.stride(0), None if planned else cu.ctypes.data_as(C.POINTER(C.c_int32)), len(cu) - 1, T, H, D,
                                int(window), C.c_float(D ** -0.5 if scale is None else scale), C.c_void_p(out.data_ptr()),
                                out.stride(0), C.c_void_p(ws.data_ptr()), ws.numel())
     ctx.check(rc)
@@ -187,9 +188,26 @@ class Encoder:
         bounds, max_len = self._bounds(cu_seqlens)
         pos = positions.to(torch.int32).contiguous()
         states = []
-        for i in range(len(self.layers)):
-            x = self._layer(i, x, bounds, pos, max_len)
-            if collect:
-                states.append(x.clone())
+        from . import device
+        ctx = device.load(x.device.index)
+        previous = getattr(ctx, "_plan", None)
+        ctx.use_plan(self._plan(ctx, bounds))        # one table copy per batch, not one per layer
+        try:
+            for i in range(len(self.layers)):
+                x = self._layer(i, x, bounds, pos, max_len)
+                if collect:
+                    states.append(x.clone())
+        finally:
+            ctx.use_plan(previous)
         y = self._ln(x, "final_norm")
         return (y, states) if collect else y
+
+    def _plan(self, ctx, bounds):
+        """The batch plan of these sequence offsets; the last few are kept, so a batch that comes again costs no copy."""
+        key = (id(ctx), tuple(bounds))
+        cache = self.__dict__.setdefault("_plans", {})
+        if key not in cache:
+            if len(cache) >= 4:
+                cache.pop(next(iter(cache)))
+            cache[key] = ctx.batch_plan(bounds, bounds[-1])
+        return cache[key]

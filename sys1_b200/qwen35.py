@@ -195,10 +195,11 @@ class LinearAttention:
         else:
             need = int(ctx._lib.s1_gated_delta_rule_workspace(len(cu) - 1, T, self.value_heads))
             ptr = ctx.workspace(need).data_ptr()
+            planned = ctx.plan_covers(len(cu) - 1, T)
             rc = ctx._lib.s1_gated_delta_rule(
                 ctx.handle, C.c_void_p(mixed.data_ptr()), mixed.stride(0), C.c_void_p(bb.data_ptr()), C.c_void_p(aa.data_ptr()),
                 bb.stride(0), C.c_void_p(self.dt_bias.data_ptr()), C.c_void_p(self.decay.data_ptr()), C.c_void_p(zz.data_ptr()),
-                zz.stride(0), C.c_void_p(self.norm.data_ptr()), C.c_float(self.eps), cu.ctypes.data_as(C.POINTER(C.c_int32)),
+                zz.stride(0), C.c_void_p(self.norm.data_ptr()), C.c_float(self.eps), None if planned else cu.ctypes.data_as(C.POINTER(C.c_int32)),
                 len(cu) - 1, T, self.key_heads, self.value_heads, C.c_void_p(y.data_ptr()), y.stride(0), C.c_void_p(ptr), need)
             ctx.check(rc)
         return y
@@ -251,11 +252,12 @@ def attention_causal_gqa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_s
     ctx = device.load(q.device.index)
     need = int(ctx._lib.s1_attention_gqa_workspace(len(cu) - 1, T))
     ws = ctx.workspace(need)
+    planned = ctx.plan_covers(len(cu) - 1, T)
     rc = ctx._lib.s1_attention_gqa(
         ctx.handle, C.c_void_p(q.data_ptr()), q.stride(0), q.stride(1), C.c_void_p(k.data_ptr()), k.stride(0), k.stride(1),
         C.c_void_p(v.data_ptr()), v.stride(0), v.stride(1), C.c_void_p(gate.data_ptr() if gate is not None else 0),
         gate.stride(0) if gate is not None else 0, gate.stride(1) if gate is not None else 0,
-        cu.ctypes.data_as(C.POINTER(C.c_int32)), len(cu) - 1, T, H, KV, D, C.c_float(D ** -0.5), C.c_void_p(out.data_ptr()),
+        None if planned else cu.ctypes.data_as(C.POINTER(C.c_int32)), len(cu) - 1, T, H, KV, D, C.c_float(D ** -0.5), C.c_void_p(out.data_ptr()),
         out.stride(0), C.c_void_p(ws.data_ptr()), ws.numel())
     ctx.check(rc)
     return out
@@ -353,9 +355,28 @@ class Decoder:
         x = _norm.embedding(self.w["embed_tokens"], ids.to(torch.int32).contiguous())
         pos = positions.to(torch.int32).contiguous()
         states = []
-        for layer in self.layers:
-            x = layer.forward(x, cu_seqlens_host, pos, inplace=True)  # x is this call's own buffer (the embedding rows)
-            if collect:
-                states.append(x.clone())
+        ctx = device.load(x.device.index)
+        bounds = [int(v) for v in cu_seqlens_host]
+        previous = getattr(ctx, "_plan", None)
+        ctx.use_plan(batch_plan_cached(self, ctx, bounds))   # one table copy per batch, not one per layer
+        try:
+            for layer in self.layers:
+                x = layer.forward(x, cu_seqlens_host, pos, inplace=True)  # x is this call's own buffer (the embedding rows)
+                if collect:
+                    states.append(x.clone())
+        finally:
+            ctx.use_plan(previous)
         y = self.norm(x)
         return (y, states) if collect else y
+
+
+def batch_plan_cached(owner, ctx, bounds):
+    """The batch plan (`s1_batch_plan`) of these sequence offsets on this context; `owner` keeps the last few, so a
+    batch that comes again costs no copy."""
+    key = (id(ctx), tuple(bounds))
+    cache = owner.__dict__.setdefault("_plans", {})
+    if key not in cache:
+        if len(cache) >= 4:
+            cache.pop(next(iter(cache)))
+        cache[key] = ctx.batch_plan(bounds, bounds[-1])
+    return cache[key]

@@ -277,11 +277,17 @@ class Decoder:
         group itself waits for it (by ticket) before its next stage, so one group computes while the other's partial sums
         travel: mixer(0), [sum(0) | mixer(1)], [sum(1) | mlp(0)], [sum(0) | mlp(1)], [sum(1) | next mixer(0)], ...
         The projections run on `SMs - comm_sms` SMs meanwhile so that the collective always finds room."""
+        from .qwen35 import batch_plan_cached
         pos = positions.to(torch.int32).contiguous()
         ctx = self.tp.ctx
+        previous = getattr(ctx, "_plan", None)
         if micro_batches <= 1:
-            for layer in self.layers:
-                x = layer.forward(x, cu_seqlens_host, pos, exchange=exchange)
+            ctx.use_plan(batch_plan_cached(self, ctx, [int(c) for c in cu_seqlens_host]))
+            try:
+                for layer in self.layers:
+                    x = layer.forward(x, cu_seqlens_host, pos, exchange=exchange)
+            finally:
+                ctx.use_plan(previous)
             return self.norm(x)
         if not x.is_contiguous():
             raise ValueError("the residual stream must be contiguous")
@@ -289,7 +295,8 @@ class Decoder:
         for s0, s1 in split_sequences(cu_seqlens_host, micro_batches):
             a, b = int(cu_seqlens_host[s0]), int(cu_seqlens_host[s1])
             if b > a:
-                groups.append((x[a:b], [int(c) - a for c in cu_seqlens_host[s0:s1 + 1]], pos[a:b]))
+                cu_g = [int(c) - a for c in cu_seqlens_host[s0:s1 + 1]]
+                groups.append((x[a:b], cu_g, pos[a:b], batch_plan_cached(self, ctx, cu_g)))
         tickets = [None] * len(groups)
         carve = exchange and self.tp.size > 1 and self.comm_sms > 0
         if carve:
@@ -297,14 +304,16 @@ class Decoder:
         try:
             for layer in self.layers:
                 for stage in (0, 1):
-                    for i, (xg, cu, pg) in enumerate(groups):
+                    for i, (xg, cu, pg, plan) in enumerate(groups):
                         if tickets[i] is not None:
                             ctx.all_reduce_wait_ticket(tickets[i])
+                        ctx.use_plan(plan)
                         tickets[i] = layer.mixer_part(xg, cu, pg, exchange) if stage == 0 else layer.mlp_part(xg, exchange)
             for t in tickets:
                 if t is not None:
                     ctx.all_reduce_wait_ticket(t)
         finally:
+            ctx.use_plan(previous)
             if carve:
                 ctx.set_option("gemm_sms", 0)
         return self.norm(x)

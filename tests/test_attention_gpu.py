@@ -124,3 +124,35 @@ def test_full_size_batch_properties(ctx):
             want = oracle.attention(sub[:, 0], sub[:, 1], sub[:, 2], window)
             assert max_rel(packed[a:z].float().cpu(), want) <= 2e-2
     ctx.sync()
+
+
+def test_batch_plan_replaces_the_per_call_tables(ctx):
+    """`s1_batch_plan`: the query-block tables built once per batch; the calls then pass no offsets and copy nothing, and
+    their results are bit-identical to the per-call form, for the global and the banded variant."""
+    lens = [300, 1, 129, 64, 700]
+    cu = np.cumsum([0] + lens).astype(np.int32)
+    T = int(cu[-1])
+    g = torch.Generator().manual_seed(23)
+    q, k, v = (torch.randn(T, 4, 64, generator=g).to(torch.bfloat16).to(DEV) for _ in range(3))
+    want = {w: modernbert.attention_varlen(q, k, v, cu, window=w).clone() for w in (-1, 64)}
+    plan = ctx.batch_plan(cu, T)
+    ctx.use_plan(plan)
+    try:
+        assert ctx.plan_covers(len(lens), T)
+        for w in (-1, 64):
+            assert torch.equal(modernbert.attention_varlen(q, k, v, cu, window=w), want[w])
+        # a batch of another shape is not covered by the plan: its call falls back to its own table
+        other = modernbert.attention_varlen(q[:300], k[:300], v[:300], np.array([0, 300], dtype=np.int32))
+        assert torch.equal(other, want[-1][:300])
+        # raw calls: no offsets and no plan for that shape -> rejected; no offsets with the plan -> accepted without a workspace
+        import ctypes as C
+        out = torch.empty(T, 256, dtype=torch.bfloat16, device=DEV)
+        P = lambda t: C.c_void_p(t.data_ptr())
+        rc = ctx._lib.s1_attention(ctx.handle, P(q), 256, P(k), 256, P(v), 256, None, len(lens) + 1, T, 4, 64, -1, C.c_float(0.125), P(out), 256, None, 0)
+        assert rc == -1 and b"no batch plan" in ctx._lib.s1_last_error(ctx.handle)
+        rc = ctx._lib.s1_attention(ctx.handle, P(q), 256, P(k), 256, P(v), 256, None, len(lens), T, 4, 64, -1, C.c_float(0.125), P(out), 256, None, 0)
+        assert rc == 0
+        assert torch.equal(out, want[-1])
+    finally:
+        ctx.use_plan(None)
+    ctx.sync()
