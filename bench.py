@@ -172,6 +172,24 @@ def _time_cpu(step, steps, warmup, budget_s):
     return sum(times) / len(times), len(times)
 
 
+def cpu_encoder_base(budget_s: float = 30.0):
+    """The ModernBERT-base configuration whole, on the host: 22 layers, ids uniform over 50368, 8 sequences of 512, seed
+    1001, f32 oracle, nothing extrapolated."""
+    import oracle
+    cores = host_threads()
+    cfg = oracle.EncoderConfig()
+    w = oracle.init_weights(cfg, 1001)
+    ids = torch.randint(0, 50368, (8, 512), generator=torch.Generator().manual_seed(1001))
+
+    def step():
+        for row in ids:
+            oracle.encoder_forward(row, w, cfg, dtype="f32")
+
+    dt, n = _time_cpu(step, 5, 1, budget_s)
+    return {"value": 4096 / dt, "unit": "tokens/s", "cores": cores, "kind": "port", "seconds_per_forward": dt,
+            "sample": f"the whole configuration (22 layers, 8 x 512 tokens), f32 torch CPU oracle, {n} timed passes"}
+
+
 def cpu_encoder(budget_s: float = 20.0):
     """ModernBERT-large-shaped oracle on the host: two layers (one global, one local) over log-uniform sequences that total
     4096 tokens, f32; tokens/s for the 28-layer model extrapolated by 14 (the layers alternate between those two kinds)."""
@@ -188,7 +206,7 @@ def cpu_encoder(budget_s: float = 20.0):
         for ids in seqs:
             oracle.encoder_forward(ids, w, cfg, dtype="f32")
 
-    dt, n = _time_cpu(step, 3, 1, budget_s)
+    dt, n = _time_cpu(step, 2, 1, budget_s)
     return {"value": 4096 / (dt * 14), "unit": "tokens/s", "cores": cores, "kind": "port",
             "sample": f"2 of 28 layers (1 global + 1 local) on {len(seqs)} sequences totalling 4096 tokens, f32 torch CPU oracle, "
                       f"{n} timed passes; the 28-layer figure is that time x 14 (extrapolated)"}
@@ -293,14 +311,18 @@ def _timed(fn, n, world, dev):
 
 
 # ================================================================================================ encoder
-def encoder_block(args, rank, world, dev, steps, warmup):
-    """ModernBERT-large-shaped encoder forward (28 layers, hidden 1024, 16 heads, GeGLU 2 x 2624, window 128, global every
+def encoder_block(args, rank, world, dev, steps, warmup, shape="large"):
+    """`shape` "base": the ModernBERT-base configuration on its configured input (22 layers, hidden 768, 12 heads, GeGLU
+    2 x 1152; ids uniform over 50368, 8 sequences of 512, seed 1001). Otherwise:
+    ModernBERT-large-shaped encoder forward (28 layers, hidden 1024, 16 heads, GeGLU 2 x 2624, window 128, global every
     3rd layer) over a packed batch of 32768 tokens with log-uniform lengths in [8, 8192], one replica per GPU. Every stage
     goes through the C ABI. Also times one global and one banded attention launch on the same batch."""
     from sys1_b200 import batching, device, modernbert, pipeline
     cfg = SimpleNamespace(vocab_size=50368, hidden_size=1024, num_hidden_layers=28, num_attention_heads=16, intermediate_size=2624,
                           layer_norm_eps=1e-5, global_attn_every_n_layers=3, local_attention=128, global_rope_theta=160000.0,
                           local_rope_theta=10000.0)
+    if shape == "base":
+        cfg.hidden_size, cfg.num_hidden_layers, cfg.num_attention_heads, cfg.intermediate_size = 768, 22, 12, 1152
     g = torch.Generator(device=dev).manual_seed(1003)
     mk = lambda *shape: (torch.randn(*shape, device=dev, generator=g) * 0.02).to(torch.bfloat16)
     ones = lambda: torch.ones(cfg.hidden_size, device=dev, dtype=torch.bfloat16)
@@ -313,9 +335,14 @@ def encoder_block(args, rank, world, dev, steps, warmup):
     enc = modernbert.Encoder(w, cfg)
     ctx = device.load(dev.index)
     T = args.encoder_tokens
-    lens = batching.synthetic_lengths(1003 + rank, 8, 8192, T, log_uniform=True)
+    if shape == "base":
+        import numpy as np
+        T, lens = 4096, np.full(8, 512, dtype=np.int32)
+        ids = torch.randint(0, 50368, (8, 512), generator=torch.Generator().manual_seed(1001)).reshape(-1).to(torch.int32).to(dev)
+    else:
+        lens = batching.synthetic_lengths(1003 + rank, 8, 8192, T, log_uniform=True)
+        ids = torch.randint(0, cfg.vocab_size, (T,), device=dev, generator=g).to(torch.int32)
     batch, _ = batching.pack_next(lens, batching.BatcherConfig(token_budget=T))
-    ids = torch.randint(0, cfg.vocab_size, (T,), device=dev, generator=g).to(torch.int32)
     pos = torch.from_numpy(batch.positions).to(dev)
     fwd = lambda: enc.forward(ids, batch.cu_seqlens, pos)
     for _ in range(warmup):
@@ -358,10 +385,12 @@ def encoder_block(args, rank, world, dev, steps, warmup):
             pairs += n * n if window < 0 or n <= window else n * (2 * window + 1) - window * (window + 1)
         attn_stats[name] = {"us": us, "tflops": 4.0 * D * H * pairs / (us * 1e-6) / 1e12}
     ctx.sync()
-    flops_tok = 28 * 2 * (1024 * 3072 + 1024 * 1024 + 1024 * 5248 + 2624 * 1024)
+    hs, it = cfg.hidden_size, cfg.intermediate_size
+    flops_tok = cfg.num_hidden_layers * 2 * (hs * 3 * hs + hs * hs + hs * 2 * it + it * hs)
+    what = ("ModernBERT-base encoder forward, 22 layers, 8 sequences of 512 ids uniform over 50368 (seed 1001)" if shape == "base" else
+            f"ModernBERT-large-shaped encoder forward, 28 layers, packed T={T} per GPU, lengths log-uniform [8,8192]")
     return {"metric": "encoder tokens/s", "value": world * T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "steps": steps,
-            "config": {"workload": f"ModernBERT-large-shaped encoder forward, 28 layers, packed T={T} per GPU, lengths log-uniform "
-                                   "[8,8192], every stage through the C ABI (projections, attention, norms, RoPE, embedding lookup)",
+            "config": {"workload": what + ", every stage through the C ABI (projections, attention, norms, RoPE, embedding lookup)",
                        "sequences": int(len(lens)), "parallelism": f"replicas x{world}"},
             "projection_tflops": world * T * flops_tok / (ms * 1e-3) / 1e12, "attention": attn_stats,
             "e2e": {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
@@ -799,12 +828,14 @@ def reference_line(args, warmup):
         workload = (f"ModernBERT-base projection microbench, packed ragged batch, T={T} tokens (lengths U[16,512]), "
                     "Wqkv / Wo+residual / Wi+GeGLU / MLP-out+residual")
     else:
-        cb = cpu_encoder(60.0) if args.workload == "encoder" else cpu_decoder("small" if args.workload == "decoder" else "27b",
+        cb = cpu_encoder_base(60.0) if args.workload == "base" else cpu_encoder(60.0) if args.workload == "encoder" else cpu_decoder("small" if args.workload == "decoder" else "27b",
                                                                                 2048 if args.workload == "decoder" else 512, 60.0)
         val, n, ms = cb["value"], 1, None
-        metric, unit = {"encoder": "encoder tokens/s", "decoder": "decoder tokens/s", "tp": "27B layer-group tokens/s"}[args.workload], "tokens/s"
-        workload = {"encoder": "ModernBERT-large-shaped encoder forward", "decoder": "Qwen3.5-small-shaped hybrid decoder forward",
-                    "tp": "27B-shaped hybrid decoder forward"}[args.workload] + " (CPU sample, extrapolated as the sample says)"
+        metric, unit = {"base": "encoder tokens/s", "encoder": "encoder tokens/s", "decoder": "decoder tokens/s",
+                        "tp": "27B layer-group tokens/s"}[args.workload], "tokens/s"
+        workload = {"base": "ModernBERT-base encoder forward, 8 x 512 ids", "encoder": "ModernBERT-large-shaped encoder forward",
+                    "decoder": "Qwen3.5-small-shaped hybrid decoder forward",
+                    "tp": "27B-shaped hybrid decoder forward"}[args.workload] + " (CPU oracle; sample and extrapolation as the sample says)"
     return {"impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": n, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload, "tokens": T, "parallelism": "host cores"}, "cpu_baseline": cb,
@@ -824,7 +855,7 @@ def main():
                     help="a short run for a profiler: the timed loop only (no sustained loop, budgets, library GEMMs, end-to-end arm, "
                          "secondary workloads or CPU baseline)")
     ap.add_argument("--no-secondary", action="store_true", help="projections workload: leave out the encoder / decoder / tp blocks")
-    ap.add_argument("--workload", default="projections", choices=["projections", "encoder", "decoder", "tp"],
+    ap.add_argument("--workload", default="projections", choices=["projections", "base", "encoder", "decoder", "tp"],
                     help="projections (default): the headline line with every block; encoder / decoder / tp: that block alone, as a line")
     ap.add_argument("--encoder-tokens", type=int, default=32768)
     ap.add_argument("--decoder-tokens", type=int, default=16384)
@@ -872,9 +903,18 @@ def main():
                 line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                         "sample": f"{args.cpu_sample_tokens} of the {args.tokens} token rows, same four projections, "
                                                   f"torch CPU f32 oracle, {n} timed passes"}
+                # the CPU oracle beside the secondary workloads too (bounded samples, extrapolated as each sample says)
+                for name, fn in (("encoder", lambda: cpu_encoder(6.0)), ("decoder", lambda: cpu_decoder("small", 2048, 6.0)),
+                                 ("tp", lambda: cpu_decoder("27b", 512, 6.0))):
+                    if isinstance(line.get(name), dict) and "error" not in line[name]:
+                        try:
+                            line[name]["cpu_baseline"] = fn()
+                        except Exception as exc:
+                            line[name]["cpu_baseline"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
         else:
             steps = max(3, min(args.steps, 20))
-            block = {"encoder": encoder_block, "decoder": decoder_block, "tp": tp_block}[args.workload](args, rank, world, dev, steps, warmup)
+            fn = {"base": lambda *a: encoder_block(*a, shape="base"), "encoder": encoder_block, "decoder": decoder_block, "tp": tp_block}[args.workload]
+            block = fn(args, rank, world, dev, steps, warmup)
             line = None
             if rank == 0:
                 line = {"n_gpus": world, "warmup": warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
