@@ -406,7 +406,7 @@ def decoder_block(args, rank, world, dev, steps, warmup):
     from sys1_b200 import batching, device, qwen35
     cfg = _decoder_cfg("small", 24, 151936)
     w = _decoder_group_weights(cfg, 1004, dev, torch.bfloat16)
-    dec = qwen35.Decoder(w, cfg)
+    dec = qwen35.Decoder(w, cfg, recurrence=args.recurrence)
     ctx = device.load(dev.index)
     T = args.decoder_tokens
     lens = batching.synthetic_lengths(1004 + rank, 64, 2048, T)
@@ -425,7 +425,8 @@ def decoder_block(args, rank, world, dev, steps, warmup):
     flops_tok = 18 * 43_057_152 + 6 * 36_700_160  # projection flops per token: linear-attention / full-attention layers
     return {"metric": "decoder tokens/s", "value": world * T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "steps": steps,
             "config": {"workload": f"Qwen3.5-small-shaped hybrid decoder forward, 24 layers, packed T={T} per GPU, lengths U[64,2048], "
-                                   "every stage through the C ABI", "sequences": int(len(lens)), "parallelism": f"replicas x{world}"},
+                                   "every stage through the C ABI" + ("" if args.recurrence == "chunked" else ", exact f32 token-sequential delta rule"),
+                       "sequences": int(len(lens)), "parallelism": f"replicas x{world}"},
             "projection_tflops": world * T * flops_tok / (ms * 1e-3) / 1e12, "gpu_launches": launches}
 
 
@@ -860,6 +861,8 @@ def main():
     ap.add_argument("--encoder-tokens", type=int, default=32768)
     ap.add_argument("--decoder-tokens", type=int, default=16384)
     ap.add_argument("--tp-tokens", type=int, default=65536)
+    ap.add_argument("--recurrence", default="chunked", choices=["chunked", "exact"],
+                    help="decoder: the gated delta rule in 64-token chunks on the tensor cores (default) or the exact f32 token-sequential kernel")
     ap.add_argument("--sustain-seconds", type=float, default=2.2)
     ap.add_argument("--slabs", type=int, default=4, help="tp: row slabs the exchange is pipelined in")
     ap.add_argument("--comm-ctas", type=int, default=0, help="tp: blocks the all-reduce may use (0 = NCCL's default)")

@@ -49,62 +49,82 @@ __global__ void __launch_bounds__(256) s1_conv_silu_kernel(const __nv_bfloat16* 
     *reinterpret_cast<uint4*>(y + static_cast<long long>(t) * ldy + c0) = *reinterpret_cast<const uint4*>(out);
 }
 
-// The same arithmetic for the usual 4 taps with each thread walking TT consecutive tokens of its 8 channels: the
-// weights (64 contiguous bytes) and the previous three rows stay in registers, so every input row is read once and the
-// weights once per TT tokens (the per-token kernel above re-reads both for every token, and its 2-byte weight loads
-// spread one warp access over 16 cache lines).
-template <int TAPS, int TT>
-__global__ void __launch_bounds__(256) s1_conv_silu_walk_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
-                                                                const __nv_bfloat16* __restrict__ w, const int32_t* __restrict__ positions,
-                                                                int T, int C, __nv_bfloat16* __restrict__ y, long long ldy) {
+// The same arithmetic for the usual 4 taps, memory-bound: each thread takes 8 channels (16 bytes) of TT consecutive tokens.
+//  * every row it needs (TT rows and the three before them) is requested up front, so TT + 3 independent 16-byte loads
+//    are in flight per thread; each input row is read once (plus 3 / TT for the history) and the weights once per thread;
+//  * the per-tap arithmetic is native bf16x2: `__hmul2` is the exact product rounded once to bf16 and `__hadd2` the
+//    sum rounded once, which is what the reference's `T(__fadd_rn(float(value), float(T(product))))` yields (the f32
+//    product of two bf16 values is exact; an f32 sum of two bf16 values is either exact or, when the exponents are
+//    more than 16 bits apart, rounds to the larger operand either way);
+//  * a tap that would read a token before the start of the sequence contributes a zero row (the reference skips it).
+// SiLU in f32 with the fast exponential and reciprocal (relative error ~2^-22, far below the bf16 rounding that follows).
+template <int TT>
+__global__ void __launch_bounds__(256, 2) s1_conv_silu_walk_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                                   const __nv_bfloat16* __restrict__ w, const int32_t* __restrict__ positions,
+                                                                   int T, int C, __nv_bfloat16* __restrict__ y, long long ldy) {
+    constexpr int TAPS = 4;
     const int groups = C / 8;
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const long long chunks = (T + TT - 1) / TT;
     if (idx >= chunks * groups) return;
     const int c0 = static_cast<int>(idx % groups) * 8;
     const int t0 = static_cast<int>(idx / groups) * TT;
-    float wv[8 * TAPS];  // wv[e * TAPS + tap]
+    // rows t0 - 3 .. t0 + TT - 1, all requested before any is used
+    uint4 rows[TT + TAPS - 1];
 #pragma unroll
-    for (int i = 0; i < TAPS; ++i) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(w + static_cast<long long>(c0) * TAPS) + i);
-        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) wv[8 * i + e] = __bfloat162float(h[e]);
+    for (int i = 0; i < TT + TAPS - 1; ++i) {
+        const int t = t0 - (TAPS - 1) + i;
+        rows[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (t >= 0 && t < T) rows[i] = __ldg(reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx + c0));
     }
-    float hist[TAPS][8];  // hist[TAPS - 1] = current row, hist[TAPS - 1 - b] = the row b tokens back
+    int pos[TT];
 #pragma unroll
-    for (int b = 1; b < TAPS; ++b) {
-        const int t = t0 - b;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (t >= 0) raw = __ldg(reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx + c0));
-        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+    for (int i = 0; i < TT; ++i) pos[i] = (t0 + i < T) ? __ldg(positions + t0 + i) : 0;
+    // weights [8 channels][4 taps] (64 contiguous bytes) -> per tap four bf16x2 pairs of neighbouring channels
+    uint32_t wraw[16];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) hist[TAPS - 1 - b][e] = __bfloat162float(h[e]);
+    for (int i = 0; i < 4; ++i) {
+        const uint4 r = __ldg(reinterpret_cast<const uint4*>(w + static_cast<long long>(c0) * TAPS) + i);
+        wraw[4 * i] = r.x, wraw[4 * i + 1] = r.y, wraw[4 * i + 2] = r.z, wraw[4 * i + 3] = r.w;
     }
+    // channel ch holds taps (0,1) in wraw[2 ch] and (2,3) in wraw[2 ch + 1]; pair p = channels 2p, 2p + 1
+    __nv_bfloat162 wt[TAPS][4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const uint32_t a01 = wraw[4 * p], a23 = wraw[4 * p + 1], b01 = wraw[4 * p + 2], b23 = wraw[4 * p + 3];
+        const uint32_t t0w = __byte_perm(a01, b01, 0x5410), t1w = __byte_perm(a01, b01, 0x7632);
+        const uint32_t t2w = __byte_perm(a23, b23, 0x5410), t3w = __byte_perm(a23, b23, 0x7632);
+        wt[0][p] = *reinterpret_cast<const __nv_bfloat162*>(&t0w);
+        wt[1][p] = *reinterpret_cast<const __nv_bfloat162*>(&t1w);
+        wt[2][p] = *reinterpret_cast<const __nv_bfloat162*>(&t2w);
+        wt[3][p] = *reinterpret_cast<const __nv_bfloat162*>(&t3w);
+    }
+    const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
-        const int t = t0 + tt;
-        if (t < T) {
-            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * ldx + c0));
-            const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+        if (t0 + tt >= T) break;
+        __nv_bfloat162 acc[4] = {zero2, zero2, zero2, zero2};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) hist[TAPS - 1][e] = __bfloat162float(h[e]);
-            const int pos = positions[t];
-            __nv_bfloat16 out[8];
+        for (int tap = 0; tap < TAPS; ++tap) {
+            const int back = TAPS - 1 - tap;
+            const bool live = back <= pos[tt];  // the same for the whole row
+            const uint4 r = rows[tt + tap];     // row t - back
+            const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                float acc = 0.f;
-#pragma unroll
-                for (int tap = 0; tap < TAPS; ++tap)
-                    if (TAPS - 1 - tap <= pos) acc = bf16r(acc + bf16r(hist[tap][e] * wv[e * TAPS + tap]));
-                out[e] = __float2bfloat16_rn(acc / (1.f + expf(-acc)));
+            for (int p = 0; p < 4; ++p) {
+                const __nv_bfloat162 xv = live ? *reinterpret_cast<const __nv_bfloat162*>(&rr[p]) : zero2;
+                acc[p] = __hadd2(acc[p], __hmul2(xv, wt[tap][p]));
             }
-            *reinterpret_cast<uint4*>(y + static_cast<long long>(t) * ldy + c0) = *reinterpret_cast<const uint4*>(out);
-#pragma unroll
-            for (int b = 0; b + 1 < TAPS; ++b)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) hist[b][e] = hist[b + 1][e];
         }
+        uint32_t out[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const float2 a = __bfloat1622float2(acc[p]);
+            const float s0 = a.x * __frcp_rn(1.f + __expf(-a.x)), s1 = a.y * __frcp_rn(1.f + __expf(-a.y));
+            const __nv_bfloat162 o = __floats2bfloat162_rn(s0, s1);
+            out[p] = *reinterpret_cast<const uint32_t*>(&o);
+        }
+        *reinterpret_cast<uint4*>(y + static_cast<long long>(t0 + tt) * ldy + c0) = make_uint4(out[0], out[1], out[2], out[3]);
     }
 }
 
@@ -166,7 +186,7 @@ __global__ void __launch_bounds__(256) s1_delta_finish_kernel(const float* __res
     float ss = ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w;
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
-    const float inv = 1.f / sqrtf(ss * (1.f / 128.f) + eps);
+    const float inv = rsqrtf(ss * (1.f / 128.f) + eps);
     const uint2 zr = __ldg(reinterpret_cast<const uint2*>(z + static_cast<long long>(t) * ldz + hv * 128 + 4 * lane));
     const uint2 wr = __ldg(reinterpret_cast<const uint2*>(norm_w + 4 * lane));
     const __nv_bfloat16* zv = reinterpret_cast<const __nv_bfloat16*>(&zr);
@@ -176,7 +196,8 @@ __global__ void __launch_bounds__(256) s1_delta_finish_kernel(const float* __res
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
         const float gate = __bfloat162float(zv[e]);
-        out[e] = __float2bfloat16_rn(of[e] * inv * __bfloat162float(wv[e]) * (gate / (1.f + expf(-gate))));
+        // fast exponential and reciprocal: relative error ~2^-22, far below the bf16 rounding of the result
+        out[e] = __float2bfloat16_rn(of[e] * inv * __bfloat162float(wv[e]) * (gate * __frcp_rn(1.f + __expf(-gate))));
     }
     *reinterpret_cast<uint2*>(y + static_cast<long long>(t) * ldy + hv * 128 + 4 * lane) = *reinterpret_cast<const uint2*>(out);
 }
@@ -208,7 +229,7 @@ extern "C" int s1_conv_silu(s1_ctx* ctx, const void* x, long long ldx, const voi
     if (taps == 4 && al16(weight)) {
         constexpr int TT = 16;
         const long long n = static_cast<long long>((total_tokens + TT - 1) / TT) * (channels / 8);
-        s1_conv_silu_walk_kernel<4, TT><<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
+        s1_conv_silu_walk_kernel<TT><<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
             static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(weight), positions, total_tokens, channels,
             static_cast<__nv_bfloat16*>(y), ldy);
     } else {
