@@ -52,14 +52,23 @@ __global__ void __launch_bounds__(256) s1_conv_silu_kernel(const __nv_bfloat16* 
 // The same arithmetic for the usual 4 taps, memory-bound: each thread takes 8 channels (16 bytes) of TT consecutive tokens.
 //  * every row it needs (TT rows and the three before them) is requested up front, so TT + 3 independent 16-byte loads
 //    are in flight per thread; each input row is read once (plus 3 / TT for the history) and the weights once per thread;
-//  * the per-tap arithmetic is native bf16x2: `__hmul2` is the exact product rounded once to bf16 and `__hadd2` the
+//  * the per-tap arithmetic is native bf16x2: `__hmul2_rn` is the exact product rounded once to bf16 and `__hadd2_rn` the
 //    sum rounded once, which is what the reference's `T(__fadd_rn(float(value), float(T(product))))` yields (the f32
 //    product of two bf16 values is exact; an f32 sum of two bf16 values is either exact or, when the exponents are
 //    more than 16 bits apart, rounds to the larger operand either way);
 //  * a tap that would read a token before the start of the sequence contributes a zero row (the reference skips it).
 // SiLU in f32 with the fast exponential and reciprocal (relative error ~2^-22, far below the bf16 rounding that follows).
+// TT = 8: 11 rows (44 registers) in flight per thread, three blocks per SM.
+// x / (1 + e^-x) with the special-function unit's exponential and reciprocal (two instructions instead of two library calls)
+__device__ __forceinline__ float silu_fast(float v) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+    return v * r;
+}
+
 template <int TT>
-__global__ void __launch_bounds__(256, 2) s1_conv_silu_walk_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+__global__ void __launch_bounds__(256, 3) s1_conv_silu_walk_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                                    const __nv_bfloat16* __restrict__ w, const int32_t* __restrict__ positions,
                                                                    int T, int C, __nv_bfloat16* __restrict__ y, long long ldy) {
     constexpr int TAPS = 4;
@@ -100,28 +109,29 @@ __global__ void __launch_bounds__(256, 2) s1_conv_silu_walk_kernel(const __nv_bf
         wt[3][p] = *reinterpret_cast<const __nv_bfloat162*>(&t3w);
     }
     const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
+    // no sequence starts inside or just before this run of tokens (the usual case; the same for a whole warp when a row
+    // has at least 32 channel groups): every tap of every token is live and no row has to be masked
+    bool clean = true;
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) clean = clean && (pos[tt] >= TAPS - 1 || t0 + tt >= T);
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
         if (t0 + tt >= T) break;
         __nv_bfloat162 acc[4] = {zero2, zero2, zero2, zero2};
 #pragma unroll
         for (int tap = 0; tap < TAPS; ++tap) {
-            const int back = TAPS - 1 - tap;
-            const bool live = back <= pos[tt];  // the same for the whole row
-            const uint4 r = rows[tt + tap];     // row t - back
-            const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+            const uint4 r = rows[tt + tap];     // row t - (TAPS - 1 - tap)
+            uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+            if (!clean && TAPS - 1 - tap > pos[tt]) rr[0] = rr[1] = rr[2] = rr[3] = 0u;  // a row of the previous sequence
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                const __nv_bfloat162 xv = live ? *reinterpret_cast<const __nv_bfloat162*>(&rr[p]) : zero2;
-                acc[p] = __hadd2(acc[p], __hmul2(xv, wt[tap][p]));
-            }
+            for (int p = 0; p < 4; ++p)  // the _rn forms are never contracted into one fma
+                acc[p] = __hadd2_rn(acc[p], __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&rr[p]), wt[tap][p]));
         }
         uint32_t out[4];
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
             const float2 a = __bfloat1622float2(acc[p]);
-            const float s0 = a.x * __frcp_rn(1.f + __expf(-a.x)), s1 = a.y * __frcp_rn(1.f + __expf(-a.y));
-            const __nv_bfloat162 o = __floats2bfloat162_rn(s0, s1);
+            const __nv_bfloat162 o = __floats2bfloat162_rn(silu_fast(a.x), silu_fast(a.y));
             out[p] = *reinterpret_cast<const uint32_t*>(&o);
         }
         *reinterpret_cast<uint4*>(y + static_cast<long long>(t0 + tt) * ldy + c0) = make_uint4(out[0], out[1], out[2], out[3]);
@@ -197,7 +207,7 @@ __global__ void __launch_bounds__(256) s1_delta_finish_kernel(const float* __res
     for (int e = 0; e < 4; ++e) {
         const float gate = __bfloat162float(zv[e]);
         // fast exponential and reciprocal: relative error ~2^-22, far below the bf16 rounding of the result
-        out[e] = __float2bfloat16_rn(of[e] * inv * __bfloat162float(wv[e]) * (gate * __frcp_rn(1.f + __expf(-gate))));
+        out[e] = __float2bfloat16_rn(of[e] * inv * __bfloat162float(wv[e]) * silu_fast(gate));
     }
     *reinterpret_cast<uint2*>(y + static_cast<long long>(t) * ldy + hv * 128 + 4 * lane) = *reinterpret_cast<const uint2*>(out);
 }
@@ -227,7 +237,7 @@ extern "C" int s1_conv_silu(s1_ctx* ctx, const void* x, long long ldx, const voi
     if (total_tokens == 0) return S1_OK;
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     if (taps == 4 && al16(weight)) {
-        constexpr int TT = 16;
+        constexpr int TT = 8;
         const long long n = static_cast<long long>((total_tokens + TT - 1) / TT) * (channels / 8);
         s1_conv_silu_walk_kernel<TT><<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(
             static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(weight), positions, total_tokens, channels,
