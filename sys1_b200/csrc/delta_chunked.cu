@@ -90,6 +90,17 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&t);
 }
 
+#ifdef S1_MEASURE
+// Timing aid of measurement builds only: SM clock stamps of one CTA's phases (read back with s1_measure_read_stamps).
+__device__ long long s1_phase_stamps[64];
+#define S1_STAMP(k)                                                                                   \
+    do {                                                                                              \
+        if (blockIdx.x == gridDim.x / 2 && blockIdx.y == gridDim.y - 1 && threadIdx.x == 0) s1_phase_stamps[k] = clock64(); \
+    } while (0)
+#else
+#define S1_STAMP(k) do { } while (0)
+#endif
+
 struct PrepParams {
     const float* q;
     const float* k;
@@ -115,9 +126,14 @@ struct PrepParams {
     int Hk;                      // key heads (H value heads; key head = value head / (H / Hk))
 };
 
-constexpr int kAStride = 68;  // floats per row of the f32 A matrix in shared memory (16-byte rows, conflict-free)
+// The f32 matrix A of each chunk is kept transposed in shared memory, AT[j][i] = A[i][j] (64 floats per row): the thread
+// that forms row i of A writes a column of AT (lanes = consecutive addresses), and the substitution reads four or sixteen
+// consecutive i of one j with 16-byte loads that every lane of a warp shares.
+constexpr int kAStride = 64;
+constexpr int kTRows = 48;    // rows of the solved columns kept in shared memory for the later 16-row blocks (rows 48.. are never re-read)
 constexpr int kPrepSmem = 2 * kTileBytes /*Kop*/ + 2 * kTileBytes /*Qop*/ + 2 * 2 * kTileBytes /*XT*/ +
-                          2 * kTileBytes /*Top*/ + 128 * kAStride * 4 /*A*/ + 128 * 4 * 4 /*G, beta, e^G, e^(Glast-G)*/ + 1024 + 64;
+                          2 * kTileBytes /*Top*/ + 128 * kAStride * 4 /*A^T*/ + 128 * 4 * 4 /*G, beta, e^G, e^(Glast-G)*/ +
+                          kTRows * 128 * 4 /*solved rows*/ + 1024 + 64;
 
 constexpr int kPrepThreads = 256;  // two threads per stacked token row: each owns one half of the features / columns
 
@@ -138,10 +154,12 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     float* bsh = gsh + 128;
     float* egs = bsh + 128;   // e^G per stacked row
     float* egl = egs + 128;   // e^{G_last - G}
-    uint64_t* bar = reinterpret_cast<uint64_t*>(egl + 128);
+    float* tbuf = egl + 128;  // [kTRows][128]: entry j of the solved column of stacked row r at tbuf[j * 128 + r]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(tbuf + kTRows * 128);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+    S1_STAMP(0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q4 = warp & 3;             // TMEM lane quarter of this warp
     const int fh = warp >> 2;            // which half of the features / of the chunk's columns this thread handles
@@ -196,6 +214,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
         }
     }
     cp_async_commit_group();
+    S1_STAMP(2);   // loads requested
 
     // ---- gates: inclusive cumulative sum inside each chunk (two warps per chunk)
     float gi = 0.f, bi = 0.f;
@@ -225,6 +244,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     gsh[r] = G;
     bsh[r] = bi;
     __syncthreads();
+    S1_STAMP(3);   // gates
     const uint32_t tmem = *tmem_slot;
     const float Glast = gsh[half * 64 + 63];
     const float eG = __expf(G);
@@ -240,6 +260,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     }
     cp_async_wait_all();
     __syncthreads();
+    S1_STAMP(4);   // staged rows landed
     const int tile = lane >> 4, col = (4 * lane) & 63;
     // this lane's 4 features of a staged row
     auto fetch4 = [&](uint32_t stage, int row) -> float4 {
@@ -292,6 +313,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
         }
     }
     __syncthreads();
+    S1_STAMP(5);   // Q operands written
 #pragma unroll
     for (int u = 0; u < 16; ++u) {
         const int row = warp * 16 + u, ri = row & 63;
@@ -311,6 +333,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
+    S1_STAMP(6);   // K operands written
 
     // ---- K K^T -> TMEM columns 0..127, Q K^T -> 128..255 (both chunks at once; cross-chunk blocks are ignored)
     if (threadIdx.x == 0) {
@@ -329,6 +352,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     }
     __syncwarp();
     bool ok = mbar_wait(smem_u32(bar), 0, abort_flag);
+    S1_STAMP(7);   // first MMAs done
     ok = __all_sync(0xffffffffu, ok);
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
     // K and Q tiles are consumed: their 64 KB now stage the raw V rows, in flight while A and P are formed
@@ -366,7 +390,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
             for (int e = 0; e < 32; ++e) {
                 const int j = c * 32 + e;
                 const float dec = __expf(G - gsh[half * 64 + j]);  // <= 1 wherever it is used (j <= i)
-                amat[r * kAStride + j] = (j < i) ? bi * __uint_as_float(kk[e]) * dec : 0.f;
+                amat[(half * 64 + j) * kAStride + i] = (j < i) ? bi * __uint_as_float(kk[e]) * dec : 0.f;  // A^T[j][i]
                 const float pv = (j <= i) ? __uint_as_float(qk[e]) * dec : 0.f;
                 if (e & 1) pp[e >> 1] = pack2(__uint_as_float(pp[e >> 1]), pv);
                 else pp[e >> 1] = __float_as_uint(pv);
@@ -382,6 +406,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     cp_async_wait_all();
     tc_fence_before();
     __syncthreads();
+    S1_STAMP(8);   // A, P formed; V rows landed
     tc_fence_after();
 
     // ---- Tm = (I + A)^-1 by forward substitution, one column per thread (columns are independent); the other half
@@ -399,33 +424,58 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
             st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(vv.x * be, vv.y * be), pack2(vv.z * be, vv.w * be));
         }
     } else {
-        float t[64];
-        const float* arow = amat + (half * 64) * kAStride;
+        // Column i of Tm = (I + A)^-1: t[ii] = [ii == i] - sum_{j < ii} A[ii][j] t[j], in blocks of 16 rows. A block first
+        // takes the contributions of the rows solved before it (a run-time loop over j: one 4-byte load of t[j] from this
+        // thread's own column in shared memory, four shared 16-byte loads of A^T[j][16 b ..], 16 fmas), then finishes its own
+        // 16 x 16 triangle in registers. The code is a few hundred instructions that are re-used by every block; the fully
+        // unrolled 64-step form was ten times slower (2000 fmas of straight-line code that each warp executes once: it
+        // ran at the speed of instruction fetch).
+        const float* at = amat + (half * 64) * kAStride;   // at[j * 64 + ii] = A[ii][j]
+        float* tcol = tbuf + r;                              // tcol[j * 128] = t[j] of this column
+        const uint32_t ttile = top + half * kTileBytes;
+#pragma unroll 1
+        for (int b = 0; b < 4; ++b) {
+            float acc[16];
 #pragma unroll
-        for (int ii = 0; ii < 64; ++ii) {
-            float a0 = (ii == i) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            for (int e = 0; e < 16; ++e) acc[e] = (16 * b + e == i) ? 1.f : 0.f;
+#pragma unroll 4
+            for (int j = 0; j < 16 * b; ++j) {
+                const float tj = tcol[j * 128];
+                const float4* arow = reinterpret_cast<const float4*>(at + j * kAStride + 16 * b);
 #pragma unroll
-            for (int j = 0; j + 3 < ii; j += 4) {
-                const float4 a = *reinterpret_cast<const float4*>(arow + ii * kAStride + j);
-                a0 = fmaf(-a.x, t[j], a0);
-                a1 = fmaf(-a.y, t[j + 1], a1);
-                a2 = fmaf(-a.z, t[j + 2], a2);
-                a3 = fmaf(-a.w, t[j + 3], a3);
+                for (int q = 0; q < 4; ++q) {
+                    const float4 a = arow[q];
+                    acc[4 * q] = fmaf(-a.x, tj, acc[4 * q]);
+                    acc[4 * q + 1] = fmaf(-a.y, tj, acc[4 * q + 1]);
+                    acc[4 * q + 2] = fmaf(-a.z, tj, acc[4 * q + 2]);
+                    acc[4 * q + 3] = fmaf(-a.w, tj, acc[4 * q + 3]);
+                }
             }
 #pragma unroll
-            for (int j = ii & ~3; j < ii; ++j) a0 = fmaf(-arow[ii * kAStride + j], t[j], a0);
-            t[ii] = (a0 + a1) + (a2 + a3);
-        }
-        // column i of this chunk's Tm -> k-tile `half` of the block-diagonal A operand
-        const uint32_t ttile = top + half * kTileBytes;
+            for (int e2 = 0; e2 < 15; ++e2) {  // acc[e2] is final here: fold it into the rows below it
+                const float4* arow = reinterpret_cast<const float4*>(at + (16 * b + e2) * kAStride + 16 * b);
 #pragma unroll
-        for (int ii = 0; ii < 64; ++ii) {
-            st_shared_b16(ttile + sw128(half * 64 + ii, i), __float2bfloat16_rn(t[ii]));
+                for (int q = (e2 + 1) / 4; q < 4; ++q) {
+                    const float4 a = arow[q];
+                    if (4 * q > e2) acc[4 * q] = fmaf(-a.x, acc[e2], acc[4 * q]);
+                    if (4 * q + 1 > e2) acc[4 * q + 1] = fmaf(-a.y, acc[e2], acc[4 * q + 1]);
+                    if (4 * q + 2 > e2) acc[4 * q + 2] = fmaf(-a.z, acc[e2], acc[4 * q + 2]);
+                    if (4 * q + 3 > e2) acc[4 * q + 3] = fmaf(-a.w, acc[e2], acc[4 * q + 3]);
+                }
+            }
+            // column i of this chunk's Tm -> k-tile `half` of the block-diagonal A operand; and, for the blocks still to come,
+            // into this thread's own column of the f32 buffer
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                st_shared_b16(ttile + sw128(half * 64 + 16 * b + e, i), __float2bfloat16_rn(acc[e]));
+                if (b < 3) tcol[(16 * b + e) * 128] = acc[e];
+            }
         }
     }
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
+    S1_STAMP(9);   // solve + beta V staged
 
     // ---- [W | U] = Tm [beta e^G K | beta V]  (M = 128 stacked rows, N = 256, K = 128 stacked tokens)
     if (threadIdx.x == 0) {
@@ -443,6 +493,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     }
     __syncwarp();
     ok = mbar_wait(smem_u32(bar), 1, abort_flag);
+    S1_STAMP(10);  // second MMA done
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
         tc_fence_after();
@@ -476,6 +527,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     }
     tc_fence_before();
     __syncthreads();
+    S1_STAMP(11);  // write-out done
     if (warp == 0) {
         tc_fence_after();
         tmem_dealloc(tmem, 256);
@@ -893,3 +945,9 @@ extern "C" int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm
     if (rc) return rc;
     return s1_delta_finish(ctx, o, z, ldz, norm_weight, eps, total_tokens, value_heads, y, ldy);
 }
+
+#ifdef S1_MEASURE
+extern "C" int s1_measure_read_stamps(long long* out, int n) {
+    return cudaMemcpyFromSymbol(out, s1_phase_stamps, sizeof(long long) * (n < 64 ? n : 64)) == cudaSuccess ? 0 : -2;
+}
+#endif
