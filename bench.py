@@ -446,8 +446,15 @@ def tp_block(args, rank, world, dev, steps, warmup):
         tp = tensor_parallel.TensorParallel(device.load(dev.index), 0, 1)
     ctx = tp.ctx
     w = _decoder_group_weights(cfg, 1005, dev, torch.bfloat16)   # the same full tensors on every rank (same seed)
-    dec = tensor_parallel.Decoder(w, cfg, tp, slabs=args.slabs, comm_sms=args.comm_sms)
+    own = world > 1 and args.exchange in ("multimem", "both")
+    # SMs the projections leave free while sums are in flight: NCCL's kernels need room of their own; the library's exchange
+    # kernel is a few fat blocks and the projections draw their tiles at run time around it, so nothing is set aside
+    comm_sms = args.comm_sms if args.comm_sms >= 0 else (0 if own else 16)
+    dec = tensor_parallel.Decoder(w, cfg, tp, slabs=args.slabs, comm_sms=comm_sms)
     H = cfg.hidden_size
+    if own:   # the residual stream lives in symmetric memory: its sums run as the library's in-switch reduction kernel
+        tp.symmetric_arena((args.tp_tokens + 2048) * H * 2 + 4096)
+    fresh = (lambda rows: tp.symmetric_empty((rows, H))) if own else (lambda rows: torch.empty(rows, H, dtype=torch.bfloat16, device=dev))
 
     def batch_of(T, seed):
         lens = batching.synthetic_lengths(seed, 256, min(8192, T), T)
@@ -462,13 +469,14 @@ def tp_block(args, rank, world, dev, steps, warmup):
     mbp = args.micro_batches if world > 1 else 1
     single = qwen35.Decoder({**w, "embed_tokens": px}, cfg)      # the embedded tokens stand in for the table: ids = arange
     y_one, states = single.forward(torch.arange(2048, device=dev, dtype=torch.int32), pb.cu_seqlens, ppos, collect=True)
-    y_tp = dec.forward_embeds(px.clone(), pb.cu_seqlens, ppos, micro_batches=mbp)
+    xp = fresh(2048)
+    y_tp = dec.forward_embeds(xp.copy_(px), pb.cu_seqlens, ppos, micro_batches=mbp).clone()
     ctx.sync()
     rel = lambda a, b_: float((a.float() - b_.float()).abs().max() / b_.float().abs().max())
     per_layer, digest = [], y_tp.view(torch.int16).to(torch.int64).sum().reshape(1)
     x_in = px
     for i, layer in enumerate(dec.layers):
-        got = layer.forward(x_in.clone(), pb.cu_seqlens, ppos)
+        got = layer.forward(xp.copy_(x_in), pb.cu_seqlens, ppos)
         per_layer.append(rel(got, states[i]))
         digest = digest + got.view(torch.int16).to(torch.int64).sum()
         x_in = states[i]
@@ -485,11 +493,11 @@ def tp_block(args, rank, world, dev, steps, warmup):
     # ---- timing at the configured budget
     T = args.tp_tokens
     b, x0, pos = batch_of(T, 1005)
-    x = torch.empty_like(x0)
+    x = fresh(T)
     mbs = args.micro_batches if world > 1 else 1
     n_ar = 2 * cfg.num_hidden_layers
 
-    def measure(decoder, micro_batches, pdl, n_steps):
+    def measure(decoder, micro_batches, pdl, n_steps, x=x):
         ctx.set_option("pdl", pdl)
 
         def step(exchange=True):
@@ -509,37 +517,58 @@ def tp_block(args, rank, world, dev, steps, warmup):
 
     pdl = 1 if args.tp_pdl < 0 else args.tp_pdl
     ms, ms_math, launches = measure(dec, mbs, pdl, steps)
-    ms_ar = 0.0
-    if world > 1:
+    def bare_allreduces(buf):
         def bare():
             for _ in range(n_ar):
-                ctx.all_reduce_(x)
+                ctx.all_reduce_(buf)
         bare()
-        ms_ar = _timed(bare, max(2, steps // 2), world, dev)
+        return _timed(bare, max(2, steps // 2), world, dev)
+
+    busbw = lambda t_ms: 2.0 * (world - 1) / world * n_ar * T * H * 2 / (t_ms * 1e-3) / 1e9
+    ms_ar = bare_allreduces(x) if world > 1 else 0.0
     ctx.sync()
+    other = None
+    if world > 1 and args.exchange == "both":   # the same step with the sums through NCCL, for comparison
+        xn = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        sms_n = args.comm_sms if args.comm_sms >= 0 else 16
+        dec_n = tensor_parallel.Decoder(w, cfg, tp, slabs=args.slabs, comm_sms=sms_n)
+        ms_n, ms_math_n, _ = measure(dec_n, mbs, pdl, steps, x=xn)
+        ms_ar_n = bare_allreduces(xn)
+        ctx.sync()
+        del dec_n
+        other = {"exchange": "nccl", "comm_sms": sms_n, "ms": ms_n, "ms_without_exchange": ms_math_n, "ms_allreduce_alone": ms_ar_n,
+                 "allreduce_busbw_gbs": busbw(ms_ar_n), "exchange_hidden_frac": 1.0 - (ms_n - ms_math_n) / ms_ar_n}
+        del xn
     sweep = None
     if args.tp_sweep and world > 1:
         sweep = []
-        for comm_sms in (8, 16, 32):
+        for comm_sms in ((0, 8, 16) if own else (8, 16, 32)):
             d2 = tensor_parallel.Decoder(w, cfg, tp, slabs=args.slabs, comm_sms=comm_sms)
-            for m in (1, 2, 4):
-                for p_ in (0, 1):
-                    a_, b_, _ = measure(d2, m, p_, 3)
-                    sweep.append({"comm_sms": comm_sms, "micro_batches": m, "pdl": p_, "ms": a_, "ms_without_exchange": b_,
-                                  "hidden_frac": 1.0 - (a_ - b_) / ms_ar if ms_ar > 0 else None})
+            for blocks in ((4, 8, 16) if own else (args.comm_ctas,)):
+                if own:
+                    ctx.set_option("comm_ctas", blocks)
+                for m in (1, 2, 4):
+                    for p_ in ((1,) if own else (0, 1)):
+                        a_, b_, _ = measure(d2, m, p_, 3)
+                        sweep.append({"comm_sms": comm_sms, "comm_ctas": blocks, "micro_batches": m, "pdl": p_, "ms": a_,
+                                      "ms_without_exchange": b_, "hidden_frac": 1.0 - (a_ - b_) / ms_ar if ms_ar > 0 else None})
             del d2
+        if own:
+            ctx.set_option("comm_ctas", args.comm_ctas)
     flops = T * (3 * 766_443_520 + 744_488_960)   # projection flops of the group (three linear-attention + one full layer)
-    bytes_ar = n_ar * T * H * 2
     return {"metric": "tensor-parallel layer-group TFLOP/s", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
             "steps": steps, "scaling": "strong",
             "config": {"workload": f"27B-shaped (linear, linear, linear, full) layer group, packed T={T}, lengths U[256,8192], "
                                    f"tensor parallel x{world}; " +
                                    (f"{mbs} micro-batches of whole sequences alternate between computing and exchanging their partial sums"
                                     if mbs > 1 else f"row-parallel outputs exchanged in {args.slabs} row slabs") +
-                                   f", {args.comm_sms} SMs left to the exchange ({args.comm_ctas or 'default'} blocks)",
+                                   f", {comm_sms} SMs left to the exchange ({args.comm_ctas or 'default'} blocks); sums over ranks by " +
+                                   ("the library's own kernel (multimem.ld_reduce / multimem.st through the NVSwitch on symmetric memory)"
+                                    if own else "ncclAllReduce" if world > 1 else "nothing (one rank)"),
                        "sequences": int(b.num_sequences), "parallelism": f"tp{world}"},
             "ms_without_exchange": ms_math, "ms_allreduce_alone": ms_ar, "allreduces_per_step": n_ar if world > 1 else 0,
-            "allreduce_busbw_gbs": (2.0 * (world - 1) / world * bytes_ar / (ms_ar * 1e-3) / 1e9) if world > 1 and ms_ar > 0 else None,
+            "allreduce_busbw_gbs": busbw(ms_ar) if world > 1 and ms_ar > 0 else None,
+            "exchange": "multimem" if own else ("nccl" if world > 1 else None), **({"compared_with": other} if other else {}),
             "exchange_hidden_frac": (1.0 - (ms - ms_math) / ms_ar) if world > 1 and ms_ar > 0 else None,
             "parity": {"tokens": 2048, "per_layer_max_rel_vs_unsharded": per_layer, "bound": 2e-2, "ranks_bit_identical": bool(same),
                        "ok": bool(same and max(per_layer) <= 2e-2),
@@ -866,9 +895,13 @@ def main():
     ap.add_argument("--sustain-seconds", type=float, default=2.2)
     ap.add_argument("--slabs", type=int, default=4, help="tp: row slabs the exchange is pipelined in")
     ap.add_argument("--comm-ctas", type=int, default=0, help="tp: blocks the all-reduce may use (0 = NCCL's default)")
-    ap.add_argument("--comm-sms", type=int, default=16, help="tp: SMs the projections leave to the exchange of the previous slab")
+    ap.add_argument("--comm-sms", type=int, default=-1,
+                    help="tp: SMs the projections leave to the exchange while it runs beside them (-1: 0 for the library's own exchange kernel, 16 for NCCL)")
     ap.add_argument("--tp-pdl", type=int, default=-1, help="tp: 0 / 1 turns programmatic dependent launch of the projections off / on (-1: default)")
     ap.add_argument("--micro-batches", type=int, default=2, help="tp: groups of whole sequences that alternate between computing and exchanging (1: row slabs inside each projection instead)")
+    ap.add_argument("--exchange", default="both", choices=["multimem", "nccl", "both"],
+                    help="tp: sums over ranks by the library's own in-switch reduction kernel on symmetric memory (multimem), by "
+                         "ncclAllReduce (nccl), or the first with the second timed beside it (both, default)")
     ap.add_argument("--tp-sweep", action="store_true", help="tp: also time the group for a grid of comm-sms x micro-batches x pdl settings")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step from a CUDA graph (for small token budgets, where launching from Python is the bottleneck)")

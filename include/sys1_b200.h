@@ -69,7 +69,12 @@ long long s1_launch_count(const s1_ctx* ctx);
  * programmatic stream serialization, so that a projection's set-up overlaps the tail of the kernel before it, 0 turns
  * that off; "wait_limit_cycles" = SM clock cycles a single wait inside a projection kernel may last before the kernel
  * gives up and s1_sync reports S1_EKERNEL (default 2e9, about a second); "comm_timeout_ms" = how long s1_comm_init
- * waits for the other ranks before it gives up with S1_ETIMEOUT (default 120000; 0 = for ever). */
+ * waits for the other ranks before it gives up with S1_ETIMEOUT (default 120000; 0 = for ever); "dynamic_tiles" = 1
+ * makes the projections' CTAs draw their tiles from a counter at run time instead of working through fixed shares: a CTA
+ * that reaches its SM late, because blocks of a collective running beside the projection were in its way, then finds
+ * little left to do, where a fixed share would hold the whole launch back (a few microseconds dearer per launch, so
+ * off by default; the tensor-parallel layers turn it on around their overlapped sums); "exchange_wait_ms" = how long the
+ * symmetric-memory exchange kernel waits for its peers (default 10000). */
 int s1_set_option(s1_ctx* ctx, const char* name, long long value);
 
 /*
@@ -213,6 +218,10 @@ int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const voi
  *                         s1_attention, s1_attention_gqa, s1_delta_rule_chunked and s1_gated_delta_rule may be called
  *                         with `cu_seqlens_host` = NULL for the same (num_seqs, total_tokens): they then read their
  *                         tables from the plan and copy nothing (the attentions need no workspace then).
+ *   s1_batch_plan_release : the context forgets the plan built in this buffer (if it is the one in use, none is in use
+ *                         afterwards); call it before the buffer is freed or reused for something else. Building a new
+ *                         plan in the same buffer replaces the old one without a release. A context keeps up to 4096
+ *                         plans alive; s1_batch_plan fails with S1_EINVAL beyond that.
  * The caller keeps the buffer alive and unchanged while the plan is in use. A call that does pass `cu_seqlens_host`
  * ignores the plan and behaves as before (and refuses to run under stream capture, where its copy from host memory
  * would be recorded with a pointer that does not outlive the call).
@@ -220,6 +229,7 @@ int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const voi
 size_t s1_batch_plan_bytes(int num_seqs, int total_tokens);
 int s1_batch_plan(s1_ctx* ctx, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens, void* plan, size_t plan_bytes);
 int s1_use_batch_plan(s1_ctx* ctx, const void* plan);
+int s1_batch_plan_release(s1_ctx* ctx, const void* plan);
 
 /*
  * Bidirectional softmax attention over a packed batch in flash form (scores stay on chip), head_dim = 64:
@@ -346,6 +356,25 @@ int s1_allreduce_bf16(s1_ctx* ctx, void* buf, size_t count);
 int s1_allreduce_wait(s1_ctx* ctx);
 long long s1_allreduce_ticket(const s1_ctx* ctx);
 int s1_allreduce_wait_ticket(s1_ctx* ctx, long long ticket);
+
+/*
+ * Symmetric-memory exchange: `s1_exchange_register` tells the context that [local_base, local_base + bytes) is symmetric
+ * memory - the same buffer allocated on every rank, with `multicast_base` the address of its NVLink multicast mapping
+ * (for instance from torch.distributed._symmetric_memory, or cuMulticast* directly) - and hands it one small flag array
+ * per rank (`flag_arrays_host`: HOST array of `size` DEVICE pointers, entry r = rank r's array as mapped on this GPU, each
+ * of at least S1_EXCHANGE_FLAG_BYTES, zeroed by its owner before the first sum). From then on s1_allreduce_bf16 on a
+ * buffer inside that range runs this library's own kernel instead of the NCCL call: every rank reduces its slice inside the
+ * NVSwitch (`multimem.ld_reduce`, f32 accumulation, one rounding) and writes the sums into every rank's copy
+ * (`multimem.st`); per GPU (1 + 1 / ranks) buffers of NVLink traffic in each direction, whatever the number of ranks;
+ * a few blocks of 1024 threads ("comm_ctas": how many, default 8, at most 64), so that the projections running beside the
+ * sum lose few SMs to it; bit-identical results on all ranks. Tickets
+ * and waits work as for the NCCL path; a context that only sums symmetric buffers needs no s1_comm_init. The ranks meet
+ * through the flag arrays with bounded polls: a rank that never shows up makes the others give up after
+ * "exchange_wait_ms" (s1_set_option, default 10000) and s1_sync report S1_EKERNEL; the context stays usable.
+ */
+#define S1_EXCHANGE_FLAG_BYTES 4096
+int s1_exchange_register(s1_ctx* ctx, int rank, int size, void* local_base, void* multicast_base, size_t bytes,
+                         void* const* flag_arrays_host, size_t flag_bytes);
 
 /*
  * s1_linear followed by s1_rope on the first `rotated_heads` heads (64 columns each) of the output, the rotation done

@@ -16,6 +16,7 @@ S1_OK = 0
 S1_EINVAL, S1_ECUDA, S1_EDEVICE, S1_EKERNEL, S1_ENOMEM, S1_ELIMIT, S1_ETIMEOUT = -1, -2, -3, -4, -5, -6, -7
 STATIC_MAX_TOKENS, STATIC_MAX_FEATURES = 262144, 32768
 COMM_ID_BYTES = 128
+EXCHANGE_FLAG_BYTES = 4096  # S1_EXCHANGE_FLAG_BYTES
 EPI_NONE, EPI_GEGLU, EPI_SWIGLU = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
 
@@ -68,6 +69,7 @@ SIGNATURES = {
     "s1_batch_plan_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "s1_batch_plan": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_void_p, C.c_size_t]),
     "s1_use_batch_plan": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "s1_batch_plan_release": (C.c_int, [C.c_void_p, C.c_void_p]),
     "s1_attention_workspace": (C.c_size_t, [C.c_int, C.c_int]),
     "s1_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
                                C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p,
@@ -82,6 +84,7 @@ SIGNATURES = {
     "s1_comm_destroy": (C.c_int, [C.c_void_p]),
     "s1_allreduce_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
     "s1_allreduce_wait": (C.c_int, [C.c_void_p]),
+    "s1_exchange_register": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_size_t]),
     "s1_allreduce_ticket": (C.c_longlong, [C.c_void_p]),
     "s1_allreduce_wait_ticket": (C.c_int, [C.c_void_p, C.c_longlong]),
     "s1_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,

@@ -22,7 +22,7 @@ LIB = PKG / "libsys1_b200.so"
 STAMP = PKG / "csrc" / ".build_stamp"
 OBJ = PKG / "csrc" / ".obj"
 
-SOURCES = ["api.cu", "linear_static.cu", "batching.cu", "plan.cu", "delta_rule.cu", "delta_chunked.cu", "delta_io.cu", "attention.cu", "attention_gqa.cu", "norm_rope.cu", "comm.cu"]
+SOURCES = ["api.cu", "linear_static.cu", "batching.cu", "plan.cu", "delta_rule.cu", "delta_chunked.cu", "delta_io.cu", "attention.cu", "attention_gqa.cu", "norm_rope.cu", "comm.cu", "exchange.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

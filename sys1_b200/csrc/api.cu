@@ -37,8 +37,9 @@ extern "C" int s1_ctx_create(int device_ordinal, void* cuda_stream, s1_ctx** out
     ctx->device = device_ordinal;
     ctx->sm_count = prop.multiProcessorCount;
     ctx->stream = static_cast<cudaStream_t>(cuda_stream);  // NULL is CUDA's default stream
-    if (cudaMalloc(&ctx->status_dev, 4 * sizeof(int)) != cudaSuccess ||
-        cudaMemset(ctx->status_dev, 0, 4 * sizeof(int)) != cudaSuccess) {
+    // int[8]: words 0..3 the status record kernels fill when they give up, words 4..5 the projections' tile counters
+    if (cudaMalloc(&ctx->status_dev, 8 * sizeof(int)) != cudaSuccess ||
+        cudaMemset(ctx->status_dev, 0, 8 * sizeof(int)) != cudaSuccess) {
         delete ctx;
         return S1_ECUDA;
     }
@@ -102,6 +103,15 @@ extern "C" int s1_set_option(s1_ctx* ctx, const char* name, long long value) {
         ctx->opt_comm_timeout_ms = value;
         return S1_OK;
     }
+    if (strcmp(name, "dynamic_tiles") == 0) {  // projections draw their tiles at run time instead of working through fixed shares
+        ctx->opt_dynamic_tiles = value != 0;
+        return S1_OK;
+    }
+    if (strcmp(name, "exchange_wait_ms") == 0) {  // longest the symmetric-memory exchange kernel waits for its peers
+        if (value < 1 || value > 600000) return s1_fail(ctx, S1_EINVAL, "exchange_wait_ms must be between 1 and 600000 (got %lld)", value);
+        ctx->opt_exchange_wait_ms = value;
+        return S1_OK;
+    }
 #ifdef S1_MEASURE
     if (strcmp(name, "debug") == 0) {
         ctx->opt_debug = static_cast<int>(value);
@@ -118,7 +128,7 @@ extern "C" int s1_sync(s1_ctx* ctx) {
     int st[4] = {0, 0, 0, 0};
     S1_CUDA_OK(ctx, cudaMemcpy(st, ctx->status_dev, sizeof(st), cudaMemcpyDeviceToHost));
     if (st[0] != 0) {
-        cudaMemset(ctx->status_dev, 0, sizeof(st));
+        cudaMemset(ctx->status_dev, 0, 8 * sizeof(int));  // the tile counters too: a kernel that gave up may have left them anywhere
         if (st[0] == 101 || st[0] == 102)
             return s1_fail(ctx, S1_EKERNEL, "%s: row %d has index %d outside the table", st[0] == 101 ? "s1_norm gather" : "s1_rope position",
                            st[2], st[3]);
@@ -317,6 +327,8 @@ static int linear_impl(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, lo
     p.residual = static_cast<const __nv_bfloat16*>(residual);
     p.bias = static_cast<const __nv_bfloat16*>(lin->bias);
     p.status = ctx->status_dev;
+    p.tile_counter = reinterpret_cast<unsigned int*>(ctx->status_dev + 4);
+    p.dynamic_tiles = ctx->opt_dynamic_tiles ? 1 : 0;
     p.rope_cos = p.rope_sin = nullptr;
     p.rope_pos = nullptr;
     p.rope_max = p.rope_cols = 0;

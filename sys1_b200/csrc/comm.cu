@@ -100,10 +100,13 @@ extern "C" int s1_comm_init(s1_ctx* ctx, const void* id, int rank, int size) {
     ctx->comm_blocking = blocking;
     int prio_low = 0, prio_high = 0;  // the collective's blocks go first when SMs free up
     cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high);
-    cudaError_t e = cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, prio_high);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_ready, cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming);
-    for (int i = 0; i < s1_ctx::kCommTickets && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&ctx->comm_ticket[i], cudaEventDisableTiming);
+    cudaError_t e = cudaSuccess;
+    if (!ctx->comm_stream) {  // (a context that has already summed symmetric buffers has its stream and events)
+        e = cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, prio_high);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_ready, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming);
+        for (int i = 0; i < s1_ctx::kCommTickets && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&ctx->comm_ticket[i], cudaEventDisableTiming);
+    }
     if (e != cudaSuccess) {
         api->CommDestroy(comm);
         return s1_fail(ctx, S1_ECUDA, "s1_comm_init: %s", cudaGetErrorString(e));
@@ -117,10 +120,10 @@ extern "C" int s1_comm_init(s1_ctx* ctx, const void* id, int rank, int size) {
 
 extern "C" int s1_comm_destroy(s1_ctx* ctx) {
     if (!ctx) return S1_EINVAL;
-    if (!ctx->comm) return S1_OK;
+    if (!ctx->comm && !ctx->comm_stream) return S1_OK;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->comm_stream);
-    nccl_api()->CommDestroy(static_cast<ncclComm_t>(ctx->comm));
+    if (ctx->comm) nccl_api()->CommDestroy(static_cast<ncclComm_t>(ctx->comm));
     cudaEventDestroy(ctx->comm_ready);
     cudaEventDestroy(ctx->comm_done);
     for (int i = 0; i < s1_ctx::kCommTickets; ++i)
@@ -134,21 +137,37 @@ extern "C" int s1_comm_destroy(s1_ctx* ctx) {
 
 extern "C" int s1_allreduce_bf16(s1_ctx* ctx, void* buf, size_t count) {
     if (!ctx) return S1_EINVAL;
-    if (!ctx->comm) return s1_fail(ctx, S1_EINVAL, "s1_allreduce_bf16: the context has no communicator (s1_comm_init)");
+    auto* b8 = static_cast<unsigned char*>(buf);
+    const bool own = ctx->xchg_size > 1 && b8 >= ctx->xchg_local && b8 + 2 * count <= ctx->xchg_local + ctx->xchg_bytes;
+    if (!ctx->comm && !own) return s1_fail(ctx, S1_EINVAL, "s1_allreduce_bf16: the context has no communicator (s1_comm_init)");
     if (!buf && count) return s1_fail(ctx, S1_EINVAL, "s1_allreduce_bf16: null pointer");
     if (count == 0) return S1_OK;
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    if (!ctx->comm_stream) {  // a context that only ever sums symmetric buffers has no NCCL communicator
+        int prio_low = 0, prio_high = 0;
+        cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high);
+        S1_CUDA_OK(ctx, cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, prio_high));
+        S1_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->comm_ready, cudaEventDisableTiming));
+        S1_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->comm_done, cudaEventDisableTiming));
+        for (int i = 0; i < s1_ctx::kCommTickets; ++i) S1_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->comm_ticket[i], cudaEventDisableTiming));
+    }
     S1_CUDA_OK(ctx, cudaEventRecord(ctx->comm_ready, ctx->stream));
     S1_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->comm_ready, 0));
-    NcclApi* api = nccl_api();
-    const ncclResult_t rc = api->AllReduce(buf, buf, count, ncclBfloat16, ncclSum, static_cast<ncclComm_t>(ctx->comm), ctx->comm_stream);
-    if (rc == ncclInProgress && !ctx->comm_blocking) {
-        // a communicator created with a deadline is non-blocking: the call is on the stream once its state says so
-        char why[160] = {0};
-        const int st = s1::comm_wait_enqueued(*api, static_cast<ncclComm_t>(ctx->comm), ctx->opt_comm_timeout_ms, why, sizeof(why));
-        if (st != S1_OK) return s1_fail(ctx, st, "ncclAllReduce: %s", why);
-    } else if (rc != ncclSuccess) {
-        return s1_fail(ctx, S1_ECUDA, "ncclAllReduce failed: %s", api->GetErrorString(rc));
+    if (own) {
+        // a buffer in registered symmetric memory: this library's own kernel, reduction inside the switch
+        const int rc = s1_exchange_launch(ctx, buf, count, ctx->comm_stream);
+        if (rc != S1_OK) return rc;
+    } else {
+        NcclApi* api = nccl_api();
+        const ncclResult_t rc = api->AllReduce(buf, buf, count, ncclBfloat16, ncclSum, static_cast<ncclComm_t>(ctx->comm), ctx->comm_stream);
+        if (rc == ncclInProgress && !ctx->comm_blocking) {
+            // a communicator created with a deadline is non-blocking: the call is on the stream once its state says so
+            char why[160] = {0};
+            const int st = s1::comm_wait_enqueued(*api, static_cast<ncclComm_t>(ctx->comm), ctx->opt_comm_timeout_ms, why, sizeof(why));
+            if (st != S1_OK) return s1_fail(ctx, st, "ncclAllReduce: %s", why);
+        } else if (rc != ncclSuccess) {
+            return s1_fail(ctx, S1_ECUDA, "ncclAllReduce failed: %s", api->GetErrorString(rc));
+        }
     }
     S1_CUDA_OK(ctx, cudaEventRecord(ctx->comm_done, ctx->comm_stream));
     ctx->comm_issued += 1;
@@ -161,7 +180,7 @@ extern "C" long long s1_allreduce_ticket(const s1_ctx* ctx) { return ctx ? ctx->
 
 extern "C" int s1_allreduce_wait_ticket(s1_ctx* ctx, long long ticket) {
     if (!ctx) return S1_EINVAL;
-    if (!ctx->comm) return s1_fail(ctx, S1_EINVAL, "s1_allreduce_wait_ticket: the context has no communicator (s1_comm_init)");
+    if (!ctx->comm_stream) return s1_fail(ctx, S1_EINVAL, "s1_allreduce_wait_ticket: no all-reduce was ever issued on this context");
     if (ticket < 1 || ticket > ctx->comm_issued)
         return s1_fail(ctx, S1_EINVAL, "s1_allreduce_wait_ticket: ticket %lld was never issued (last: %lld)", ticket, ctx->comm_issued);
     S1_CUDA_OK(ctx, cudaSetDevice(ctx->device));

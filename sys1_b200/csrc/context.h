@@ -3,6 +3,8 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+
+#include <atomic>
 #include <cudaTypedefs.h>
 #include <stdarg.h>
 #include <stdio.h>
@@ -69,8 +71,10 @@ struct s1_ctx {
     int opt_debug = 0;                          // only read by builds with -DS1_MEASURE (timing ablations)
     long long opt_wait_limit = 2000000000LL;    // SM clock cycles a wait inside a projection kernel may take (~1 s)
     long long opt_comm_timeout_ms = 120000;     // deadline of s1_comm_init; 0 = none
+    long long opt_exchange_wait_ms = 10000;     // longest the symmetric-memory exchange kernel waits for its peers
     int opt_gemm_sms = 0;  // 0 = all SMs
     int opt_comm_ctas = 0;  // blocks the collective may use (0 = the library's default); read by s1_comm_init
+    bool opt_dynamic_tiles = false;  // projections draw tiles from a counter at run time ("dynamic_tiles")
     bool opt_pdl = true;   // launch the projections with programmatic stream serialization
     PFN_cuTensorMapEncodeTiled encode = nullptr;
     std::unordered_map<S1TmapKey, CUtensorMap, S1TmapKeyHash> tmaps;
@@ -89,6 +93,14 @@ struct s1_ctx {
     static constexpr int kCommTickets = 64;
     cudaEvent_t comm_ticket[kCommTickets] = {};  // completion of the all-reduce with sequence number n sits in slot n % 64
     long long comm_issued = 0;                // all-reduces issued so far (the last one's ticket)
+    // symmetric-memory exchange (s1_exchange_register): sums of buffers inside [xchg_local, xchg_local + xchg_bytes) run as
+    // this library's own multimem kernel instead of the NCCL call
+    unsigned char* xchg_local = nullptr;
+    unsigned char* xchg_mc = nullptr;
+    size_t xchg_bytes = 0;
+    void* xchg_flags[16] = {};
+    int xchg_rank = 0, xchg_size = 0;
+    unsigned int xchg_epoch = 1;
     int comm_rank = 0, comm_size = 0;
     bool comm_pending = false;
     bool comm_blocking = true;                // false: created with a deadline (non-blocking NCCL communicator)
@@ -105,6 +117,26 @@ inline int s1_fail(s1_ctx* ctx, int code, const char* fmt, ...) {
     return code;
 }
 
+// An SM changes its split between L1 and shared memory only while it is empty, and the projections need nearly all of it
+// as shared memory. A kernel whose blocks sit beside the projections' CTAs (the exchange kernel) asks for the same split,
+// so that an SM it reached first does not have to drain before a projection CTA can join. (The streaming kernels keep the
+// default split: with the small L1 that goes with it they ran 10 to 50 % slower.) The hint is given once per kernel and device.
+template <typename Kernel>
+inline void s1_keep_projection_split(Kernel kernel) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, static_cast<int>(cudaSharedmemCarveoutMaxShared));
+}
+#define S1_KEEP_PROJECTION_SPLIT(kernel)                                          \
+    do {                                                                          \
+        static std::atomic<unsigned long long> told{0}; /* one bit per device */    \
+        int dev_ = 0;                                                             \
+        cudaGetDevice(&dev_);                                                     \
+        const unsigned long long bit_ = 1ull << (dev_ & 63);                      \
+        if (!(told.load(std::memory_order_relaxed) & bit_)) {                     \
+            s1_keep_projection_split(kernel);                                     \
+            told.fetch_or(bit_, std::memory_order_relaxed);                       \
+        }                                                                         \
+    } while (0)
+
 #define S1_CUDA_OK(ctx, call)                                                                        \
     do {                                                                                             \
         cudaError_t e__ = (call);                                                                    \
@@ -114,5 +146,9 @@ inline int s1_fail(s1_ctx* ctx, int code, const char* fmt, ...) {
 
 // Encodes (or fetches from the cache) a 2-D tiled tensor map over a row-major matrix whose rows are `ld`
 // elements apart: dim0 = cols (contiguous), dim1 = rows. swizzle_bytes is 0, 64 or 128.
+// Blocks the exchange kernel may use at most (the flag arrays hold one slot per block and rank).
+#define S1_EXCHANGE_MAX_BLOCKS 64
+int s1_exchange_launch(s1_ctx* ctx, void* buf, size_t count, cudaStream_t stream);
+
 int s1_get_tmap(s1_ctx* ctx, const void* ptr, long long rows, long long cols, long long ld, int box_rows,
                 int box_cols, int elem_bytes, int swizzle_bytes, CUtensorMap* out);

@@ -51,6 +51,8 @@ struct GemmParams {
     const __nv_bfloat16* residual;  // [M, n_out] or null
     const __nv_bfloat16* bias;      // [n_out] or null
     int* status;                    // device int[4]: {code, block, role, tile}; 0 = ok
+    unsigned int* tile_counter;     // device uint[2], zero between launches: {next tile to hand out, units that are done}
+    int dynamic_tiles;              // 0: every unit works through a fixed share of the tiles; 1: tiles are drawn at run time
     // MODE 8 (rotary embedding in the epilogue): output columns [0, rope_cols) are heads of 64 columns whose halves are
     // rotated by the f32 table row of the token's position; columns past rope_cols are written as they are
     const float* rope_cos;          // [rope_max, 32]
@@ -62,6 +64,10 @@ struct GemmParams {
 constexpr int kBM = 128;  // rows per CTA
 constexpr int kBK = 64;   // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kEpiWarp0 = 2;
+// Tile feed: how many tile numbers may be published and not yet read by the slowest role. The operand ring lets the
+// producer run at most 6 tiles ahead of the MMA issuer (6 stages, one k-block per tile at worst), the two accumulators let
+// the issuer run 2 ahead of the epilogue, and numbers are published 2 iterations ahead: 10 in all.
+constexpr int kFeedSlots = 16;
 
 // Epilogue warps: 8 for the plain epilogues; 16 for the gated ones, whose erf / exp evaluation is latency-bound and
 // needs the extra warps to keep the issue slots busy.
@@ -93,7 +99,7 @@ struct GemmCfg {
     // 224 KB of operand ring + epilogue staging: 6 (or 4) stages beside 32 KB of staging, 5 beside 64 KB
     static constexpr int stages(int staging_bytes) { return (224 * 1024 - staging_bytes) / kStageBytes; }
     static constexpr int smem_bytes(int staging_bytes) {
-        return stages(staging_bytes) * kStageBytes + staging_bytes + 1024 /*align slack*/ + 256 /*barriers*/;
+        return stages(staging_bytes) * kStageBytes + staging_bytes + 1024 /*align slack*/ + 512 /*barriers, tile feed*/;
     }
 };
 
@@ -417,6 +423,10 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // tile feed: kFeedSlots barriers at +192 and kFeedSlots tile numbers behind them (see "tile feed" below)
+    const uint32_t feed_bar0 = smem_u32(bars) + 192u;
+    const uint32_t feed_tile0 = feed_bar0 + 8u * kFeedSlots;
+    static_assert((2 * STAGES + 4) * 8 + 8 <= 192 && 192 + 12 * kFeedSlots <= 512, "barrier block layout");
 
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = full0 + 8u * STAGES;
@@ -443,6 +453,8 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             mbar_init(tfull0 + 8u * a, 1);
             mbar_init(tempty0 + 8u * a, EW * CTAS);
         }
+        if (p.dynamic_tiles)
+            for (int f = 0; f < kFeedSlots; ++f) mbar_init(feed_bar0 + 8u * f, 1);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmA);
@@ -471,11 +483,106 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     int fail_role = 0, fail_tile = -1;
 
+    // ---- tile feed. Lane 0 of the leader's producer warp decides which tile each iteration works on and publishes it to
+    // every role of the CTA (pair) through a small ring in shared memory: slot `(it - 1) % kFeedSlots` holds the tile of
+    // iteration `it` >= 1 (-1: no more), its barrier's phase says it is there; iteration 0 is always tile `unit`.
+    // By default the sequence is the unit's fixed share (`unit + it * num_units`), which every role works out by itself:
+    // nothing is published. With `dynamic_tiles` the tiles past the first are drawn from a counter in global memory (a draw n
+    // stands for tile `num_units + n`): a CTA that reaches its SM late - blocks of a collective running beside the
+    // projection were in the way - then finds little left to do, where a fixed share would make the whole launch wait
+    // for it. Draws are issued a tile ahead of their use; the burst of draws at the start of a launch and the hand-over to
+    // the peer CTA still cost 1 to 5 microseconds per launch, which is why it is an option.
+    const int first_tile = (unit < num_tiles) ? unit : -1;
+    bool drained = false;  // (drawer only) the counter has run past the last tile
+    unsigned fixed_draws = 0;
+    auto feed_draw_raw = [&]() -> unsigned {
+        // fixed shares (tile `unit + k * num_units` for the k-th draw): the same feed, no traffic on the counter
+        if (!p.dynamic_tiles) return (fixed_draws++) * static_cast<unsigned>(num_units) + static_cast<unsigned>(unit);
+        return atomicAdd(p.tile_counter, 1u);
+    };
+    // The drawer that learns there is nothing left says so once; the last of all units to say so puts both counters back
+    // to zero for the next launch on this stream (which draws only after this grid has completed: stream order, or
+    // griddepcontrol.wait). No unit draws again after it has said so.
+    auto feed_drained = [&]() {
+        if (drained) return;
+        drained = true;
+        if (!p.dynamic_tiles) return;
+        if (atomicAdd(p.tile_counter + 1, 1u) == static_cast<unsigned>(num_units) - 1u) {
+            p.tile_counter[0] = 0u;
+            p.tile_counter[1] = 0u;
+        }
+    };
+    auto feed_resolve = [&](unsigned raw) -> int {
+        const unsigned t = raw + static_cast<unsigned>(num_units);
+        if (t < static_cast<unsigned>(num_tiles)) return static_cast<int>(t);
+        feed_drained();
+        return -1;
+    };
+    auto feed_publish = [&](uint32_t it, int tile) {
+        if (!p.dynamic_tiles) return;  // every role works the fixed sequence out by itself
+        const uint32_t slot = (it - 1u) % kFeedSlots;
+        st_shared_u32(feed_tile0 + 4u * slot, static_cast<uint32_t>(tile));
+        mbar_arrive(feed_bar0 + 8u * slot);
+        if constexpr (CTAS == 2) {
+            st_cluster_u32(map_to_cta(feed_tile0 + 4u * slot, 1), static_cast<uint32_t>(tile));
+            mbar_arrive_cluster(map_to_cta(feed_bar0 + 8u * slot, 1));
+        }
+    };
+    // false: the wait ran out (or the CTA is unwinding); otherwise `tile` is the tile of iteration `it`, -1 at the end
+    auto feed_take = [&](uint32_t it, int& tile) -> bool {
+        if (it == 0) {
+            tile = first_tile;
+            return true;
+        }
+        if (!p.dynamic_tiles) {
+            const long long t = static_cast<long long>(it) * num_units + unit;
+            tile = (first_tile >= 0 && t < num_tiles) ? static_cast<int>(t) : -1;
+            return true;
+        }
+        const uint32_t slot = (it - 1u) % kFeedSlots;
+        // the leader's roles read what a thread of their own CTA wrote; the peer's need the cluster-wide acquire
+        const bool there = (CTAS == 2 && cta_rank != 0)
+                               ? mbar_wait_cluster(feed_bar0 + 8u * slot, ((it - 1u) / kFeedSlots) & 1u, abort_flag, p.wait_limit)
+                               : mbar_wait(feed_bar0 + 8u * slot, ((it - 1u) / kFeedSlots) & 1u, abort_flag, p.wait_limit);
+        if (!there) return false;
+        tile = static_cast<int>(ld_shared_u32(feed_tile0 + 4u * slot));
+        return true;
+    };
+
+    // One look, no waiting: a role asks for the next iteration's tile before it starts on the current one (it is normally
+    // there already, published two iterations ahead) and falls back to feed_take afterwards, so that the look-up costs
+    // nothing between two tiles. (Waiting here would deadlock the first tile: its successor is published only once the
+    // producer has issued all of its loads, which needs the MMA issuer to consume them.)
+    auto feed_try = [&](uint32_t it, int& tile) -> bool {
+        if (!p.dynamic_tiles) return feed_take(it, tile);
+        const uint32_t slot = (it - 1u) % kFeedSlots;
+        const bool there = (CTAS == 2 && cta_rank != 0) ? mbar_try_wait_cluster(feed_bar0 + 8u * slot, ((it - 1u) / kFeedSlots) & 1u)
+                                                        : mbar_try_wait(feed_bar0 + 8u * slot, ((it - 1u) / kFeedSlots) & 1u);
+        if (!there) return false;
+        tile = static_cast<int>(ld_shared_u32(feed_tile0 + 4u * slot));
+        return true;
+    };
+
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer (both CTAs of a pair)
         if (lane == 0) {
-            uint32_t cnt = 0;
-            for (int tile = unit; tile < num_tiles && !fail_role; tile += num_units) {
+            uint32_t cnt = 0, it = 0;
+            const bool draws = (cta_rank == 0);   // the peer's producer reads what the leader's publishes
+            int tile = first_tile;
+            int next = -2;                        // -2: the first two draws are still in flight
+            unsigned raw1 = 0, raw2 = 0;
+            if (draws) {
+                if (tile >= 0 && num_tiles > num_units) raw1 = feed_draw_raw(), raw2 = feed_draw_raw();
+                else if (tile >= 0) next = -3;    // one tile per unit at most: nothing to draw
+                else feed_drained();
+            }
+            while (tile >= 0 && !fail_role) {
+                // the draw for the iteration after next is in flight while this tile's loads are issued
+                unsigned raw_new = 0;
+                const bool drew = draws && next >= 0;
+                if (drew) raw_new = feed_draw_raw();
+                int ahead = -1;
+                const bool looked = !draws && feed_try(it + 1, ahead);
                 const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
                 const int m0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM;
                 const int r0 = tn * p.n_tile_stride;
@@ -503,6 +610,32 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         else tma_load_2d_pair(sa + Cfg::kABytes, &tmB1, kb * kBK, r1, fb);
                     }
                 }
+                if (fail_role) break;
+                ++it;
+                if (draws) {
+                    if (next == -3) {            // single-tile launch
+                        feed_drained();
+                        feed_publish(1, -1);
+                        tile = -1;
+                    } else if (next == -2) {     // end of the first tile: both early draws are back by now
+                        const int n1 = feed_resolve(raw1);
+                        feed_publish(1, n1);
+                        const int n2 = (n1 >= 0) ? feed_resolve(raw2) : -1;
+                        if (n1 >= 0) feed_publish(2, n2);
+                        tile = n1;
+                        next = n2;
+                    } else {
+                        const int n2 = drew ? feed_resolve(raw_new) : -1;
+                        if (next >= 0) feed_publish(it + 1, n2);
+                        tile = next;
+                        next = n2;
+                    }
+                } else if (looked) {
+                    tile = ahead;
+                } else if (!feed_take(it, tile)) {
+                    fail_role = 5;
+                    fail_tile = static_cast<int>(it);
+                }
             }
         }
         __syncwarp();
@@ -510,8 +643,11 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // ------------------------------------------------------------- MMA issuer (leader CTA only)
         if (lane == 0 && cta_rank == 0) {
             constexpr uint32_t idesc = make_idesc(1, kBM * CTAS, BN);
-            uint32_t cnt = 0, it = 0;
-            for (int tile = unit; tile < num_tiles && !fail_role; tile += num_units, ++it) {
+            uint32_t cnt = 0;
+            int tile = first_tile;
+            for (uint32_t it = 0; tile >= 0 && !fail_role; ++it) {
+                int ahead = -1;
+                const bool looked = feed_try(it + 1, ahead);
                 const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
                 if (!mbar_wait(tempty0 + 8u * acc, aph ^ 1u, abort_flag, p.wait_limit)) {
                     fail_role = 2;
@@ -545,6 +681,12 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 // accumulator complete (each CTA of a pair is told on its own barrier)
                 if constexpr (CTAS == 2) umma_commit_2cta(tfull0 + 8u * acc);
                 else umma_commit(tfull0 + 8u * acc);
+                if (looked) {
+                    tile = ahead;
+                } else if (!feed_take(it + 1, tile)) {
+                    fail_role = 6;
+                    fail_tile = static_cast<int>(it + 1);
+                }
             }
         }
         __syncwarp();
@@ -556,8 +698,14 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int hh = (warp - kEpiWarp0) >> 2;
         constexpr int NBUF = Store::kStagingBytes / (EW * Store::kTileBytes);  // staging tiles per warp
         const uint32_t stage_buf = smem_base + STAGES * Cfg::kStageBytes + (warp - kEpiWarp0) * (Store::kStagingBytes / EW);
-        uint32_t it = 0, nstore = 0;
-        for (int tile = unit; tile < num_tiles; tile += num_units, ++it) {
+        uint32_t nstore = 0;
+        int tile = first_tile;
+        for (uint32_t it = 0; tile >= 0; ++it) {
+            // one lane looks whether the next iteration's tile is already known; the warp shares the answer
+            int ahead = -1, looked = 0;
+            if (lane == 0) looked = feed_try(it + 1, ahead) ? 1 : 0;
+            looked = __shfl_sync(0xffffffffu, looked, 0);
+            ahead = __shfl_sync(0xffffffffu, ahead, 0);
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
             const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + q * 32;
@@ -573,16 +721,28 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             tc_fence_after();
             const uint32_t tempty_bar = lead_tempty0 + 8u * acc;
+            bool skip = false;
 #ifdef S1_MEASURE
             if (p.debug & 2) {
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(tempty_bar);
-                continue;
+                skip = true;
             }
 #endif
-            const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + hh * (CH * 32);
-            epilogue_tile<BN, EPI, MODE, EW, Store::kCols, NBUF>(p, &tmY, taddr, row0, col0, stage_buf, nstore, tempty_bar, lane, res);
+            if (!skip) {
+                const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16) + hh * (CH * 32);
+                epilogue_tile<BN, EPI, MODE, EW, Store::kCols, NBUF>(p, &tmY, taddr, row0, col0, stage_buf, nstore, tempty_bar, lane, res);
+            }
+            if (!looked) {
+                const bool fed = feed_take(it + 1, ahead);
+                if (!__all_sync(0xffffffffu, fed)) {
+                    fail_role = 7;
+                    fail_tile = static_cast<int>(it + 1);
+                    break;
+                }
+            }
+            tile = ahead;
         }
         if (lane == 0) tma_store_wait<0>();  // smem reads and global writes of this warp's stores are complete
         __syncwarp();

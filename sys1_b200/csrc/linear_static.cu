@@ -26,7 +26,7 @@ using namespace s1;
 
 // The scratch itself: 256 bytes per GPU that loads the library, held until the process exits.
 // Words 0..3 are the status record the GEMM kernel fills when one of its bounded waits runs out
-// ({code, block, role, tile}); the rest is spare. Device code may name the array directly; host code may not -
+// ({code, block, role, tile}), words 4..5 the counters its CTAs draw their tiles from; the rest is spare. Device code may name the array directly; host code may not -
 // on the host this symbol is only a handle, the real address comes from cudaGetSymbolAddress (below).
 #define S1_STATIC_SCRATCH_BYTES 256
 static __device__ __align__(256) int s1_static_scratch[S1_STATIC_SCRATCH_BYTES / sizeof(int)];
@@ -203,6 +203,8 @@ extern "C" int s1_linear_static(int device_ordinal, void* cuda_stream, const s1_
     p.residual = static_cast<const __nv_bfloat16*>(residual);
     p.bias = nullptr;
     p.status = d.scratch;  // the device address obtained at set-up, never the host-side symbol
+    p.tile_counter = reinterpret_cast<unsigned int*>(d.scratch + 4);
+    p.dynamic_tiles = 0;
     if (epi == S1_EPI_SWIGLU) {
         p.n_tile_stride = 128;
         p.half1_base = 0;
@@ -223,7 +225,7 @@ extern "C" int s1_linear_static(int device_ordinal, void* cuda_stream, const s1_
         return fail(err, err_len, S1_ECUDA, "s1_linear_static: cuTensorMapEncodeTiled failed");
 
     // the array keeps whatever the last call left in it: the status record must start at zero
-    e = cudaMemsetAsync(d.scratch, 0, 4 * sizeof(int), stream);
+    e = cudaMemsetAsync(d.scratch, 0, 8 * sizeof(int), stream);  // and the two tile counters behind it
     if (e != cudaSuccess) return fail(err, err_len, S1_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
 
     int mode = residual ? 1 : 0;

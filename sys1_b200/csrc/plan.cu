@@ -14,6 +14,8 @@
 #include "context.h"
 
 namespace {
+
+constexpr size_t kMaxLivePlans = 4096;  // records of a few dozen bytes; a caller that never releases is told so
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Layout {
@@ -89,19 +91,30 @@ extern "C" int s1_batch_plan(s1_ctx* ctx, const int32_t* cu_seqlens_host, int nu
     for (auto& p : ctx->plans)
         if (p.dev == rec.dev) p = rec, replaced = true;
     if (!replaced) {
-        if (ctx->plans.size() >= 16) {  // a few batches in flight at most: forget the oldest that is not in use
-            for (size_t i = 0; i < ctx->plans.size(); ++i)
-                if (ctx->plans[i].dev != used_dev) {
-                    ctx->plans.erase(ctx->plans.begin() + i);
-                    break;
-                }
-        }
+        if (ctx->plans.size() >= kMaxLivePlans)
+            return s1_fail(ctx, S1_EINVAL, "s1_batch_plan: %zu plans are alive on this context; release the ones no longer needed (s1_batch_plan_release)",
+                           ctx->plans.size());
         ctx->plans.push_back(rec);
     }
     ctx->plan_in_use = -1;
     for (size_t i = 0; i < ctx->plans.size(); ++i)
         if (used_dev && ctx->plans[i].dev == used_dev) ctx->plan_in_use = static_cast<int>(i);
     return S1_OK;
+}
+
+extern "C" int s1_batch_plan_release(s1_ctx* ctx, const void* plan) {
+    if (!ctx) return S1_EINVAL;
+    const unsigned char* used_dev = (ctx->plan_in_use >= 0) ? ctx->plans[ctx->plan_in_use].dev : nullptr;
+    for (size_t i = 0; i < ctx->plans.size(); ++i)
+        if (ctx->plans[i].dev == plan) {
+            ctx->plans.erase(ctx->plans.begin() + i);
+            ctx->plan_in_use = -1;
+            if (used_dev && used_dev != plan)
+                for (size_t k = 0; k < ctx->plans.size(); ++k)
+                    if (ctx->plans[k].dev == used_dev) ctx->plan_in_use = static_cast<int>(k);
+            return S1_OK;
+        }
+    return S1_OK;  // not (or no longer) known: nothing to forget
 }
 
 extern "C" int s1_use_batch_plan(s1_ctx* ctx, const void* plan) {

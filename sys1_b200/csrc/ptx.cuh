@@ -69,6 +69,46 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// The same with cluster-scope acquire: the data the barrier guards may have been written by the peer CTA of a pair
+// (st.shared::cluster followed by mbarrier.arrive.release.cluster on this CTA's barrier).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, long long limit_cycles) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((spin & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > limit_cycles) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+// Store into shared memory of any CTA of the cluster (cluster-space address from map_to_cta).
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
 // ------------------------------------------------------------------ clusters (CTA pairs)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

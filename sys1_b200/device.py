@@ -8,6 +8,7 @@ library's work is ordered with the tensors' producers and consumers).
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -83,7 +84,15 @@ class Context:
                                            C.c_void_p(plan.data_ptr()), need))
         plan._s1_shape = (len(cu) - 1, int(total_tokens))   # (num_seqs, total_tokens) the plan describes
         plan._s1_owner = buf
+        # the context forgets the plan when the tensor goes (its memory may then hold anything)
+        weakref.finalize(plan, Context._release_plan, weakref.ref(self), plan.data_ptr())
         return plan
+
+    @staticmethod
+    def _release_plan(ctx_ref, pointer: int) -> None:
+        ctx = ctx_ref()
+        if ctx is not None and getattr(ctx, "_h", None) is not None:
+            ctx._lib.s1_batch_plan_release(ctx._h, C.c_void_p(pointer))
 
     def use_plan(self, plan: Optional[torch.Tensor]) -> None:
         self.check(self._lib.s1_use_batch_plan(self.handle, C.c_void_p(0 if plan is None else plan.data_ptr())))
@@ -108,6 +117,16 @@ class Context:
         buf = C.create_string_buffer(unique_id, _lib.COMM_ID_BYTES)
         self.check(self._lib.s1_comm_init(self.handle, C.cast(buf, C.c_void_p), int(rank), int(size)))
         self.comm_rank, self.comm_size = int(rank), int(size)
+
+    def exchange_register(self, rank: int, size: int, local_base: int, multicast_base: int, nbytes: int, flag_ptrs) -> None:
+        """`s1_exchange_register`: sums of buffers inside `[local_base, local_base + nbytes)` (symmetric memory with a
+        multicast mapping) run as this library's own NVSwitch kernel. `flag_ptrs[r]` = rank r's zeroed flag array as
+        mapped on this GPU."""
+        if len(flag_ptrs) != size:
+            raise ValueError("one flag array per rank")
+        arr = (C.c_void_p * size)(*[int(p) for p in flag_ptrs])
+        self.check(self._lib.s1_exchange_register(self.handle, int(rank), int(size), C.c_void_p(int(local_base)),
+                                                  C.c_void_p(int(multicast_base)), int(nbytes), arr, _lib.EXCHANGE_FLAG_BYTES))
 
     def all_reduce_(self, t: torch.Tensor, wait: bool = True) -> torch.Tensor:
         """In-place bf16 sum over the ranks (`s1_allreduce_bf16`), after the work queued on this context's stream.

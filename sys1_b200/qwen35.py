@@ -376,7 +376,7 @@ def batch_plan_cached(owner, ctx, bounds):
     key = (id(ctx), tuple(bounds))
     cache = owner.__dict__.setdefault("_plans", {})
     if key not in cache:
-        if len(cache) >= 4:
+        if len(cache) >= 8:
             cache.pop(next(iter(cache)))
         cache[key] = ctx.batch_plan(bounds, bounds[-1])
     return cache[key]

@@ -19,7 +19,7 @@ from typing import Optional
 import torch
 
 from . import device
-from ._lib import EPI_SWIGLU
+from ._lib import EPI_SWIGLU, EXCHANGE_FLAG_BYTES
 from .linear import fused_linear
 
 
@@ -42,6 +42,48 @@ class TensorParallel:
             ctx.set_option("comm_ctas", comm_ctas)
             ctx.comm_init(rank, size, box[0])
         return cls(ctx, rank, size)
+
+    def symmetric_arena(self, nbytes: int, group=None) -> None:
+        """Collective. Allocates `nbytes` of symmetric memory (the same buffer on every rank plus its NVLink multicast
+        mapping, from `torch.distributed._symmetric_memory`) and registers it with the context: sums of tensors carved
+        out of it by `symmetric_empty` run as the library's own in-switch reduction kernel instead of the NCCL call.
+        Torch only allocates and maps the memory; no torch collective touches it."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = dist.group.WORLD if group is None else group
+        dev = torch.device("cuda", self.ctx.ordinal)
+        nbytes = -(-int(nbytes) // 256) * 256
+        arena = symm.empty(nbytes, dtype=torch.uint8, device=dev)
+        arena_handle = symm.rendezvous(arena, group)
+        flags = symm.empty(EXCHANGE_FLAG_BYTES // 4, dtype=torch.int32, device=dev)
+        flags.zero_()
+        flags_handle = symm.rendezvous(flags, group)
+        if not arena_handle.multicast_ptr:
+            raise RuntimeError("symmetric memory without a multicast mapping: the in-switch reduction needs NVSwitch")
+        torch.cuda.synchronize(dev)
+        dist.barrier(group)  # every rank's flags are zero before anyone can raise one
+        self.ctx.exchange_register(self.rank, self.size, arena.data_ptr(), arena_handle.multicast_ptr, nbytes,
+                                   [flags_handle.buffer_ptrs[r] for r in range(self.size)])
+        self._arena, self._arena_at, self._arena_keep = arena, 0, (arena_handle, flags, flags_handle)
+
+    def symmetric_empty(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        """A tensor inside the registered arena (256-byte aligned; a bump allocator: `symmetric_reset` frees all).
+        Every rank must carve the same sequence of shapes, so that a tensor sits at the same offset everywhere."""
+        arena = getattr(self, "_arena", None)
+        if arena is None:
+            raise RuntimeError("call symmetric_arena first")
+        count = 1
+        for d in shape:
+            count *= int(d)
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        if self._arena_at + nbytes > arena.numel():
+            raise RuntimeError(f"symmetric arena of {arena.numel()} bytes is full ({self._arena_at} used, {nbytes} asked)")
+        t = arena[self._arena_at:self._arena_at + nbytes].view(dtype).view(*shape)
+        self._arena_at += -(-nbytes // 256) * 256
+        return t
+
+    def symmetric_reset(self) -> None:
+        self._arena_at = 0
 
     def column_shard(self, weight: torch.Tensor) -> torch.Tensor:
         return device.column_parallel_shard(weight, self.rank, self.size)
@@ -73,7 +115,10 @@ class RowParallelLinear:
         step = -(-T // self.slabs)
         step = max(128, -(-step // 128) * 128)  # whole 128-row tiles per slab
         ctx = self.tp.ctx
-        share = exchange and self.tp.size > 1 and self.comm_sms > 0 and T > step
+        beside = exchange and self.tp.size > 1 and T > step   # a slab's sum runs beside the next slab's projections
+        share = beside and self.comm_sms > 0
+        if beside:
+            ctx.set_option("dynamic_tiles", 1)   # a projection CTA held up by the collective's blocks must not hold up the launch
         try:
             for a in range(0, T, step):
                 b = min(T, a + step)
@@ -83,6 +128,8 @@ class RowParallelLinear:
                 if exchange and self.tp.size > 1:
                     ctx.all_reduce_(out[a:b], wait=False)
         finally:
+            if beside:
+                ctx.set_option("dynamic_tiles", 0)
             if share:
                 ctx.set_option("gemm_sms", 0)
         if exchange and self.tp.size > 1:
@@ -119,7 +166,10 @@ class Mlp:
         res = residual if self.tp.rank == 0 else None
         step = max(128, -(-(-(-T // self.slabs)) // 128) * 128)  # whole 128-row tiles per slab
         h = torch.empty((min(step, T), self.gate.shape[0]), dtype=torch.bfloat16, device=x.device)
-        share = exchange and self.tp.size > 1 and self.comm_sms > 0 and T > step
+        beside = exchange and self.tp.size > 1 and T > step   # a slab's sum runs beside the next slab's projections
+        share = beside and self.comm_sms > 0
+        if beside:
+            ctx.set_option("dynamic_tiles", 1)   # a projection CTA held up by the collective's blocks must not hold up the launch
         try:
             for a in range(0, T, step):
                 b = min(T, a + step)
@@ -130,6 +180,8 @@ class Mlp:
                 if exchange and self.tp.size > 1:
                     ctx.all_reduce_(out[a:b], wait=False)
         finally:
+            if beside:
+                ctx.set_option("dynamic_tiles", 0)
             if share:
                 ctx.set_option("gemm_sms", 0)
         if exchange and self.tp.size > 1:
@@ -298,7 +350,10 @@ class Decoder:
                 cu_g = [int(c) - a for c in cu_seqlens_host[s0:s1 + 1]]
                 groups.append((x[a:b], cu_g, pos[a:b], batch_plan_cached(self, ctx, cu_g)))
         tickets = [None] * len(groups)
-        carve = exchange and self.tp.size > 1 and self.comm_sms > 0
+        beside = exchange and self.tp.size > 1   # one group's sums run beside the other group's kernels
+        carve = beside and self.comm_sms > 0
+        if beside:
+            ctx.set_option("dynamic_tiles", 1)   # a projection CTA held up by the collective's blocks must not hold up the launch
         if carve:
             ctx.set_option("gemm_sms", max(2, device.sm_count(ctx) - self.comm_sms))
         try:
@@ -314,6 +369,8 @@ class Decoder:
                     ctx.all_reduce_wait_ticket(t)
         finally:
             ctx.use_plan(previous)
+            if beside:
+                ctx.set_option("dynamic_tiles", 0)
             if carve:
                 ctx.set_option("gemm_sms", 0)
         return self.norm(x)

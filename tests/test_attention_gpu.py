@@ -156,3 +156,32 @@ def test_batch_plan_replaces_the_per_call_tables(ctx):
     finally:
         ctx.use_plan(None)
     ctx.sync()
+
+
+def test_batch_plans_live_until_released(ctx):
+    """A plan stays known to its context however many others are built after it (a stack caches the plans of its recent
+    batches) and is forgotten when released, which the Python tensor does by itself when it is dropped."""
+    import ctypes as C
+    cu = np.array([0, 200, 456], dtype=np.int32)
+    first = ctx.batch_plan(cu, 456)
+    later = [ctx.batch_plan(np.array([0, 128 + i], dtype=np.int32), 128 + i) for i in range(40)]
+    ctx.use_plan(first)
+    assert ctx.plan_covers(2, 456)
+    ctx.use_plan(None)
+    pointer = first.data_ptr()
+    keep = first._s1_owner   # the memory stays allocated: only the plan object goes
+    del first
+    rc = ctx._lib.s1_use_batch_plan(ctx.handle, C.c_void_p(pointer))
+    assert rc == -1 and b"no plan was built" in ctx._lib.s1_last_error(ctx.handle)
+    # releasing the plan in use leaves none in use; releasing an unknown buffer is not an error
+    ctx.use_plan(later[0])
+    assert ctx._lib.s1_batch_plan_release(ctx.handle, C.c_void_p(later[0].data_ptr())) == 0
+    assert ctx._lib.s1_batch_plan_release(ctx.handle, C.c_void_p(later[0].data_ptr())) == 0
+    q = torch.randn(128, 4, 64).to(torch.bfloat16).to(DEV)
+    out = torch.empty(128, 256, dtype=torch.bfloat16, device=DEV)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    rc = ctx._lib.s1_attention(ctx.handle, P(q), 256, P(q), 256, P(q), 256, None, 1, 128, 4, 64, -1, C.c_float(0.125), P(out), 256, None, 0)
+    assert rc == -1 and b"no batch plan" in ctx._lib.s1_last_error(ctx.handle)
+    ctx._plan = None
+    del keep, later
+    ctx.sync()

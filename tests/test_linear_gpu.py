@@ -222,3 +222,29 @@ def test_residual_stream_updated_in_place(ctx):
     assert got.data_ptr() == stream.data_ptr()
     assert_matches_bf16_oracle(got, oracle.linear(x.cpu(), w.cpu(), residual=res.cpu()), "in-place residual")
     assert (got.float() - want.float()).abs().max() <= 2 ** -7 * want.float().abs().max()
+
+
+@pytest.mark.parametrize("bn", [0, 128, 256, 512])
+def test_tiles_drawn_at_run_time_give_the_same_result(ctx, bn):
+    """`dynamic_tiles`: the CTAs draw their tiles from a counter instead of working through fixed shares. Which CTA computes
+    a tile does not change the tile, so every epilogue must give bit-identical results, launch after launch (the counter
+    is put back by the kernel itself), for tile counts below, at and far above the number of CTAs."""
+    g = torch.Generator().manual_seed(77)
+    for T, K, N in [(300, 256, 512), (9000, 768, 2304), (40000, 320, 1536)]:
+        x = dev_bf16(torch.randn(T, K, generator=g))
+        w = dev_bf16(torch.randn(N, K, generator=g) * 0.05)
+        r = dev_bf16(torch.randn(T, N, generator=g))
+        ctx.set_option("gemm_bn", bn)
+        try:
+            want = [linear.fused_linear(x, w), linear.fused_linear(x, w, residual=r),
+                    linear.fused_linear(x, w, epilogue=EPI_GEGLU), linear.fused_linear(x, w[: N // 2], weight_up=w[N // 2:], epilogue=EPI_SWIGLU)]
+            ctx.set_option("dynamic_tiles", 1)
+            for _ in range(3):
+                got = [linear.fused_linear(x, w), linear.fused_linear(x, w, residual=r),
+                       linear.fused_linear(x, w, epilogue=EPI_GEGLU), linear.fused_linear(x, w[: N // 2], weight_up=w[N // 2:], epilogue=EPI_SWIGLU)]
+                for a, b in zip(got, want):
+                    assert torch.equal(a, b)
+        finally:
+            ctx.set_option("dynamic_tiles", 0)
+            ctx.set_option("gemm_bn", 0)
+    ctx.sync()

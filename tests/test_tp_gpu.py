@@ -57,14 +57,46 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize()
         ok_sum = bool((t == float(sum(range(1, world + 1)))).all())
         layers = _layer_group(rank, world, dev, tp, dist)
-        q.put((rank, err_single, err_oracle, same, ok_sum, layers))
+        own = _own_exchange(rank, world, dev, tp, dist, mlp, xd, y)
+        q.put((rank, err_single, err_oracle, same, ok_sum, layers, own))
     except Exception as exc:  # pragma: no cover
         q.put((rank, repr(exc)))
     finally:
         dist.destroy_process_group()
 
 
-def _layer_group(rank, world, dev, tp, dist):
+def _own_exchange(rank, world, dev, tp, dist, mlp, xd, y_nccl):
+    """The same sums through the library's own kernel (in-switch reduction on symmetric memory) instead of NCCL: bare sums
+    of many sizes back to back (ragged against the block and rank split), the MLP with its output in the arena, and the layer
+    group with the residual stream in the arena. Returns (sums exact, largest relative difference of the MLP from the NCCL path, ranks bit-identical, layer results)."""
+    tp.symmetric_arena(24 << 20)
+    sums_ok = True
+    for i, count in enumerate([8, 4096, 1000 * 8, 3 * 512 * 8 + 8, 1 << 20, 123456 * 8] * 3):
+        t = tp.symmetric_empty((count,))
+        t.copy_(torch.arange(count, device=dev).remainder(61).to(torch.bfloat16) * float(rank + 1))
+        tp.ctx.all_reduce_(t)
+        want = torch.arange(count, device=dev).remainder(61).to(torch.bfloat16).float() * float(sum(range(1, world + 1)))
+        sums_ok = sums_ok and bool((t.float() == want.to(torch.bfloat16).float()).all())
+        if i % 6 == 5:
+            tp.ctx.sync()
+            dist.barrier()   # nobody reuses the arena while a peer may still read it
+            tp.symmetric_reset()
+    tp.ctx.sync()
+    dist.barrier()
+    tp.symmetric_reset()
+    out = tp.symmetric_empty(tuple(xd.shape))
+    y = mlp(xd, residual=xd, out=out)
+    tp.ctx.sync()
+    # against the NCCL path: the same two partials added with one rounding each way; the switch may break ties its own way
+    mlp_close = float(((y.float() - y_nccl.float()).abs() / y_nccl.float().abs().clamp_min(0.25)).max())
+    gathered = [torch.zeros_like(y.cpu()) for _ in range(world)]
+    dist.all_gather(gathered, y.cpu())
+    mlp_same = all(torch.equal(gathered[0], t) for t in gathered[1:])
+    layers = _layer_group(rank, world, dev, tp, dist, symmetric=True)
+    return sums_ok, mlp_close, mlp_same, layers
+
+
+def _layer_group(rank, world, dev, tp, dist, symmetric=False):
     """A (linear, linear, linear, full) group of tensor-parallel layers at a reduced width with the large model's head
     ratios (repeat 3 between key and value heads, 6 query heads per KV head) against the unsharded stack on this GPU and
     the f32 oracle; returns (max-rel vs unsharded, max-rel vs oracle, all ranks bit-identical)."""
@@ -80,11 +112,18 @@ def _layer_group(rank, world, dev, tp, dist):
     pos = torch.from_numpy(b.positions).to(dev)
     x0 = dw["embed_tokens"][ids.to(dev)]
     dec = tensor_parallel.Decoder(dw, cfg, tp, slabs=2)
+    if symmetric:   # the residual stream in the arena: every sum of the group runs as the library's own kernel
+        tp.ctx.sync()
+        dist.barrier()
+        tp.symmetric_reset()
+        fresh = lambda: tp.symmetric_empty(tuple(x0.shape)).copy_(x0)
+    else:
+        fresh = x0.clone
     for _ in range(2):
-        y = dec.forward_embeds(x0.clone(), b.cu_seqlens, pos)
+        y = dec.forward_embeds(fresh(), b.cu_seqlens, pos)
     tp.ctx.sync()
     # two micro-batches of whole sequences alternating between computing and exchanging (ticketed waits)
-    y2 = dec.forward_embeds(x0.clone(), b.cu_seqlens, pos, micro_batches=2)
+    y2 = dec.forward_embeds(fresh(), b.cu_seqlens, pos, micro_batches=2)
     tp.ctx.sync()
     torch.cuda.synchronize()
     assert float((y2.float() - y.float()).abs().max()) <= 3e-2 * float(y.float().abs().max())
@@ -117,8 +156,10 @@ def test_tensor_parallel_mlp_on_two_gpus():
     for p in procs:
         p.join(timeout=30)
     for r in results:
-        assert len(r) == 6, r
-        rank, err_single, err_oracle, same, ok_sum, layers = r
+        assert len(r) == 7, r
+        rank, err_single, err_oracle, same, ok_sum, layers, own = r
         assert err_single <= 2e-2 and err_oracle <= 2e-2, r
         assert same and ok_sum, r
         assert layers[0] <= 3e-2 and layers[1] <= 3e-2 and layers[2], r  # four layers deep: two bf16 evaluations drift apart a little
+        assert own[0] and own[1] <= 2.0 ** -7 and own[2], r   # the library's own exchange kernel: exact sums, the MLP as through NCCL to one rounding, identical on all ranks
+        assert own[3][0] <= 3e-2 and own[3][1] <= 3e-2 and own[3][2], r
