@@ -366,11 +366,12 @@ int s1_allreduce_wait_ticket(s1_ctx* ctx, long long ticket);
  * buffer inside that range runs this library's own kernel instead of the NCCL call: every rank reduces its slice inside the
  * NVSwitch (`multimem.ld_reduce`, f32 accumulation, one rounding) and writes the sums into every rank's copy
  * (`multimem.st`); per GPU (1 + 1 / ranks) buffers of NVLink traffic in each direction, whatever the number of ranks;
- * a few blocks of 1024 threads ("comm_ctas": how many, default 8, at most 64), so that the projections running beside the
+ * a few blocks of 1024 threads ("comm_ctas": how many, by default 16 for two ranks and 8 for four or more, at most 64), so that the projections running beside the
  * sum lose few SMs to it; bit-identical results on all ranks. Tickets
  * and waits work as for the NCCL path; a context that only sums symmetric buffers needs no s1_comm_init. The ranks meet
  * through the flag arrays with bounded polls: a rank that never shows up makes the others give up after
  * "exchange_wait_ms" (s1_set_option, default 10000) and s1_sync report S1_EKERNEL; the context stays usable.
+ * `size` = 0 forgets the registration (the other arguments are ignored). The caller keeps the memory mapped until then.
  */
 #define S1_EXCHANGE_FLAG_BYTES 4096
 int s1_exchange_register(s1_ctx* ctx, int rank, int size, void* local_base, void* multicast_base, size_t bytes,

@@ -111,6 +111,12 @@ __global__ void __launch_bounds__(kThreads, 1) s1_exchange_allreduce_kernel(cons
 extern "C" int s1_exchange_register(s1_ctx* ctx, int rank, int size, void* local_base, void* multicast_base, size_t bytes,
                                     void* const* flag_arrays_host, size_t flag_bytes) {
     if (!ctx) return S1_EINVAL;
+    if (size == 0) {  // forget the registration: sums go back to the communicator path
+        ctx->xchg_local = ctx->xchg_mc = nullptr;
+        ctx->xchg_bytes = 0;
+        ctx->xchg_size = 0;
+        return S1_OK;
+    }
     if (size < 2 || size > kMaxRanks || rank < 0 || rank >= size)
         return s1_fail(ctx, S1_EINVAL, "s1_exchange_register: rank %d of %d (2 to %d ranks)", rank, size, kMaxRanks);
     if (!local_base || !multicast_base || !flag_arrays_host || bytes < 16)
@@ -144,7 +150,8 @@ int s1_exchange_launch(s1_ctx* ctx, void* buf, size_t count, cudaStream_t stream
     ctx->xchg_epoch += 2;
     p.status = ctx->status_dev;
     p.wait_ns = static_cast<unsigned long long>(ctx->opt_exchange_wait_ms) * 1000000ull;
-    int blocks = ctx->opt_comm_ctas > 0 ? ctx->opt_comm_ctas : 8;
+    // a rank reduces 1 / size of the buffer: fewer ranks, more blocks (8 for four ranks and up, 16 for two)
+    int blocks = ctx->opt_comm_ctas > 0 ? ctx->opt_comm_ctas : (32 / ctx->xchg_size > 8 ? 32 / ctx->xchg_size : 8);
     if (blocks > S1_EXCHANGE_MAX_BLOCKS) blocks = S1_EXCHANGE_MAX_BLOCKS;
     S1_KEEP_PROJECTION_SPLIT(s1_exchange_allreduce_kernel);  // or its blocks would keep the projections' CTAs off their SMs
     s1_exchange_allreduce_kernel<<<blocks, kThreads, 0, stream>>>(p);
