@@ -431,6 +431,29 @@ def decoder_block(args, rank, world, dev, steps, warmup):
 
 
 # ================================================================================================ tensor parallel
+def _kernel_timeline(step, ctx, rank, path):
+    """Every kernel of one step with its start and duration (torch's profiler, i.e. CUPTI activity records; the step is
+    run twice under the profiler and the second run is kept), written as CSV `name,start_us,duration_us` to
+    `<path>.rank<r>.csv`: shows which kernels ran beside which (a sum over ranks beside the other micro-batch's projections)."""
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step()
+        ctx.sync()
+        torch.cuda.synchronize()
+        step()
+        ctx.sync()
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
+    # the second run starts at the first device-to-device copy (the step's `x.copy_`) after the first run's last kernel
+    copies = [i for i, e in enumerate(ev) if e.name.startswith("Memcpy DtoD")]
+    ev = ev[copies[1]:] if len(copies) > 1 else ev
+    t0 = ev[0].time_range.start if ev else 0
+    with open(f"{path}.rank{rank}.csv", "w") as f:
+        f.write("name,start_us,duration_us\n")
+        for e in ev:
+            f.write("%s,%.1f,%.1f\n" % (e.name[:80].replace(",", ";"), e.time_range.start - t0, e.time_range.end - e.time_range.start))
+
+
 def tp_block(args, rank, world, dev, steps, warmup):
     """One (linear, linear, linear, full) layer group of the 27B-shaped hybrid model (hidden 5120, SwiGLU 17408, 16 key / 48
     value delta-rule heads of 128, 24 query / 4 KV heads of 256) over a packed batch of `--tp-tokens` tokens with lengths
@@ -539,6 +562,8 @@ def tp_block(args, rank, world, dev, steps, warmup):
         other = {"exchange": "nccl", "comm_sms": sms_n, "ms": ms_n, "ms_without_exchange": ms_math_n, "ms_allreduce_alone": ms_ar_n,
                  "allreduce_busbw_gbs": busbw(ms_ar_n), "exchange_hidden_frac": 1.0 - (ms_n - ms_math_n) / ms_ar_n}
         del xn
+    if args.timeline:
+        _kernel_timeline(lambda: (x.copy_(x0), dec.forward_embeds(x, b.cu_seqlens, pos, micro_batches=mbs)), ctx, rank, args.timeline)
     sweep = None
     if args.tp_sweep and world > 1:
         sweep = []
@@ -902,6 +927,7 @@ def main():
     ap.add_argument("--exchange", default="both", choices=["multimem", "nccl", "both"],
                     help="tp: sums over ranks by the library's own in-switch reduction kernel on symmetric memory (multimem), by "
                          "ncclAllReduce (nccl), or the first with the second timed beside it (both, default)")
+    ap.add_argument("--timeline", default="", help="tp: also write one step's kernel timeline (CSV per rank) to this path prefix")
     ap.add_argument("--tp-sweep", action="store_true", help="tp: also time the group for a grid of comm-sms x micro-batches x pdl settings")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step from a CUDA graph (for small token budgets, where launching from Python is the bottleneck)")
