@@ -86,6 +86,19 @@ __device__ __forceinline__ void pair_barrier(int q4) {
     else if (q4 == 2) named_barrier<3, 64>();
     else named_barrier<4, 64>();
 }
+// The same barrier, carrying one bit: true if any of the 64 threads says so.
+__device__ __forceinline__ bool pair_any(int q4, bool mine) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "barrier.cta.red.or.pred p, %2, 64, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(static_cast<uint32_t>(mine)), "r"(q4 + 1)
+        : "memory");
+    return r != 0;
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -250,24 +263,26 @@ s1_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 mx3 = fmax3(mx3, __uint_as_float(s[e + 6]), __uint_as_float(s[e + 7]));
             }
             const float mx_own = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            // the other half's maximum, through two spare TMEM columns (double-buffered by tile parity)
-            const uint32_t xcol = lane_addr + 192 + 2 * (i & 1);
-            tmem_st_32x32b_x1(xcol + ch, __float_as_uint(mx_own));
-            tmem_st_wait();
-            tc_fence_before();
-            pair_barrier(q4);
-            tc_fence_after();
-            const float mx_other = __uint_as_float(tmem_ld_32x32b_x1(xcol + (ch ^ 1)));
-            tmem_ld_wait();
-            const float m_new = fmaxf(m_used, fmaxf(mx_own, mx_other));
+            // Does any row of this quarter need a new reference maximum - its own half's maximum more than 2^8 above the
+            // one in use, or none in use yet? One bit through the pair's barrier settles it for both warps; only then is the
+            // other half's maximum fetched (through two spare TMEM columns, double-buffered by tile parity). Most tiles past
+            // a row's first few skip the exchange.
+            // NaN (both -inf) compares false; -inf -> finite gives +inf, which rescales by ex2(-inf) = 0
+            const bool rescale = pair_any(q4, i == 0 || (mx_own - m_used) * c > kRescaleLog2);
             float alpha = 1.f;
-            bool rescale = false;
-            if (i == 0) {
-                m_used = m_new;
-            } else {
-                // NaN (both -inf) compares false; -inf -> finite gives +inf and rescales by ex2(-inf) = 0
-                rescale = __any_sync(0xffffffffu, (m_new - m_used) * c > kRescaleLog2);
-                if (rescale && m_new != -INFINITY) {
+            if (rescale) {
+                const uint32_t xcol = lane_addr + 192 + 2 * (i & 1);
+                tmem_st_32x32b_x1(xcol + ch, __float_as_uint(mx_own));
+                tmem_st_wait();
+                tc_fence_before();
+                pair_barrier(q4);
+                tc_fence_after();
+                const float mx_other = __uint_as_float(tmem_ld_32x32b_x1(xcol + (ch ^ 1)));
+                tmem_ld_wait();
+                const float m_new = fmaxf(m_used, fmaxf(mx_own, mx_other));
+                if (i == 0) {
+                    m_used = m_new;
+                } else if (m_new != -INFINITY) {
                     alpha = ex2((m_used - m_new) * c);
                     m_used = m_new;
                 }
@@ -288,7 +303,7 @@ s1_attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 ok = mbar_wait(bar_o, (i - 1) & 1, abort_flag);
                 if (!__all_sync(0xffffffffu, ok)) { fail = 9; break; }
                 tc_fence_after();
-                if (rescale) {  // this thread's 32 of the row's 64 output dims
+                if (rescale) {  // this thread's 32 of the row's 64 output dims (i >= 1 here)
                     uint32_t o[32];
                     tmem_ld_32x32b_x32(lane_addr + 128 + ch * 32, o);
                     tmem_ld_wait();

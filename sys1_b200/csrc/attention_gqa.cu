@@ -86,6 +86,19 @@ __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(_
 constexpr float kRescaleLog2 = 8.f;
 
 // Barrier of the two warps that share a quarter of the query rows (ids 1..4; 0 is __syncthreads).
+// The pair's barrier carrying one bit: true if any of its 64 threads says so.
+__device__ __forceinline__ bool pair_any_gqa(int q4, bool mine) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "barrier.cta.red.or.pred p, %2, 64, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(static_cast<uint32_t>(mine)), "r"(q4 + 1)
+        : "memory");
+    return r != 0;
+}
 __device__ __forceinline__ void pair_barrier_gqa(int q4) {
     if (q4 == 0) named_barrier<1, 64>();
     else if (q4 == 1) named_barrier<2, 64>();
@@ -248,23 +261,25 @@ s1_attention_gqa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                 mx1 = max3(mx1, __uint_as_float(s[e + 2]), __uint_as_float(s[e + 3]));
             }
             const float mx_own = fmaxf(mx0, mx1);
-            // the other half's maximum, through two spare TMEM columns (double-buffered by step parity)
-            const uint32_t xcol = lane_addr + 320 + 2 * (i & 1);
-            tmem_st_32x32b_x1(xcol + ch, __float_as_uint(mx_own));
-            tmem_st_wait();
-            tc_fence_before();
-            pair_barrier_gqa(q4);
-            tc_fence_after();
-            const float mx_other = __uint_as_float(tmem_ld_32x32b_x1(xcol + (ch ^ 1)));
-            tmem_ld_wait();
-            const float m_new = fmaxf(m_used, fmaxf(mx_own, mx_other));
+            // One bit through the pair's barrier: does any row of this quarter need a new reference maximum (its own half's
+            // maximum more than 2^8 above the one in use, or none in use yet)? Only then is the other half's maximum fetched
+            // (two spare TMEM columns, double-buffered by step parity). NaN (both -inf) compares false; -inf -> finite gives
+            // +inf, which rescales by ex2(-inf) = 0.
+            const bool rescale = pair_any_gqa(q4, i == 0 || (mx_own - m_used) * c > kRescaleLog2);
             float alpha = 1.f;
-            bool rescale = false;
-            if (i == 0) {
-                m_used = m_new;
-            } else {
-                rescale = __any_sync(0xffffffffu, (m_new - m_used) * c > kRescaleLog2);
-                if (rescale && m_new != -INFINITY) {
+            if (rescale) {
+                const uint32_t xcol = lane_addr + 320 + 2 * (i & 1);
+                tmem_st_32x32b_x1(xcol + ch, __float_as_uint(mx_own));
+                tmem_st_wait();
+                tc_fence_before();
+                pair_barrier_gqa(q4);
+                tc_fence_after();
+                const float mx_other = __uint_as_float(tmem_ld_32x32b_x1(xcol + (ch ^ 1)));
+                tmem_ld_wait();
+                const float m_new = fmaxf(m_used, fmaxf(mx_own, mx_other));
+                if (i == 0) {
+                    m_used = m_new;
+                } else if (m_new != -INFINITY) {
                     alpha = ex2f((m_used - m_new) * c);
                     m_used = m_new;
                 }
