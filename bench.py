@@ -473,7 +473,7 @@ def tp_block(args, rank, world, dev, steps, warmup):
     # SMs the projections leave free while sums are in flight: NCCL's kernels need room of their own; the library's exchange
     # kernel is a few fat blocks and the projections draw their tiles at run time around it, so nothing is set aside
     comm_sms = args.comm_sms if args.comm_sms >= 0 else (0 if own else 16)
-    dec = tensor_parallel.Decoder(w, cfg, tp, slabs=args.slabs, comm_sms=comm_sms)
+    dec = tensor_parallel.Decoder(w, cfg, tp, slabs=args.slabs, comm_sms=comm_sms, comm_ctas=args.comm_ctas)
     H = cfg.hidden_size
     if own:   # the residual stream lives in symmetric memory: its sums run as the library's in-switch reduction kernel
         tp.symmetric_arena((args.tp_tokens + 2048) * H * 2 + 4096)
@@ -567,17 +567,17 @@ def tp_block(args, rank, world, dev, steps, warmup):
     sweep = None
     if args.tp_sweep and world > 1:
         sweep = []
-        for comm_sms in ((0, 8, 16) if own else (8, 16, 32)):
-            d2 = tensor_parallel.Decoder(w, cfg, tp, slabs=args.slabs, comm_sms=comm_sms)
+        for sweep_sms in ((0, 8, 16) if own else (8, 16, 32)):
             for blocks in ((4, 8, 16) if own else (args.comm_ctas,)):
+                d2 = tensor_parallel.Decoder(w, cfg, tp, slabs=args.slabs, comm_sms=sweep_sms, comm_ctas=blocks)
                 if own:
                     ctx.set_option("comm_ctas", blocks)
                 for m in (1, 2, 4):
                     for p_ in ((1,) if own else (0, 1)):
                         a_, b_, _ = measure(d2, m, p_, 3)
-                        sweep.append({"comm_sms": comm_sms, "comm_ctas": blocks, "micro_batches": m, "pdl": p_, "ms": a_,
+                        sweep.append({"comm_sms": sweep_sms, "comm_ctas": blocks, "micro_batches": m, "pdl": p_, "ms": a_,
                                       "ms_without_exchange": b_, "hidden_frac": 1.0 - (a_ - b_) / ms_ar if ms_ar > 0 else None})
-            del d2
+                del d2
         if own:
             ctx.set_option("comm_ctas", args.comm_ctas)
     flops = T * (3 * 766_443_520 + 744_488_960)   # projection flops of the group (three linear-attention + one full layer)

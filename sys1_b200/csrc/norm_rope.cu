@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(256) s1_norm_kernel(const NormParams p) {
     }
 }
 
-// Any width: one warp per row, the row re-read from L1 for each pass.
+// Any width (beyond 6144): one warp per row, the row re-read from L1 for each pass.
 __global__ void __launch_bounds__(256) s1_norm_wide_kernel(const NormParams p) {
     const int lane = threadIdx.x & 31;
     const long long row = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) >> 5;
@@ -360,6 +360,8 @@ extern "C" int s1_norm(s1_ctx* ctx, const void* x, long long ldx, const int32_t*
     else if (chunks <= 64) launch_norm<2, 32>(p, ctx->stream);
     else if (chunks <= 128) launch_norm<4, 32>(p, ctx->stream);
     else if (chunks <= 256) launch_norm<8, 32>(p, ctx->stream);
+    else if (chunks <= 512) launch_norm<16, 32>(p, ctx->stream);
+    else if (chunks <= 768) launch_norm<24, 32>(p, ctx->stream);   // hidden 5120: the row still fits the warp's registers
     else s1_norm_wide_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, ctx->stream>>>(p);
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;

@@ -308,11 +308,12 @@ class Decoder:
     `sys1_b200.qwen35.Decoder`); every rank cuts its own shards out of them."""
 
     def __init__(self, weights, cfg, tp: TensorParallel, max_positions: int = 8192, slabs: int = 4, comm_sms: int = 16,
-                 recurrence: str = "chunked"):
+                 recurrence: str = "chunked", comm_ctas: int = 0):
+        """`comm_ctas`: blocks of the library's own exchange kernel while it runs beside the projections (0 = its default)."""
         from . import qwen35
         dev = weights["norm"].device
         rope = qwen35.RopeParams(cfg.rope_theta, cfg.rotary_dim, max_positions, dev)
-        self.cfg, self.tp, self.comm_sms = cfg, tp, int(comm_sms)
+        self.cfg, self.tp, self.comm_sms, self.comm_ctas = cfg, tp, int(comm_sms), int(comm_ctas)
         self.layers = []
         for i in range(cfg.num_hidden_layers):
             kind = cfg.layer_type(i)
@@ -363,7 +364,15 @@ class Decoder:
                         if tickets[i] is not None:
                             ctx.all_reduce_wait_ticket(tickets[i])
                         ctx.use_plan(plan)
-                        tickets[i] = layer.mixer_part(xg, cu, pg, exchange) if stage == 0 else layer.mlp_part(xg, exchange)
+                        # the step's very last sum has nothing left to run beside: it may take every block it can use
+                        last = beside and layer is self.layers[-1] and stage == 1 and i == len(groups) - 1
+                        if last:
+                            ctx.set_option("comm_ctas", 32)
+                        try:
+                            tickets[i] = layer.mixer_part(xg, cu, pg, exchange) if stage == 0 else layer.mlp_part(xg, exchange)
+                        finally:
+                            if last:
+                                ctx.set_option("comm_ctas", self.comm_ctas)
             for t in tickets:
                 if t is not None:
                     ctx.all_reduce_wait_ticket(t)

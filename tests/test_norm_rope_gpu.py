@@ -23,7 +23,7 @@ def _close_one_step(got: torch.Tensor, want: torch.Tensor, min_exact: float = 0.
 
 @pytest.mark.parametrize("kind", [norm.LAYER_NORM, norm.RMS_NORM])
 @pytest.mark.parametrize("rows,width", [(1, 8), (37, 64), (100, 128), (33, 256), (19, 768), (65, 1024), (9, 1536), (5, 2048),
-                                        (7, 2560), (3, 5120), (1000, 1024)])
+                                        (7, 2560), (70, 4096), (3, 5120), (41, 6144), (5, 8192), (1000, 1024)])
 def test_norm_matches_oracle(ctx, kind, rows, width):
     g = torch.Generator().manual_seed(rows * 7 + width + kind)
     x = (torch.randn(rows, width, generator=g) * 2 + 0.3).to(torch.bfloat16)
