@@ -4,8 +4,10 @@
 //
 // Rank r owns the r-th slice of the buffer. Per 16 bytes of its slice it issues one `multimem.ld_reduce` (the switch
 // fetches that location from every GPU, adds in f32 and returns the bf16 sum) and one `multimem.st` (the switch writes the
-// sum into every GPU's copy). Per GPU that is one buffer's worth of traffic out and one in, whatever the number of ranks,
-// and a handful of SMs: the projections of the next micro-batch keep the rest. Every rank ends with bit-identical values.
+// sum into every GPU's copy). Per GPU that is (1 + 1 / ranks) buffers of NVLink traffic in each direction, whatever the
+// number of ranks, and a handful of SMs: the projections of the next micro-batch keep the rest. Every rank ends with
+// bit-identical values. The blocks are few and fat (1024 threads, 8 reductions in flight each): a projection CTA needs nearly
+// all of an SM's shared memory, so an SM that holds a block of this kernel is lost to the projection beside it either way.
 //
 // Two flag exchanges bracket the data phase (every rank's partial is complete before anyone reduces; every rank's
 // stores have landed before anyone reads): block b of rank r writes the call's epoch into slot (b, r) of every peer's flag
@@ -51,7 +53,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 // All ranks' block `blockIdx.x` meet: thread r < size tells peer r "rank `rank` reached `epoch`" and waits for peer r's word.
 // Flags only grow (epochs are issued in order), so "at least epoch" is the test. Returns false if a peer never showed up.
-// (The verdict travels through the barrier itself; the kernel uses no shared memory.)
+// (The outcome travels through the barrier itself; the kernel uses no shared memory.)
 __device__ __forceinline__ bool meet(const ExchangeParams& p, uint32_t epoch) {
     int timed_out = 0;
     __syncthreads();
