@@ -169,3 +169,28 @@ def test_split_sequences_into_micro_batches():
         assert groups[0][0] == 0 and groups[-1][1] == len(lens) and all(a[1] == b[0] for a, b in zip(groups, groups[1:]))
         sizes = [cu[b] - cu[a] for a, b in groups]
         assert sum(sizes) == 65536 and max(sizes) - min(sizes) <= 2 * 8192  # cuts fall on sequence boundaries
+
+
+def test_symmetric_arena_hands_out_aligned_slices_in_order():
+    """`symmetric_empty` is a bump allocator over the registered arena: 256-byte aligned slices in call order (so that every
+    rank, carving the same shapes, gets the same offsets), an error when the arena is full, everything free again after
+    `symmetric_reset`. Checked on a plain CPU byte buffer standing in for the arena."""
+    from sys1_b200 import tensor_parallel
+    tp = tensor_parallel.TensorParallel.__new__(tensor_parallel.TensorParallel)
+    tp.rank, tp.size = 0, 2
+    with pytest.raises(RuntimeError):
+        tp.symmetric_empty((4, 4))   # no arena yet
+    tp._arena, tp._arena_at = torch.zeros(4096, dtype=torch.uint8), 0
+    a = tp.symmetric_empty((3, 5))                      # 30 bytes -> next slice starts 256 further
+    b = tp.symmetric_empty((100,), dtype=torch.float32)  # 400 bytes -> 512
+    c = tp.symmetric_empty((8, 16))
+    base = tp._arena.data_ptr()
+    assert (a.data_ptr() - base, b.data_ptr() - base, c.data_ptr() - base) == (0, 256, 768)
+    assert a.dtype == torch.bfloat16 and tuple(a.shape) == (3, 5) and b.dtype == torch.float32 and a.is_contiguous()
+    a.fill_(1.0)
+    b.fill_(2.0)
+    assert float(a.float().sum()) == 15.0 and float(b.sum()) == 200.0   # the slices do not overlap
+    with pytest.raises(RuntimeError):
+        tp.symmetric_empty((4096,))
+    tp.symmetric_reset()
+    assert tp.symmetric_empty((2, 2)).data_ptr() == base
