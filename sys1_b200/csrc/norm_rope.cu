@@ -253,8 +253,27 @@ __global__ void __launch_bounds__(256) s1_head_norm_rope_kernel(__nv_bfloat16* _
     const long long t = live ? row / heads : 0;
     const int h = live ? static_cast<int>(row % heads) : 0;
     __nv_bfloat16* ptr = x + t * ldx + h * head_stride + sub * 8;
+    // Everything the row needs is requested before anything is computed: the token's position first (the table rows hang on
+    // it), the row itself, then the cosine / sine entries of the lanes that rotate - the norm's reduction runs while they
+    // are on their way, instead of three dependent round trips to memory one after the other.
+    const int halfc = rot / 16;
+    const bool rotates = live && sub < 2 * halfc;
+    int pos = rotates ? __ldg(positions + t) : 0;
+    const uint4 raw = live ? *reinterpret_cast<const uint4*>(ptr) : make_uint4(0, 0, 0, 0);
+    const bool pos_ok = pos >= 0 && pos < max_pos;
+    float c[8], sn[8];
+    if (rotates && pos_ok) {
+        const long long tb = static_cast<long long>(pos) * (rot / 2) + (sub % halfc) * 8;
+        *reinterpret_cast<float4*>(c) = __ldg(reinterpret_cast<const float4*>(cos_t + tb));
+        *reinterpret_cast<float4*>(c + 4) = __ldg(reinterpret_cast<const float4*>(cos_t + tb) + 1);
+        *reinterpret_cast<float4*>(sn) = __ldg(reinterpret_cast<const float4*>(sin_t + tb));
+        *reinterpret_cast<float4*>(sn + 4) = __ldg(reinterpret_cast<const float4*>(sin_t + tb) + 1);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) c[e] = 1.f, sn[e] = 0.f;
+    }
     float f[8];
-    unpack8(live ? *reinterpret_cast<const uint4*>(ptr) : make_uint4(0, 0, 0, 0), f);
+    unpack8(raw, f);
     float sq = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) sq += f[e] * f[e];
@@ -270,30 +289,23 @@ __global__ void __launch_bounds__(256) s1_head_norm_rope_kernel(__nv_bfloat16* _
         unpack8(normed, f);  // the bf16 values the rotation starts from
     }
     // the partner half of the rotated span sits rot / 16 lanes away (every lane takes part in the exchange)
-    const int halfc = rot / 16;
     uint4 other_raw;
     other_raw.x = __shfl_xor_sync(0xffffffffu, normed.x, halfc);
     other_raw.y = __shfl_xor_sync(0xffffffffu, normed.y, halfc);
     other_raw.z = __shfl_xor_sync(0xffffffffu, normed.z, halfc);
     other_raw.w = __shfl_xor_sync(0xffffffffu, normed.w, halfc);
     if (!live) return;
-    if (sub < 2 * halfc) {
-        int pos = positions[t];
-        if (pos < 0 || pos >= max_pos) {
+    if (rotates) {
+        if (!pos_ok) {
             if (atomicCAS(status, 0, 102) == 0) {
                 status[1] = static_cast<int>(blockIdx.x);
                 status[2] = static_cast<int>(t);
                 status[3] = pos;
             }
         } else {
-            float o[8], c[8], sn[8];
+            float o[8];
             unpack8(other_raw, o);
             const bool is_lo = sub < halfc;
-            const long long tb = static_cast<long long>(pos) * (rot / 2) + (sub % halfc) * 8;
-            *reinterpret_cast<float4*>(c) = __ldg(reinterpret_cast<const float4*>(cos_t + tb));
-            *reinterpret_cast<float4*>(c + 4) = __ldg(reinterpret_cast<const float4*>(cos_t + tb) + 1);
-            *reinterpret_cast<float4*>(sn) = __ldg(reinterpret_cast<const float4*>(sin_t + tb));
-            *reinterpret_cast<float4*>(sn + 4) = __ldg(reinterpret_cast<const float4*>(sin_t + tb) + 1);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float own_c = __fmul_rn(f[e], c[e]);
