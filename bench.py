@@ -18,7 +18,10 @@ Work counted per step: 2 * T * sum(K * N) flops (epilogue flops not counted).
   encoder    ModernBERT-large-shaped encoder forward over a packed 32768-token batch, tokens/s, with its own e2e
   decoder    Qwen3.5-small-shaped hybrid decoder forward over a packed 16384-token batch, tokens/s
   tp         a (linear, linear, linear, full) layer group of the 27B-shaped hybrid model over a packed 65536-token batch,
-             tensor-parallel over the ranks (one rank: unsharded), with the exchange timed alone and a parity field
+             tensor-parallel over the ranks (one rank: unsharded), with the exchange timed alone and a parity field; the
+             sums over ranks run as the library's own in-switch reduction kernel on symmetric memory, with the same step
+             through ncclAllReduce timed beside it (`--exchange multimem | nccl | both`; `--timeline PATH` also writes one
+             step's kernel timeline per rank)
 Under torchrun (N > 1) the projection / encoder / decoder workloads run as independent replicas, one per GPU, with no
 collective on the data path (whole-job rate = N x work / max-over-ranks time); the tp block is the one workload whose
 ranks exchange data. `--impl reference` times the CPU oracle (the restatement of the reference's CPU path) on the host
