@@ -135,7 +135,8 @@ constexpr int kPrepSmem = 2 * kTileBytes /*Kop*/ + 2 * kTileBytes /*Qop*/ + 2 * 
                           2 * kTileBytes /*Top*/ + 128 * kAStride * 4 /*A^T*/ + 128 * 4 * 4 /*G, beta, e^G, e^(Glast-G)*/ +
                           kTRows * 128 * 4 /*solved rows*/ + 1024 + 64;
 
-constexpr int kPrepThreads = 256;  // two threads per stacked token row: each owns one half of the features / columns
+constexpr int kPrepThreads = 512;  // four threads per stacked token row: each owns a quarter of the features / columns
+constexpr int kPrepRowsPerWarp = 128 / (kPrepThreads / 32);  // rows a warp stages and converts in the row-wise phases (8)
 
 // FUSED = false: q, k (already normalised), v, g, beta given as f32 (the drop-in form of `chunked_delta_rule`).
 // FUSED = true : the steps of `delta_inputs` (src/archs/qwen35_text.rs:528-579) happen here: bf16 rows of the mixed
@@ -162,7 +163,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     S1_STAMP(0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q4 = warp & 3;             // TMEM lane quarter of this warp
-    const int fh = warp >> 2;            // which half of the features / of the chunk's columns this thread handles
+    const int fq = warp >> 2;            // which quarter of the features / of the chunk's columns this thread handles
     const int r = q4 * 32 + lane;        // stacked token row = TMEM lane
     const int half = r >> 6, i = r & 63;  // which of the two chunks, row inside it
     const int head = blockIdx.y;
@@ -194,8 +195,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     const int hk = FUSED ? head / (p.H / p.Hk) : 0;
     if constexpr (FUSED) {
 #pragma unroll 4
-        for (int u = 0; u < 8; ++u) {  // one 16-byte piece per lane: two 256-byte rows per warp instruction
-            const int row = warp * 16 + 2 * u + (lane >> 4), ri = row & 63;
+        for (int u = 0; u < kPrepRowsPerWarp / 2; ++u) {  // one 16-byte piece per lane: two 256-byte rows per warp instruction
+            const int row = warp * kPrepRowsPerWarp + 2 * u + (lane >> 4), ri = row & 63;
             const SlotInfo sr = (row >> 6) ? s1 : s0;
             const bool rv = ri < sr.len;
             const long long src = rv ? static_cast<long long>(sr.tok_start + ri) * p.ldm + hk * 128 + 8 * (lane & 15) : 0;
@@ -204,8 +205,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
         }
     } else {
 #pragma unroll 4
-        for (int u = 0; u < 16; ++u) {
-            const int row = warp * 16 + u, ri = row & 63;
+        for (int u = 0; u < kPrepRowsPerWarp; ++u) {
+            const int row = warp * kPrepRowsPerWarp + u, ri = row & 63;
             const SlotInfo sr = (row >> 6) ? s1 : s0;
             const bool rv = ri < sr.len;
             const long long base_f = rv ? (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane : 0;
@@ -249,12 +250,12 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     const float Glast = gsh[half * 64 + 63];
     const float eG = __expf(G);
     const float eGl = __expf(Glast - G);
-    if (slot_ok && i == 0 && fh == 0) p.decay[hs] = __expf(Glast);
+    if (slot_ok && i == 0 && fq == 0) p.decay[hs] = __expf(Glast);
 
     // ---- operands, one warp per row at a time (lane = 4 consecutive features), from the staged f32 rows:
     //      Q, K, beta e^G K as bf16 [token x feature] tiles; Q e^G and K e^{G_last - G} to the workspace
     //      (beta V is staged later, by the warps that are idle during the triangular solve)
-    if (fh == 0) {
+    if (fq == 0) {
         egs[r] = eG;
         egl[r] = eGl;
     }
@@ -274,33 +275,33 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
             return make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
         }
     };
-    // fused form: L2 norms of this warp's 16 q rows and 16 k rows, all 32 warp reductions interleaved
+    // fused form: L2 norms of this warp's q rows and k rows, all the warp reductions interleaved
     // (q = l2norm(q) * 128^-1/2, k = l2norm(k), 1e-6 inside the root: src/archs/qwen35_text.rs:560-565)
-    float qsc[16], ksc[16];
+    float qsc[kPrepRowsPerWarp], ksc[kPrepRowsPerWarp];
     if constexpr (FUSED) {
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            const float4 a = fetch4(stage_q, warp * 16 + u), b = fetch4(stage_k, warp * 16 + u);
+        for (int u = 0; u < kPrepRowsPerWarp; ++u) {
+            const float4 a = fetch4(stage_q, warp * kPrepRowsPerWarp + u), b = fetch4(stage_k, warp * kPrepRowsPerWarp + u);
             qsc[u] = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
             ksc[u] = b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
-            for (int u = 0; u < 16; ++u) {
+            for (int u = 0; u < kPrepRowsPerWarp; ++u) {
                 qsc[u] += __shfl_xor_sync(0xffffffffu, qsc[u], o);
                 ksc[u] += __shfl_xor_sync(0xffffffffu, ksc[u], o);
             }
         }
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
+        for (int u = 0; u < kPrepRowsPerWarp; ++u) {
             qsc[u] = 0.08838834764831845f * rsqrtf(qsc[u] + 1e-6f);
             ksc[u] = rsqrtf(ksc[u] + 1e-6f);
         }
     }
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {  // Q first: its staging area is where beta e^G K goes next
-        const int row = warp * 16 + u, ri = row & 63;
+    for (int u = 0; u < kPrepRowsPerWarp; ++u) {  // Q first: its staging area is where beta e^G K goes next
+        const int row = warp * kPrepRowsPerWarp + u, ri = row & 63;
         const int rslot = 2 * blockIdx.x + (row >> 6);
         float4 qq = fetch4(stage_q, row);
         if constexpr (FUSED) qq.x *= qsc[u], qq.y *= qsc[u], qq.z *= qsc[u], qq.w *= qsc[u];
@@ -315,8 +316,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     __syncthreads();
     S1_STAMP(5);   // Q operands written
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {
-        const int row = warp * 16 + u, ri = row & 63;
+    for (int u = 0; u < kPrepRowsPerWarp; ++u) {
+        const int row = warp * kPrepRowsPerWarp + u, ri = row & 63;
         const int rslot = 2 * blockIdx.x + (row >> 6);
         float4 kk = fetch4(stage_k, row);
         if constexpr (FUSED) kk.x *= ksc[u], kk.y *= ksc[u], kk.z *= ksc[u], kk.w *= ksc[u];
@@ -358,8 +359,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     // K and Q tiles are consumed: their 64 KB now stage the raw V rows, in flight while A and P are formed
     if constexpr (FUSED) {
 #pragma unroll 4
-        for (int u = 0; u < 8; ++u) {
-            const int row = warp * 16 + 2 * u + (lane >> 4), ri = row & 63;
+        for (int u = 0; u < kPrepRowsPerWarp / 2; ++u) {
+            const int row = warp * kPrepRowsPerWarp + 2 * u + (lane >> 4), ri = row & 63;
             const SlotInfo sr = (row >> 6) ? s1 : s0;
             const bool rv = ok && ri < sr.len;
             const long long src = rv ? static_cast<long long>(sr.tok_start + ri) * p.ldm + 2 * kw + head * 128 + 8 * (lane & 15) : 0;
@@ -367,8 +368,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
         }
     } else {
 #pragma unroll 4
-        for (int u = 0; u < 16; ++u) {
-            const int row = warp * 16 + u, ri = row & 63;
+        for (int u = 0; u < kPrepRowsPerWarp; ++u) {
+            const int row = warp * kPrepRowsPerWarp + u, ri = row & 63;
             const SlotInfo sr = (row >> 6) ? s1 : s0;
             const bool rv = ok && ri < sr.len;
             const long long base_f = rv ? (static_cast<long long>(sr.tok_start + ri) * p.H + head) * kD + 4 * lane : 0;
@@ -378,17 +379,17 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     cp_async_commit_group();
     if (ok) {
         tc_fence_after();
-        // this thread's 32 of the own chunk's 64 columns of row r
+        // this thread's 16 of the own chunk's 64 columns of row r
         {
-            const int c = fh;
-            uint32_t kk[32], qk[32];
-            tmem_ld_32x32b_x32(lane_addr + half * 64 + c * 32, kk);
-            tmem_ld_32x32b_x32(lane_addr + 128 + half * 64 + c * 32, qk);
+            const int c = fq;
+            uint32_t kk[16], qk[16];
+            tmem_ld_32x32b_x16(lane_addr + half * 64 + c * 16, kk);
+            tmem_ld_32x32b_x16(lane_addr + 128 + half * 64 + c * 16, qk);
             tmem_ld_wait();
-            uint32_t pp[16];
+            uint32_t pp[8];
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                const int j = c * 32 + e;
+            for (int e = 0; e < 16; ++e) {
+                const int j = c * 16 + e;
                 const float dec = __expf(G - gsh[half * 64 + j]);  // <= 1 wherever it is used (j <= i)
                 amat[(half * 64 + j) * kAStride + i] = (j < i) ? bi * __uint_as_float(kk[e]) * dec : 0.f;  // A^T[j][i]
                 const float pv = (j <= i) ? __uint_as_float(qk[e]) * dec : 0.f;
@@ -397,8 +398,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
             }
             if (slot_ok) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    *reinterpret_cast<uint4*>(p.p + (hs * 64 + i) * kC + c * 32 + 8 * e) =
+                for (int e = 0; e < 2; ++e)
+                    *reinterpret_cast<uint4*>(p.p + (hs * 64 + i) * kC + c * 16 + 8 * e) =
                         make_uint4(pp[4 * e], pp[4 * e + 1], pp[4 * e + 2], pp[4 * e + 3]);
             }
         }
@@ -409,16 +410,18 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     S1_STAMP(8);   // A, P formed; V rows landed
     tc_fence_after();
 
-    // ---- Tm = (I + A)^-1 by forward substitution, one column per thread (columns are independent); the other half
-    //      of the warps meanwhile fills the zero blocks of the block-diagonal operand and stages beta V
-    if (fh == 1) {
+    // ---- Tm = (I + A)^-1 by forward substitution, one column per thread (columns are independent: the warps of column
+    //      quarter 0 solve); the others meanwhile fill the zero blocks of the block-diagonal operand (quarter 1) and stage
+    //      beta V (quarters 2 and 3)
+    if (fq == 1) {
         const uint32_t ttile = top + half * kTileBytes;
 #pragma unroll
         for (int ii = 0; ii < 64; ++ii) st_shared_b16(ttile + sw128((1 - half) * 64 + ii, i), __float2bfloat16_rn(0.f));
-        // beta V rows (staged f32) -> tiles 2, 3 of the B operand: 4 warps x 32 rows
+    } else if (fq >= 2) {
+        // beta V rows (staged) -> tiles 2, 3 of the B operand: 8 warps x 16 rows
 #pragma unroll 4
-        for (int u = 0; u < 32; ++u) {
-            const int row = q4 * 32 + u;
+        for (int u = 0; u < 16; ++u) {
+            const int row = (warp - 8) * 16 + u;
             const float4 vv = fetch4(stage_v, row);
             const float be = bsh[row];
             st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(vv.x * be, vv.y * be), pack2(vv.z * be, vv.w * be));
@@ -497,8 +500,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int c = 2 * fh; c < 2 * fh + 2; ++c) {  // W row: this thread's 64 of the 128 key features
+        {  // W row: this thread's 32 of the 128 key features
+            const int c = fq;
             uint32_t w[32];
             tmem_ld_32x32b_x32(lane_addr + c * 32, w);
             tmem_ld_wait();
@@ -510,8 +513,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
                         pack2(__uint_as_float(w[8 * e + 4]), __uint_as_float(w[8 * e + 5])), pack2(__uint_as_float(w[8 * e + 6]), __uint_as_float(w[8 * e + 7])));
             }
         }
-#pragma unroll
-        for (int c = 2 * fh; c < 2 * fh + 2; ++c) {  // U row -> transposed: ut[dv][token]
+        {  // U row -> transposed: ut[dv][token]; this thread's 32 of the 128 value columns
+            const int c = fq;
             uint32_t u[32];
             tmem_ld_32x32b_x32(lane_addr + 128 + c * 32, u);
             tmem_ld_wait();
