@@ -191,6 +191,11 @@ int s1_delta_rule_chunked(s1_ctx* ctx, const float* q, const float* k, const flo
  *                   Its recurrence is the chunk form (bf16 operands, f32 state): within 2e-2 of the output scale of the
  *                   exact f32 recurrence, not within the reference's 1e-4; s1_delta_inputs -> s1_delta_rule ->
  *                   s1_delta_finish is the same path at the reference's own precision.
+ *  s1_gated_delta_rule_conv  s1_conv_silu (4 taps) and s1_gated_delta_rule as one call: `mixed_before_conv` is the
+ *                   projection the conv would read, `conv_weight` [2 * key_heads * 128 + value_heads * 128, 4] bf16
+ *                   (16-byte aligned), `positions` as for s1_conv_silu. The recurrence's first kernel applies conv + SiLU to
+ *                   the rows it stages (with three rows of history per 64-token chunk), so the conv's pass over the
+ *                   [T, channels] tensor and back is never made; the result is bit-identical to the two calls.
  */
 int s1_conv_silu(s1_ctx* ctx, const void* x, long long ldx, const void* weight, const int32_t* positions, int total_tokens,
                  int channels, int taps, void* y, long long ldy);
@@ -204,6 +209,11 @@ int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const voi
                         const float* dt_bias, const float* neg_exp_a, const void* z, long long ldz, const void* norm_weight,
                         float eps, const int32_t* cu_seqlens_host, int num_seqs, int total_tokens, int key_heads,
                         int value_heads, void* y, long long ldy, void* workspace, size_t workspace_bytes);
+int s1_gated_delta_rule_conv(s1_ctx* ctx, const void* mixed_before_conv, long long ldm, const void* conv_weight,
+                             const int32_t* positions, const void* b_proj, const void* a_proj, long long ldba, const float* dt_bias,
+                             const float* neg_exp_a, const void* z, long long ldz, const void* norm_weight, float eps,
+                             const int32_t* cu_seqlens_host, int num_seqs, int total_tokens, int key_heads, int value_heads, void* y,
+                             long long ldy, void* workspace, size_t workspace_bytes);
 
 /*
  * Batch plan: the tables the attention and delta-rule kernels walk - the 128-query blocks of every sequence in the order

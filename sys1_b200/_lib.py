@@ -66,6 +66,10 @@ SIGNATURES = {
     "s1_gated_delta_rule": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_float, C.POINTER(C.c_int32),
                                       C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_size_t]),
+    "s1_gated_delta_rule_conv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                           C.c_longlong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_float,
+                                           C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong,
+                                           C.c_void_p, C.c_size_t]),
     "s1_batch_plan_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "s1_batch_plan": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_void_p, C.c_size_t]),
     "s1_use_batch_plan": (C.c_int, [C.c_void_p, C.c_void_p]),

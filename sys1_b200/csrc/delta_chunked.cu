@@ -89,6 +89,13 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&t);
 }
+// x / (1 + e^-x) on the special-function unit: the same two instructions as s1_conv_silu's, so both give the same bits.
+__device__ __forceinline__ float silu_sfu(float v) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+    return v * r;
+}
 
 #ifdef S1_MEASURE
 // Timing aid of measurement builds only: SM clock stamps of one CTA's phases (read back with s1_measure_read_stamps).
@@ -124,6 +131,10 @@ struct PrepParams {
     const float* dt_bias;        // [H]
     const float* neg_exp_a;      // [H]
     int Hk;                      // key heads (H value heads; key head = value head / (H / Hk))
+    // conv form (s1_gated_delta_rule_conv): `mixed` is the projection BEFORE the causal conv + SiLU; the kernel applies them
+    // to the rows it stages (src/kernels/qwen35.cu:3-29; 4 taps, same arithmetic as s1_conv_silu)
+    const __nv_bfloat16* conv_w;   // [2 * Hk * 128 + H * 128, 4]
+    const int32_t* positions;      // [T] index of every token inside its sequence
 };
 
 // The f32 matrix A of each chunk is kept transposed in shared memory, AT[j][i] = A[i][j] (64 floats per row): the thread
@@ -141,8 +152,12 @@ constexpr int kPrepRowsPerWarp = 128 / (kPrepThreads / 32);  // rows a warp stag
 // FUSED = false: q, k (already normalised), v, g, beta given as f32 (the drop-in form of `chunked_delta_rule`).
 // FUSED = true : the steps of `delta_inputs` (src/archs/qwen35_text.rs:528-579) happen here: bf16 rows of the mixed
 //                projection are staged, L2-normalised per row by the warp that converts them, gates from a / b.
-template <bool FUSED>
+//                CONV (with FUSED): the staged rows are the projection before the depthwise causal conv; every row's conv +
+//                SiLU is formed on the way from the staging area to the operands (three rows of history per chunk are
+//                staged with it), so the conv kernel's pass over the [T, channels] tensor and back disappears.
+template <bool FUSED, bool CONV = false>
 __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const PrepParams p) {
+    static_assert(FUSED || !CONV, "the conv form reads the layer's bf16 projection");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* al = smem_raw + (base - smem_u32(smem_raw));
@@ -190,6 +205,11 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     const SlotInfo s0 = p.slots[min(2 * static_cast<int>(blockIdx.x), p.num_slots - 1)];
     const SlotInfo s1 = (2 * blockIdx.x + 1 < p.num_slots) ? p.slots[2 * blockIdx.x + 1] : SlotInfo{0, 0};
     const uint32_t stage_q = xt, stage_k = top, stage_v = kop;
+    // conv form: history rows of q, k in the (not yet used) solved-rows buffer, those of v over the Q tiles once they are
+    // consumed; the rows after conv + SiLU of q in the upper half of xt, of k where A^T goes later
+    const uint32_t halo_qk = smem_u32(tbuf), halo_v = qop;
+    const uint32_t post_q = xt + 2 * kTileBytes, post_k = smem_u32(amat);
+    int pos0[2] = {0, 0};
     constexpr int kRowBytes = FUSED ? 256 : 512;  // staged row: 128 bf16 or 128 f32
     const int kw = FUSED ? p.Hk * 128 : 0;
     const int hk = FUSED ? head / (p.H / p.Hk) : 0;
@@ -202,6 +222,20 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
             const long long src = rv ? static_cast<long long>(sr.tok_start + ri) * p.ldm + hk * 128 + 8 * (lane & 15) : 0;
             cp_async16_zfill(stage_q + row * 256 + (lane & 15) * 16, p.mixed + src, rv ? 16u : 0u);
             cp_async16_zfill(stage_k + row * 256 + (lane & 15) * 16, p.mixed + src + (rv ? kw : 0), rv ? 16u : 0u);
+        }
+        if constexpr (CONV) {
+            // the three rows before each chunk's first token (zero where the sequence starts later): q rows of chunk 0, 1,
+            // then k rows of chunk 0, 1; two rows per warp instruction, six instructions
+            pos0[0] = s0.len > 0 ? __ldg(p.positions + s0.tok_start) : 0;
+            pos0[1] = s1.len > 0 ? __ldg(p.positions + s1.tok_start) : 0;
+            if (warp < 6) {
+                const int r12 = 2 * warp + (lane >> 4);
+                const int which = r12 / 6, hh = (r12 % 6) / 3, back = 3 - r12 % 3;
+                const SlotInfo sr = hh ? s1 : s0;
+                const bool rv = sr.len > 0 && pos0[hh] >= back;
+                const long long src = rv ? static_cast<long long>(sr.tok_start - back) * p.ldm + hk * 128 + which * kw + 8 * (lane & 15) : 0;
+                cp_async16_zfill(halo_qk + r12 * 256 + (lane & 15) * 16, p.mixed + src, rv ? 16u : 0u);
+            }
         }
     } else {
 #pragma unroll 4
@@ -275,13 +309,70 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
             return make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
         }
     };
+    // conv form: this lane's four channels' taps of one tensor as bf16x2 pairs of neighbouring channels, and the conv +
+    // SiLU of eight consecutive rows of a chunk from the staged rows (or the history rows, for the chunk's first three):
+    // the arithmetic of s1_conv_silu, tap by tap in bf16 (`__hmul2_rn` / `__hadd2_rn`, never contracted), SiLU in f32
+    auto conv_taps = [&](int channel, uint32_t (&wt)[4][2]) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p.conv_w + static_cast<long long>(channel) * 4));
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.conv_w + static_cast<long long>(channel) * 4) + 1);
+        wt[0][0] = __byte_perm(a.x, a.z, 0x5410), wt[1][0] = __byte_perm(a.x, a.z, 0x7632);
+        wt[2][0] = __byte_perm(a.y, a.w, 0x5410), wt[3][0] = __byte_perm(a.y, a.w, 0x7632);
+        wt[0][1] = __byte_perm(b.x, b.z, 0x5410), wt[1][1] = __byte_perm(b.x, b.z, 0x7632);
+        wt[2][1] = __byte_perm(b.y, b.w, 0x5410), wt[3][1] = __byte_perm(b.y, b.w, 0x7632);
+    };
+    auto ld2 = [&](uint32_t addr) -> uint2 {
+        uint2 v;
+        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+        return v;
+    };
+    // rows row0 .. row0 + 7 of the stacked pair (all in one chunk, whose history rows sit at `halo`); rows at or past `len`
+    // come out as zero, like rows that were never staged
+    auto conv8 = [&](uint32_t stage, uint32_t halo, int row0, int len, const uint32_t (&wt)[4][2], uint2 (&out)[8]) {
+        const int ri0 = row0 & 63;
+        uint2 x[11];
+#pragma unroll
+        for (int t = 0; t < 11; ++t) {
+            const int idx = ri0 - 3 + t;
+            x[t] = (idx >= 0) ? ld2(stage + (row0 - 3 + t) * 256 + lane * 8) : ld2(halo + (idx + 3) * 256 + lane * 8);
+        }
+        const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            __nv_bfloat162 a0 = zero2, a1 = zero2;
+#pragma unroll
+            for (int tap = 0; tap < 4; ++tap) {
+                a0 = __hadd2_rn(a0, __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&x[u + tap].x), *reinterpret_cast<const __nv_bfloat162*>(&wt[tap][0])));
+                a1 = __hadd2_rn(a1, __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&x[u + tap].y), *reinterpret_cast<const __nv_bfloat162*>(&wt[tap][1])));
+            }
+            const float2 f0 = __bfloat1622float2(a0), f1 = __bfloat1622float2(a1);
+            const bool live = ri0 + u < len;
+            out[u].x = live ? pack2(silu_sfu(f0.x), silu_sfu(f0.y)) : 0u;
+            out[u].y = live ? pack2(silu_sfu(f1.x), silu_sfu(f1.y)) : 0u;
+        }
+    };
+    const uint32_t src_q = CONV ? post_q : stage_q, src_k = CONV ? post_k : stage_k;
+    if constexpr (CONV) {
+        const int row0 = warp * kPrepRowsPerWarp, hh = row0 >> 6;
+        const int len = hh ? s1.len : s0.len;
+        uint32_t wt[4][2];
+        uint2 o8[8];
+        conv_taps(hk * 128 + 4 * lane, wt);
+        conv8(stage_q, halo_qk + hh * 768, row0, len, wt, o8);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) st_shared_v2(post_q + (row0 + u) * 256 + lane * 8, o8[u].x, o8[u].y);
+        conv_taps(kw + hk * 128 + 4 * lane, wt);
+        conv8(stage_k, halo_qk + 1536 + hh * 768, row0, len, wt, o8);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) st_shared_v2(post_k + (row0 + u) * 256 + lane * 8, o8[u].x, o8[u].y);
+        // (every lane reads back only what it wrote itself: no barrier is needed before the loops below)
+    }
     // fused form: L2 norms of this warp's q rows and k rows, all the warp reductions interleaved
     // (q = l2norm(q) * 128^-1/2, k = l2norm(k), 1e-6 inside the root: src/archs/qwen35_text.rs:560-565)
     float qsc[kPrepRowsPerWarp], ksc[kPrepRowsPerWarp];
     if constexpr (FUSED) {
 #pragma unroll
         for (int u = 0; u < kPrepRowsPerWarp; ++u) {
-            const float4 a = fetch4(stage_q, warp * kPrepRowsPerWarp + u), b = fetch4(stage_k, warp * kPrepRowsPerWarp + u);
+            const float4 a = fetch4(src_q, warp * kPrepRowsPerWarp + u), b = fetch4(src_k, warp * kPrepRowsPerWarp + u);
             qsc[u] = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
             ksc[u] = b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
         }
@@ -303,7 +394,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     for (int u = 0; u < kPrepRowsPerWarp; ++u) {  // Q first: its staging area is where beta e^G K goes next
         const int row = warp * kPrepRowsPerWarp + u, ri = row & 63;
         const int rslot = 2 * blockIdx.x + (row >> 6);
-        float4 qq = fetch4(stage_q, row);
+        float4 qq = fetch4(src_q, row);
         if constexpr (FUSED) qq.x *= qsc[u], qq.y *= qsc[u], qq.z *= qsc[u], qq.w *= qsc[u];
         const float eg = egs[row];
         st_shared_v2(qop + tile * kTileBytes + sw128(row, col), pack2(qq.x, qq.y), pack2(qq.z, qq.w));
@@ -319,7 +410,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
     for (int u = 0; u < kPrepRowsPerWarp; ++u) {
         const int row = warp * kPrepRowsPerWarp + u, ri = row & 63;
         const int rslot = 2 * blockIdx.x + (row >> 6);
-        float4 kk = fetch4(stage_k, row);
+        float4 kk = fetch4(src_k, row);
         if constexpr (FUSED) kk.x *= ksc[u], kk.y *= ksc[u], kk.z *= ksc[u], kk.w *= ksc[u];
         const float el = egl[row], sk = bsh[row] * egs[row];
         const uint32_t off = tile * kTileBytes + sw128(row, col);
@@ -365,6 +456,16 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
             const bool rv = ok && ri < sr.len;
             const long long src = rv ? static_cast<long long>(sr.tok_start + ri) * p.ldm + 2 * kw + head * 128 + 8 * (lane & 15) : 0;
             cp_async16_zfill(stage_v + row * 256 + (lane & 15) * 16, p.mixed + src, rv ? 16u : 0u);
+        }
+        if constexpr (CONV) {
+            if (warp < 3) {  // the three v rows before each chunk's first token, over the consumed Q tiles
+                const int r6 = 2 * warp + (lane >> 4);
+                const int hh = r6 / 3, back = 3 - r6 % 3;
+                const SlotInfo sr = hh ? s1 : s0;
+                const bool rv = ok && sr.len > 0 && pos0[hh] >= back;
+                const long long src = rv ? static_cast<long long>(sr.tok_start - back) * p.ldm + 2 * kw + head * 128 + 8 * (lane & 15) : 0;
+                cp_async16_zfill(halo_v + r6 * 256 + (lane & 15) * 16, p.mixed + src, rv ? 16u : 0u);
+            }
         }
     } else {
 #pragma unroll 4
@@ -419,12 +520,31 @@ __global__ void __launch_bounds__(kPrepThreads, 1) s1_delta_prep_kernel(const Pr
         for (int ii = 0; ii < 64; ++ii) st_shared_b16(ttile + sw128((1 - half) * 64 + ii, i), __float2bfloat16_rn(0.f));
     } else if (fq >= 2) {
         // beta V rows (staged) -> tiles 2, 3 of the B operand: 8 warps x 16 rows
+        if constexpr (CONV) {
+            uint32_t wt[4][2];
+            conv_taps(2 * kw + head * 128 + 4 * lane, wt);
+#pragma unroll 1
+            for (int part = 0; part < 2; ++part) {
+                const int row0 = (warp - 8) * 16 + 8 * part, hh = row0 >> 6;
+                uint2 o8[8];
+                conv8(stage_v, halo_v + hh * 768, row0, hh ? s1.len : s0.len, wt, o8);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int row = row0 + u;
+                    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&o8[u].x), hi = *reinterpret_cast<const __nv_bfloat162*>(&o8[u].y);
+                    const float be = bsh[row];
+                    st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(__low2float(lo) * be, __high2float(lo) * be),
+                                 pack2(__low2float(hi) * be, __high2float(hi) * be));
+                }
+            }
+        } else {
 #pragma unroll 4
-        for (int u = 0; u < 16; ++u) {
-            const int row = (warp - 8) * 16 + u;
-            const float4 vv = fetch4(stage_v, row);
-            const float be = bsh[row];
-            st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(vv.x * be, vv.y * be), pack2(vv.z * be, vv.w * be));
+            for (int u = 0; u < 16; ++u) {
+                const int row = (warp - 8) * 16 + u;
+                const float4 vv = fetch4(stage_v, row);
+                const float be = bsh[row];
+                st_shared_v2(xt + (2 + tile) * kTileBytes + sw128(row, col), pack2(vv.x * be, vv.y * be), pack2(vv.z * be, vv.w * be));
+            }
         }
     } else {
         // Column i of Tm = (I + A)^-1: t[ii] = [ii == i] - sum_{j < ii} A[ii][j] t[j], in blocks of 16 rows. A block first
@@ -859,11 +979,13 @@ static int run_chunked(s1_ctx* ctx, const char* who, PrepParams pp, bool fused, 
     if (configured_device != ctx->device) {
         S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_prep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem));
         S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_prep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem));
+        S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_prep_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem));
         S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanSmem));
         configured_device = ctx->device;
     }
     const dim3 pgrid((num_slots + 1) / 2, heads);
-    if (fused) s1_delta_prep_kernel<true><<<pgrid, kPrepThreads, kPrepSmem, ctx->stream>>>(pp);
+    if (fused && pp.conv_w) s1_delta_prep_kernel<true, true><<<pgrid, kPrepThreads, kPrepSmem, ctx->stream>>>(pp);
+    else if (fused) s1_delta_prep_kernel<true><<<pgrid, kPrepThreads, kPrepSmem, ctx->stream>>>(pp);
     else s1_delta_prep_kernel<false><<<pgrid, kPrepThreads, kPrepSmem, ctx->stream>>>(pp);
     S1_CUDA_OK(ctx, cudaGetLastError());
     ctx->launches += 1;
@@ -918,35 +1040,61 @@ extern "C" size_t s1_gated_delta_rule_workspace(int num_seqs, int total_tokens, 
            s1_delta_rule_chunked_workspace(num_seqs, total_tokens, value_heads);
 }
 
-extern "C" int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const void* b_proj, const void* a_proj,
-                                   long long ldba, const float* dt_bias, const float* neg_exp_a, const void* z, long long ldz,
-                                   const void* norm_weight, float eps, const int32_t* cu_seqlens_host, int num_seqs,
-                                   int total_tokens, int key_heads, int value_heads, void* y, long long ldy, void* workspace,
-                                   size_t workspace_bytes) {
+// Shared body of s1_gated_delta_rule (conv_weight = NULL: `mixed` is the conv output) and s1_gated_delta_rule_conv.
+static int gated_delta_rule(s1_ctx* ctx, const char* who, const void* mixed, long long ldm, const void* conv_weight,
+                            const int32_t* positions, const void* b_proj, const void* a_proj, long long ldba, const float* dt_bias,
+                            const float* neg_exp_a, const void* z, long long ldz, const void* norm_weight, float eps,
+                            const int32_t* cu_seqlens_host, int num_seqs, int total_tokens, int key_heads, int value_heads, void* y,
+                            long long ldy, void* workspace, size_t workspace_bytes) {
     if (!ctx) return S1_EINVAL;
     if (!mixed || !b_proj || !a_proj || !dt_bias || !neg_exp_a || !z || !norm_weight || !y || !workspace)
-        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: null pointer");
+        return s1_fail(ctx, S1_EINVAL, "%s: null pointer", who);
     if (key_heads < 1 || value_heads < key_heads || value_heads % key_heads)
-        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: value_heads must be a multiple of key_heads");
+        return s1_fail(ctx, S1_EINVAL, "%s: value_heads must be a multiple of key_heads", who);
     const long long width = 2LL * key_heads * 128 + 1LL * value_heads * 128;
     if (ldm < width || (ldm % 8) || ldba < value_heads || (reinterpret_cast<uintptr_t>(mixed) & 15u))
-        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: mixed needs %lld columns per row and 16-byte aligned rows", width);
+        return s1_fail(ctx, S1_EINVAL, "%s: mixed needs %lld columns per row and 16-byte aligned rows", who, width);
+    if (conv_weight && (reinterpret_cast<uintptr_t>(conv_weight) & 15u))
+        return s1_fail(ctx, S1_EINVAL, "%s: the conv weight must be 16-byte aligned", who);
     if (reinterpret_cast<uintptr_t>(workspace) & 1023u)
-        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: the workspace must be 1024-byte aligned device memory");
+        return s1_fail(ctx, S1_EINVAL, "%s: the workspace must be 1024-byte aligned device memory", who);
     if (workspace_bytes < s1_gated_delta_rule_workspace(num_seqs, total_tokens, value_heads))
-        return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule: workspace of %zu bytes, %zu needed", workspace_bytes,
+        return s1_fail(ctx, S1_EINVAL, "%s: workspace of %zu bytes, %zu needed", who, workspace_bytes,
                        s1_gated_delta_rule_workspace(num_seqs, total_tokens, value_heads));
     if (total_tokens == 0) return S1_OK;
     const size_t obytes = align_up(static_cast<size_t>(total_tokens) * value_heads * 128 * 4, 1024);
     float* o = static_cast<float*>(workspace);
     PrepParams pp = {};
     pp.mixed = static_cast<const __nv_bfloat16*>(mixed), pp.ldm = ldm;
+    pp.conv_w = static_cast<const __nv_bfloat16*>(conv_weight), pp.positions = positions;
     pp.bproj = static_cast<const __nv_bfloat16*>(b_proj), pp.aproj = static_cast<const __nv_bfloat16*>(a_proj), pp.ldba = ldba;
     pp.dt_bias = dt_bias, pp.neg_exp_a = neg_exp_a, pp.Hk = key_heads;
-    int rc = run_chunked(ctx, "s1_gated_delta_rule", pp, true, cu_seqlens_host, num_seqs, total_tokens, value_heads, o,
+    int rc = run_chunked(ctx, who, pp, true, cu_seqlens_host, num_seqs, total_tokens, value_heads, o,
                          static_cast<uint8_t*>(workspace) + obytes, workspace_bytes - obytes);
     if (rc) return rc;
     return s1_delta_finish(ctx, o, z, ldz, norm_weight, eps, total_tokens, value_heads, y, ldy);
+}
+
+extern "C" int s1_gated_delta_rule(s1_ctx* ctx, const void* mixed, long long ldm, const void* b_proj, const void* a_proj,
+                                   long long ldba, const float* dt_bias, const float* neg_exp_a, const void* z, long long ldz,
+                                   const void* norm_weight, float eps, const int32_t* cu_seqlens_host, int num_seqs,
+                                   int total_tokens, int key_heads, int value_heads, void* y, long long ldy, void* workspace,
+                                   size_t workspace_bytes) {
+    return gated_delta_rule(ctx, "s1_gated_delta_rule", mixed, ldm, nullptr, nullptr, b_proj, a_proj, ldba, dt_bias, neg_exp_a, z, ldz,
+                            norm_weight, eps, cu_seqlens_host, num_seqs, total_tokens, key_heads, value_heads, y, ldy, workspace,
+                            workspace_bytes);
+}
+
+extern "C" int s1_gated_delta_rule_conv(s1_ctx* ctx, const void* mixed_before_conv, long long ldm, const void* conv_weight,
+                                        const int32_t* positions, const void* b_proj, const void* a_proj, long long ldba,
+                                        const float* dt_bias, const float* neg_exp_a, const void* z, long long ldz,
+                                        const void* norm_weight, float eps, const int32_t* cu_seqlens_host, int num_seqs,
+                                        int total_tokens, int key_heads, int value_heads, void* y, long long ldy, void* workspace,
+                                        size_t workspace_bytes) {
+    if (ctx && (!conv_weight || !positions)) return s1_fail(ctx, S1_EINVAL, "s1_gated_delta_rule_conv: null pointer");
+    return gated_delta_rule(ctx, "s1_gated_delta_rule_conv", mixed_before_conv, ldm, conv_weight, positions, b_proj, a_proj, ldba, dt_bias,
+                            neg_exp_a, z, ldz, norm_weight, eps, cu_seqlens_host, num_seqs, total_tokens, key_heads, value_heads, y, ldy,
+                            workspace, workspace_bytes);
 }
 
 #ifdef S1_MEASURE

@@ -139,11 +139,14 @@ class LinearAttention:
 
     def __init__(self, qkv: Linear, z: Linear, b: Linear, a: Linear, conv: torch.Tensor, decay: torch.Tensor,
                  dt_bias: torch.Tensor, norm: torch.Tensor, output: Linear, key_heads: int, value_heads: int, eps: float,
-                 merge_inputs: bool = True, recurrence: str = "chunked"):
+                 merge_inputs: bool = True, recurrence: str = "chunked", fuse_conv: bool = True):
         """`recurrence`: "chunked" (default) evaluates the gated delta rule in 64-token chunks on the tensor cores with
         bf16 operands and f32 state (`s1_gated_delta_rule`; within 2e-2 of the output scale of the f32 recurrence, which
         is the layer-level bound of this path); "exact" runs the token-sequential f32 kernel (`s1_delta_rule`, the
         reference's own arithmetic and its 1e-4 bound), about three times slower.
+        `fuse_conv` (chunked recurrence, 4 taps): the causal conv + SiLU is applied by the recurrence's first kernel to the rows
+        it stages (`s1_gated_delta_rule_conv`) instead of by a kernel of its own that writes the `[T, channels]` tensor out and
+        the next one reads back; bit-identical to the two calls.
         `merge_inputs`: stack the four input projections, which share their input, into one weight `[N_qkv + N_z + 2 Hv,
         K]` at load time, so that they run as one contraction (two of them are only `Hv` = 16 or 48 columns wide, a
         launch each for next to no work); the outputs are column views of one buffer."""
@@ -153,6 +156,8 @@ class LinearAttention:
         if recurrence not in ("chunked", "exact"):
             raise ValueError("recurrence must be 'chunked' or 'exact'")
         self.recurrence = recurrence
+        self.conv_taps = conv.reshape(conv.shape[0], -1).contiguous()   # [C, taps]
+        self.fuse_conv = bool(fuse_conv) and recurrence == "chunked" and self.conv_taps.shape[1] == 4
         self.merged = None
         if merge_inputs and all(l.bias is None for l in (qkv, z, b, a)):
             # b and a are only `value_heads` rows each (6 on a tensor-parallel rank of the large model): padded with zero
@@ -188,20 +193,25 @@ class LinearAttention:
         T = x.shape[0]
         cu = np.ascontiguousarray(cu_seqlens_host, dtype=np.int32)
         pre, zz, bb, aa = self._inputs(x)
-        mixed = conv_silu(pre, self.conv, positions, ctx)                         # project_and_mix (:515-526)
         y = torch.empty((T, self.value_heads * 128), dtype=torch.bfloat16, device=x.device)
+        P = lambda t: C.c_void_p(t.data_ptr())
         if self.recurrence == "exact":
+            mixed = conv_silu(pre, self.conv, positions, ctx)                     # project_and_mix (:515-526)
             self._exact(ctx, mixed, zz, bb, aa, cu, y)
+            return y
+        need = int(ctx._lib.s1_gated_delta_rule_workspace(len(cu) - 1, T, self.value_heads))
+        ptr = ctx.workspace(need).data_ptr()
+        planned = ctx.plan_covers(len(cu) - 1, T)
+        offsets = None if planned else cu.ctypes.data_as(C.POINTER(C.c_int32))
+        tail = (P(bb), P(aa), bb.stride(0), P(self.dt_bias), P(self.decay), P(zz), zz.stride(0), P(self.norm), C.c_float(self.eps), offsets,
+                len(cu) - 1, T, self.key_heads, self.value_heads, P(y), y.stride(0), C.c_void_p(ptr), need)
+        if self.fuse_conv:
+            pos = positions if positions.dtype == torch.int32 and positions.is_contiguous() else positions.to(torch.int32).contiguous()
+            rc = ctx._lib.s1_gated_delta_rule_conv(ctx.handle, P(pre), pre.stride(0), P(self.conv_taps), P(pos), *tail)
         else:
-            need = int(ctx._lib.s1_gated_delta_rule_workspace(len(cu) - 1, T, self.value_heads))
-            ptr = ctx.workspace(need).data_ptr()
-            planned = ctx.plan_covers(len(cu) - 1, T)
-            rc = ctx._lib.s1_gated_delta_rule(
-                ctx.handle, C.c_void_p(mixed.data_ptr()), mixed.stride(0), C.c_void_p(bb.data_ptr()), C.c_void_p(aa.data_ptr()),
-                bb.stride(0), C.c_void_p(self.dt_bias.data_ptr()), C.c_void_p(self.decay.data_ptr()), C.c_void_p(zz.data_ptr()),
-                zz.stride(0), C.c_void_p(self.norm.data_ptr()), C.c_float(self.eps), None if planned else cu.ctypes.data_as(C.POINTER(C.c_int32)),
-                len(cu) - 1, T, self.key_heads, self.value_heads, C.c_void_p(y.data_ptr()), y.stride(0), C.c_void_p(ptr), need)
-            ctx.check(rc)
+            mixed = conv_silu(pre, self.conv, positions, ctx)                     # project_and_mix (:515-526)
+            rc = ctx._lib.s1_gated_delta_rule(ctx.handle, P(mixed), mixed.stride(0), *tail)
+        ctx.check(rc)
         return y
 
     def _exact(self, ctx, mixed, zz, bb, aa, cu, y) -> None:

@@ -108,3 +108,26 @@ def test_linear_attention_layer_on_a_packed_batch(ctx):
         want[a:z] = oracle.linear(y, P["out"], residual=xs)
     assert torch.isfinite(got).all()
     assert max_rel(got, want) <= 2e-2
+
+
+@pytest.mark.parametrize("lens,Hk,Hv", [([70, 9, 130], 4, 8), ([1, 2, 3, 64, 65, 127, 128, 129, 5], 2, 2), ([700, 61], 2, 6)])
+def test_conv_inside_the_recurrence_is_bit_identical_to_the_two_calls(ctx, lens, Hk, Hv):
+    """`s1_gated_delta_rule_conv` applies the causal conv + SiLU to the rows its first kernel stages, with three rows of
+    history per 64-token chunk; `s1_conv_silu` followed by `s1_gated_delta_rule` is the same arithmetic in two passes.
+    Sequences shorter than the history, ending on and next to chunk boundaries, and key heads shared by several value heads."""
+    P = _layer(21 + Hv, hidden=128, Hk=Hk, Hv=Hv)
+    b, _ = batching.pack_next(lens, batching.BatcherConfig(token_budget=2048))
+    g = torch.Generator().manual_seed(22)
+    x = torch.randn(b.total_tokens, P["hidden"], generator=g).to(torch.bfloat16).to(DEV)
+    lin = lambda w: linear.linear_no_bias(w.to(DEV))
+    pos = torch.from_numpy(b.positions).to(DEV)
+    outs = []
+    for fuse in (True, False):
+        layer = qwen35.LinearAttention(lin(P["qkv"]), lin(P["z"]), lin(P["b"]), lin(P["a"]), P["conv"].to(DEV),
+                                       (-torch.exp(P["A_log"])).to(DEV), P["dt_bias"].to(DEV), P["norm"].to(DEV), lin(P["out"]),
+                                       Hk, Hv, 1e-6, fuse_conv=fuse)
+        assert layer.fuse_conv == fuse
+        outs.append(layer.mix(x, b.cu_seqlens, pos).clone())
+    ctx.sync()
+    assert torch.isfinite(outs[0]).all()
+    assert torch.equal(outs[0], outs[1])
