@@ -73,7 +73,8 @@ long long s1_launch_count(const s1_ctx* ctx);
  * makes the projections' CTAs draw their tiles from a counter at run time instead of working through fixed shares: a CTA
  * that reaches its SM late, because blocks of a collective running beside the projection were in its way, then finds
  * little left to do, where a fixed share would hold the whole launch back (a few microseconds dearer per launch, so
- * off by default; the tensor-parallel layers turn it on around their overlapped sums); "exchange_wait_ms" = how long the
+ * off by default; a separate kernel, built for the 256 x 256 pair tiles that large projections use - other shapes keep
+ * their fixed shares; the tensor-parallel layers turn it on around their overlapped sums); "exchange_wait_ms" = how long the
  * symmetric-memory exchange kernel waits for its peers (default 10000). */
 int s1_set_option(s1_ctx* ctx, const char* name, long long value);
 

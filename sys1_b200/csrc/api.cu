@@ -205,9 +205,18 @@ static int launch_gemm(s1_ctx* ctx, const CUtensorMap& a, const CUtensorMap& b0,
                        const CUtensorMap& ty, const GemmParams& p) {
     using Cfg = GemmCfg<BN, CTAS>;
     auto kern = s1_gemm_kernel<BN, EPI, MODE, CTAS>;
+    // the kernel that draws its tiles at run time exists for the 256 x 256 pair tiles (the large projections a collective runs
+    // beside); every other shape keeps its fixed shares whatever the option says
+    constexpr bool kHasDyn = (BN == 256 && CTAS == 2);
+    if constexpr (kHasDyn) {
+        if (p.dynamic_tiles) kern = s1_gemm_kernel<BN, EPI, MODE, CTAS, true>;
+    }
     static thread_local int configured_device = -1;
     if (configured_device != ctx->device) {
-        S1_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::smem_bytes(StoreCfg<BN, EPI, CTAS>::kStagingBytes)));
+        const int smem = Cfg::smem_bytes(StoreCfg<BN, EPI, CTAS>::kStagingBytes);
+        S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_gemm_kernel<BN, EPI, MODE, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if constexpr (kHasDyn)
+            S1_CUDA_OK(ctx, cudaFuncSetAttribute(s1_gemm_kernel<BN, EPI, MODE, CTAS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured_device = ctx->device;
     }
     const int tiles = p.tiles_m * p.tiles_n;

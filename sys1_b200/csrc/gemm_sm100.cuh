@@ -52,7 +52,7 @@ struct GemmParams {
     const __nv_bfloat16* bias;      // [n_out] or null
     int* status;                    // device int[4]: {code, block, role, tile}; 0 = ok
     unsigned int* tile_counter;     // device uint[2], zero between launches: {next tile to hand out, units that are done}
-    int dynamic_tiles;              // 0: every unit works through a fixed share of the tiles; 1: tiles are drawn at run time
+    int dynamic_tiles;              // host side: launch the DYN kernel (tiles drawn at run time) where one is built
     // MODE 8 (rotary embedding in the epilogue): output columns [0, rope_cols) are heads of 64 columns whose halves are
     // rotated by the f32 table row of the token's position; columns past rope_cols are written as they are
     const float* rope_cos;          // [rope_max, 32]
@@ -403,7 +403,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     }
 }
 
-template <int BN, int EPI, int MODE, int CTAS>
+// DYN: the tiles past a unit's first are drawn at run time (see "tile feed" below); compiled as a kernel of its own so that
+// the default kernels carry none of that code (their launches of a few tiles are sensitive to every instruction fetched).
+template <int BN, int EPI, int MODE, int CTAS, bool DYN = false>
 __global__ void __launch_bounds__(gemm_threads<BN, EPI>(), 1)
 s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmY,
@@ -453,7 +455,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             mbar_init(tfull0 + 8u * a, 1);
             mbar_init(tempty0 + 8u * a, EW * CTAS);
         }
-        if (p.dynamic_tiles)
+        if constexpr (DYN)
             for (int f = 0; f < kFeedSlots; ++f) mbar_init(feed_bar0 + 8u * f, 1);
         *abort_flag = 0;
         fence_mbar_init();
@@ -486,8 +488,8 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ---- tile feed. Lane 0 of the leader's producer warp decides which tile each iteration works on and publishes it to
     // every role of the CTA (pair) through a small ring in shared memory: slot `(it - 1) % kFeedSlots` holds the tile of
     // iteration `it` >= 1 (-1: no more), its barrier's phase says it is there; iteration 0 is always tile `unit`.
-    // By default the sequence is the unit's fixed share (`unit + it * num_units`), which every role works out by itself:
-    // nothing is published. With `dynamic_tiles` the tiles past the first are drawn from a counter in global memory (a draw n
+    // In the default kernels (DYN = false) the sequence is the unit's fixed share (`unit + it * num_units`), which every role works out by itself:
+    // nothing is published. In the DYN kernels (option `dynamic_tiles`; built for the 256 x 256 pair tiles) the tiles past the first are drawn from a counter in global memory (a draw n
     // stands for tile `num_units + n`): a CTA that reaches its SM late - blocks of a collective running beside the
     // projection were in the way - then finds little left to do, where a fixed share would make the whole launch wait
     // for it. Draws are issued a tile ahead of their use; the burst of draws at the start of a launch and the hand-over to
@@ -497,7 +499,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     unsigned fixed_draws = 0;
     auto feed_draw_raw = [&]() -> unsigned {
         // fixed shares (tile `unit + k * num_units` for the k-th draw): the same feed, no traffic on the counter
-        if (!p.dynamic_tiles) return (fixed_draws++) * static_cast<unsigned>(num_units) + static_cast<unsigned>(unit);
+        if constexpr (!DYN) return (fixed_draws++) * static_cast<unsigned>(num_units) + static_cast<unsigned>(unit);
         return atomicAdd(p.tile_counter, 1u);
     };
     // The drawer that learns there is nothing left says so once; the last of all units to say so puts both counters back
@@ -506,7 +508,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     auto feed_drained = [&]() {
         if (drained) return;
         drained = true;
-        if (!p.dynamic_tiles) return;
+        if constexpr (!DYN) return;
         if (atomicAdd(p.tile_counter + 1, 1u) == static_cast<unsigned>(num_units) - 1u) {
             p.tile_counter[0] = 0u;
             p.tile_counter[1] = 0u;
@@ -519,7 +521,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         return -1;
     };
     auto feed_publish = [&](uint32_t it, int tile) {
-        if (!p.dynamic_tiles) return;  // every role works the fixed sequence out by itself
+        if constexpr (!DYN) return;  // every role works the fixed sequence out by itself
         const uint32_t slot = (it - 1u) % kFeedSlots;
         st_shared_u32(feed_tile0 + 4u * slot, static_cast<uint32_t>(tile));
         mbar_arrive(feed_bar0 + 8u * slot);
@@ -534,7 +536,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tile = first_tile;
             return true;
         }
-        if (!p.dynamic_tiles) {
+        if constexpr (!DYN) {
             const long long t = static_cast<long long>(it) * num_units + unit;
             tile = (first_tile >= 0 && t < num_tiles) ? static_cast<int>(t) : -1;
             return true;
@@ -554,7 +556,7 @@ s1_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // nothing between two tiles. (Waiting here would deadlock the first tile: its successor is published only once the
     // producer has issued all of its loads, which needs the MMA issuer to consume them.)
     auto feed_try = [&](uint32_t it, int& tile) -> bool {
-        if (!p.dynamic_tiles) return feed_take(it, tile);
+        if constexpr (!DYN) return feed_take(it, tile);
         const uint32_t slot = (it - 1u) % kFeedSlots;
         const bool there = (CTAS == 2 && cta_rank != 0) ? mbar_try_wait_cluster(feed_bar0 + 8u * slot, ((it - 1u) / kFeedSlots) & 1u)
                                                         : mbar_try_wait(feed_bar0 + 8u * slot, ((it - 1u) / kFeedSlots) & 1u);
