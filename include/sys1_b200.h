@@ -381,7 +381,9 @@ int s1_allreduce_wait_ticket(s1_ctx* ctx, long long ticket);
  * sum lose few SMs to it; bit-identical results on all ranks. Tickets
  * and waits work as for the NCCL path; a context that only sums symmetric buffers needs no s1_comm_init. The ranks meet
  * through the flag arrays with bounded polls: a rank that never shows up makes the others give up after
- * "exchange_wait_ms" (s1_set_option, default 10000) and s1_sync report S1_EKERNEL; the context stays usable.
+ * "exchange_wait_ms" (s1_set_option, default 10000) and s1_sync report S1_EKERNEL; the context stays usable. The
+ * ranks' epoch counters no longer agree after that: before summing again every rank zeroes its flag array and registers
+ * anew (which restarts the epochs).
  * `size` = 0 forgets the registration (the other arguments are ignored). The caller keeps the memory mapped until then.
  */
 #define S1_EXCHANGE_FLAG_BYTES 4096
