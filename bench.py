@@ -210,7 +210,7 @@ def cpu_encoder(budget_s: float = 20.0):
             oracle.encoder_forward(ids, w, cfg, dtype="f32")
 
     dt, n = _time_cpu(step, 2, 1, budget_s)
-    return {"value": 4096 / (dt * 14), "unit": "tokens/s", "cores": cores, "kind": "port",
+    return {"value": 4096 / (dt * 14), "unit": "tokens/s", "cores": cores, "kind": "port", "seconds_per_sample": dt,
             "sample": f"2 of 28 layers (1 global + 1 local) on {len(seqs)} sequences totalling 4096 tokens, f32 torch CPU oracle, "
                       f"{n} timed passes; the 28-layer figure is that time x 14 (extrapolated)"}
 
@@ -280,7 +280,7 @@ def cpu_decoder(shape: str, tokens: int, budget_s: float = 20.0):
 
     dt, n = _time_cpu(step, 2, 1, budget_s)
     groups = 6 if shape == "small" else 16
-    return {"value": tokens / (dt * groups), "unit": "tokens/s", "cores": cores, "kind": "port",
+    return {"value": tokens / (dt * groups), "unit": "tokens/s", "cores": cores, "kind": "port", "seconds_per_sample": dt,
             "sample": f"one (linear, linear, linear, full) group on {len(seqs)} sequences totalling {tokens} tokens, f32 torch CPU oracle, "
                       f"{n} timed passes; the whole stack is that time x {groups} (extrapolated)"}
 
@@ -888,7 +888,9 @@ def reference_line(args, warmup):
     else:
         cb = cpu_encoder_base(60.0) if args.workload == "base" else cpu_encoder(60.0) if args.workload == "encoder" else cpu_decoder("small" if args.workload == "decoder" else "27b",
                                                                                 2048 if args.workload == "decoder" else 512, 60.0)
-        val, n, ms = cb["value"], 1, None
+        val, n = cb["value"], 1
+        # one "step" of these arms is one timed pass over the sample the block describes
+        ms = cb["seconds_per_forward"] * 1e3 if "seconds_per_forward" in cb else cb.get("seconds_per_sample", 0.0) * 1e3 or None
         metric, unit = {"base": "encoder tokens/s", "encoder": "encoder tokens/s", "decoder": "decoder tokens/s",
                         "tp": "27B layer-group tokens/s"}[args.workload], "tokens/s"
         workload = {"base": "ModernBERT-base encoder forward, 8 x 512 ids", "encoder": "ModernBERT-large-shaped encoder forward",
