@@ -354,6 +354,30 @@ def encoder_block(args, rank, world, dev, steps, warmup, shape="large"):
     l0 = ctx.launch_count()
     ms = _timed(fwd, steps, world, dev)
     launches = ctx.launch_count() - l0
+    # the same forward replayed from one CUDA graph (the batch's tables come from the batch plan, so nothing in a pass copies
+    # from host memory and the whole pass can be captured): what a serving loop does for a batch shape it sees again, and
+    # the number that matters where a pass is a few hundred launches of a few microseconds each
+    ms_graph = None
+    if shape == "base" or args.graph:
+        try:
+            cap = torch.cuda.Stream(dev)
+            with torch.cuda.stream(cap):
+                cap_ctx = device.load(dev.index)   # the capture stream's context, created (and warmed) before the capture
+                for _ in range(2):
+                    fwd()
+                cap_ctx.sync()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=cap):
+                    y_graph = fwd()
+            torch.cuda.synchronize()
+            y_eager = fwd()
+            graph.replay()
+            torch.cuda.synchronize()
+            if not torch.equal(y_graph, y_eager):
+                raise RuntimeError("graph replay and eager pass disagree")
+            ms_graph = _timed(graph.replay, steps, world, dev)
+        except Exception as exc:  # noqa: BLE001 - the eager numbers stand on their own
+            ms_graph = f"unavailable: {exc!r}"[:200]
     # end to end through the public call: token ids and positions from pinned host memory every step, final hidden states
     # back to pinned host memory every step (copies on side streams, overlapped with the previous / next step)
     host_ids, host_pos = ids.cpu().pin_memory(), pos.to(torch.int32).cpu().pin_memory()
@@ -396,6 +420,8 @@ def encoder_block(args, rank, world, dev, steps, warmup, shape="large"):
             "config": {"workload": what + ", every stage through the C ABI (projections, attention, norms, RoPE, embedding lookup)",
                        "sequences": int(len(lens)), "parallelism": f"replicas x{world}"},
             "projection_tflops": world * T * flops_tok / (ms * 1e-3) / 1e12, "attention": attn_stats,
+            **({"graph_replay": ({"ms_per_step": ms_graph, "value": world * T / (ms_graph * 1e-3), "unit": "tokens/s"}
+                                 if isinstance(ms_graph, float) else {"note": ms_graph})} if ms_graph is not None else {}),
             "e2e": {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": 8 * T, "d2h_bytes_per_step": 2 * T * cfg.hidden_size},
             "gpu_launches": launches}
