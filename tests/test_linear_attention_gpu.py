@@ -110,7 +110,8 @@ def test_linear_attention_layer_on_a_packed_batch(ctx):
     assert max_rel(got, want) <= 2e-2
 
 
-@pytest.mark.parametrize("lens,Hk,Hv", [([70, 9, 130], 4, 8), ([1, 2, 3, 64, 65, 127, 128, 129, 5], 2, 2), ([700, 61], 2, 6)])
+@pytest.mark.parametrize("lens,Hk,Hv", [([70, 9, 130], 4, 8), ([1, 2, 3, 64, 65, 127, 128, 129, 5], 2, 2), ([700, 61], 2, 6),
+                                        ([2048, 1500, 64, 1, 483], 16, 16)])
 def test_conv_inside_the_recurrence_is_bit_identical_to_the_two_calls(ctx, lens, Hk, Hv):
     """`s1_gated_delta_rule_conv` applies the causal conv + SiLU to the rows its first kernel stages, with three rows of
     history per 64-token chunk; `s1_conv_silu` followed by `s1_gated_delta_rule` is the same arithmetic in two passes.
