@@ -297,15 +297,21 @@ static int linear_impl(s1_ctx* ctx, const s1_linear_desc* lin, const void* x, lo
     const int tiles_m1 = (T + kBM - 1) / kBM;
     if (ctx->opt_gemm_bn == 512 || ctx->opt_gemm_bn == 384 || (ctx->opt_gemm_bn == 0 && pair_tiles >= ctx->sm_count / 2)) {
         ctas = 2;
-        // 192-wide pair tiles fill the waves of CTA pairs better for N = 768 (4 x 192 instead of 3 x 256)
+        // 192-wide pair tiles: a quarter less work per tile at about 0.9 of the cost of a 256-wide one (measured on the N = 768
+        // projections: 13.6 against 14.5 us and 17.0 against 18.2 us at T = 8192, where 96 tiles of 256 columns need two waves of
+        // the 74 CTA pairs and 128 tiles of 192 columns need two shorter ones; slower at T = 16384 and 32768, where they need
+        // a wave more). Taken when the wave count says so, for plain epilogues whose width is a multiple of 192.
         if (epi == S1_EPI_NONE) {
-            const long long m2 = (T + 2 * kBM - 1) / (2 * kBM);
-            const long long t192 = m2 * ((n_out + 191) / 192);
-            const int pairs = ctx->sm_count / 2;
-            // (measured: no faster than 256-wide tiles on the N = 768 projections, so only on request)
-            (void)t192;
-            (void)pairs;
-            if (ctx->opt_gemm_bn == 384) bn = 192;
+            if (ctx->opt_gemm_bn == 384) {
+                bn = 192;
+            } else if (ctx->opt_gemm_bn == 0 && !rope && !ctx->opt_dynamic_tiles && n_out % 192 == 0) {
+                const long long m2 = (T + 2 * kBM - 1) / (2 * kBM);
+                const int sms = (ctx->opt_gemm_sms > 0 && ctx->opt_gemm_sms < ctx->sm_count) ? ctx->opt_gemm_sms : ctx->sm_count;
+                const long long pairs = sms / 2;
+                const long long waves256 = (m2 * n_tiles256 + pairs - 1) / pairs;
+                const long long waves192 = (m2 * (n_out / 192) + pairs - 1) / pairs;
+                if (10 * waves256 > 9 * waves192) bn = 192;
+            }
         }
     } else if (ctx->opt_gemm_bn == 128 || ctx->opt_gemm_bn == 256) {
         bn = ctx->opt_gemm_bn;
